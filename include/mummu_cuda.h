@@ -1,0 +1,183 @@
+/*
+ * mummu_cuda.h — C ABI of the B200 (sm_100a) sparse mixture-of-experts expert bank.
+ *
+ * This is the boundary a `mummu-cuda` FFI crate binds: plain pointers and sizes, no C++ or
+ * framework types.  The reference project (physics515/Mummu) has no FFI for this path; every entry
+ * point below names the reference interface it stands in for (file:line inside the reference
+ * tree, `crates/mummu/src/...`).
+ *
+ * Conventions
+ *  - Every function returns an int32 status (MUMMU_OK = 0).  Nothing aborts; nothing falls back to
+ *    the CPU.  `mummu_cuda_last_error()` returns the calling thread's last message.
+ *  - Contract violations (bad top_k, mismatched widths, wrong byte counts) return
+ *    MUMMU_ERR_CONTRACT with a message that carries the reference's panic stem ("top_k",
+ *    "num_experts_per_tok", ...), so a Rust wrapper can re-raise the panic the reference raises
+ *    (nn/moe.rs:62-76, 119-126, 250-253).
+ *  - A handle serialises its own calls with an internal lock; distinct handles are independent.
+ *  - Matrices are row-major.  Router weight: [hidden, experts] (burn `Linear` stores [in, out],
+ *    nn/moe.rs:1642) or [experts, hidden] (GGUF `ffn_gate_inp`, models/olmoe.rs:338-339), chosen by
+ *    a flag.  Banks: [experts, out, in], byte-identical to GGUF `ffn_{gate,up,down}_exps`
+ *    (nn/moe.rs:19-30).  For MUMMU_Q4_K a bank row is in/256 super-blocks of 144 bytes
+ *    (gguf.rs:342, 372).
+ */
+#ifndef MUMMU_CUDA_H
+#define MUMMU_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MUMMU_OK               0
+#define MUMMU_ERR_CONTRACT     1   /* caller broke the interface contract (reference: panic)   */
+#define MUMMU_ERR_DEVICE       2   /* CUDA runtime / driver error                               */
+#define MUMMU_ERR_TIMEOUT      3   /* a bounded device-side wait ran out                        */
+#define MUMMU_ERR_UNSUPPORTED  4   /* valid request this build has no kernel for                */
+#define MUMMU_ERR_NUMERIC      5   /* non-finite router logit (qwen4exp/experts.rs:553-560)     */
+
+typedef enum {
+    MUMMU_F32  = 0,
+    MUMMU_F16  = 1,
+    MUMMU_BF16 = 2,
+    MUMMU_Q4_K = 3      /* GGUF Q4_K super-blocks; weights only */
+} mummu_dtype;
+
+#define MUMMU_BANK_GATE 0
+#define MUMMU_BANK_UP   1
+#define MUMMU_BANK_DOWN 2
+
+/* router weight memory order */
+#define MUMMU_ROUTER_IN_OUT 0      /* [hidden, experts] — burn Linear (nn/moe.rs:1642)          */
+#define MUMMU_ROUTER_OUT_IN 1      /* [experts, hidden] — GGUF ffn_gate_inp (olmoe.rs:338-339)  */
+
+typedef struct MummuMoe MummuMoe;  /* opaque: device weights, scratch, one internal stream     */
+
+/* Stands in for `SparseMoeConfig` (nn/moe.rs:42-50).  `experts` is the router width; this handle
+ * stores `experts_local` of them starting at global id `expert_first` (expert parallelism keeps a
+ * contiguous block per GPU; single GPU: expert_first = 0, experts_local = experts). */
+typedef struct {
+    int32_t device;          /* CUDA ordinal                                                   */
+    int32_t hidden;          /* hidden_size                                                     */
+    int32_t inter;           /* expert_intermediate_size                                        */
+    int32_t experts;         /* num_experts (>= 2)                                              */
+    int32_t top_k;           /* num_experts_per_tok, 1..=experts: upper bound for later calls   */
+    int32_t act_dtype;       /* mummu_dtype of x / y: F32, F16 or BF16                          */
+    int32_t weight_dtype;    /* mummu_dtype of the banks: F32, F16, BF16 or Q4_K                */
+    int32_t expert_first;    /* first global expert id held by this handle                      */
+    int32_t experts_local;   /* number of experts held by this handle                           */
+    int32_t max_tokens;      /* scratch is sized for this many tokens (grown on demand if 0)   */
+} MummuMoeConfig;
+
+/* -------- life cycle ---------------------------------------------------------------------- */
+
+/* `SparseMoeConfig::init` (nn/moe.rs:61-99): checks experts >= 2, 1 <= top_k <= experts,
+ * hidden, inter >= 1 (messages keep the reference's wording), allocates the device banks. Weights
+ * start undefined; set them with the two calls below.  Q4_K needs hidden % 256 == 0 and
+ * inter % 256 == 0 (whole super-blocks per row, gguf.rs:1442-1460). */
+int32_t mummu_moe_create(const MummuMoeConfig* cfg, MummuMoe** out);
+int32_t mummu_moe_destroy(MummuMoe* moe);
+
+/* Router `gate: Linear` weight (nn/moe.rs:36-37, 92; olmoe.rs:338-339).  `w` is a HOST pointer to
+ * hidden*experts values of `dtype` (F32/F16/BF16) in `layout` order; copied.  `bias` is NULL (the
+ * reference builds the router without bias) or `experts` f32 values added to the logits. */
+int32_t mummu_moe_set_router(MummuMoe* moe, const void* w, int32_t dtype, int32_t layout,
+                             const float* bias);
+
+/* One of `MoeExperts::{gate, up, down}` (nn/moe.rs:22-30): `data` points to experts_local*out*in
+ * values of the handle's weight_dtype (for Q4_K: the raw ggml bytes), `bytes` is checked.
+ * `on_device` != 0 means `data` is a device pointer on the handle's device.  Copied. */
+int32_t mummu_moe_set_bank(MummuMoe* moe, int32_t which, const void* data, size_t bytes,
+                           int32_t on_device);
+
+/* -------- the layer ------------------------------------------------------------------------- */
+
+/* `SparseMoe::forward` / `SparseMoePerExpert::forward` (nn/moe.rs:116-177, 214-219) on the
+ * flattened [tokens, hidden] input: router -> softmax over all experts (f32) -> top_k of the
+ * probabilities (ties: lowest expert id) -> optional renormalisation -> routed SwiGLU experts ->
+ * weighted sum in ascending expert order.  x and y hold tokens*hidden values of act_dtype;
+ * `on_device` != 0: both are device pointers and the work is queued on `stream` (a cudaStream_t,
+ * NULL = the handle's own stream) without waiting; otherwise both are host pointers and the call
+ * returns when y is written.  Requires expert_first == 0 and experts_local == experts. */
+int32_t mummu_moe_forward(MummuMoe* moe, const void* x, void* y, int32_t tokens, int32_t top_k,
+                          int32_t norm_topk_prob, int32_t on_device, void* stream);
+
+/* Router only — `SparseMoePerExpert::route` (nn/moe.rs:247-290) / `qwen4exp::experts::route`
+ * (models/qwen4exp/experts.rs:541-582): ids_out[tokens*top_k] (descending probability, ties to
+ * the lowest id) and w_out[tokens*top_k] (f32).  Pointers follow `on_device` as above. */
+int32_t mummu_moe_route(MummuMoe* moe, const void* x, int32_t tokens, int32_t top_k,
+                        int32_t norm_topk_prob, int32_t* ids_out, float* w_out,
+                        int32_t on_device, void* stream);
+
+/* Group the routed (token, slot) pairs by expert — the `Routing.per_expert` lists of
+ * nn/moe.rs:275-289 as flat device arrays.  ids: device [tokens*top_k] global expert ids.
+ * Outputs (device): counts[experts] rows per expert; offsets[experts+1] exclusive prefix sum;
+ * row_token[tokens*top_k] token of each sorted row (ascending token within an expert);
+ * pos[tokens*top_k] sorted row of pair (token, slot).  Any output may be NULL. */
+int32_t mummu_moe_permute(MummuMoe* moe, const int32_t* ids, int32_t tokens, int32_t top_k,
+                          int32_t* counts, int32_t* offsets, int32_t* row_token, int32_t* pos,
+                          void* stream);
+
+/* Expert bank over rows already grouped by expert — the loop body of
+ * `SparseMoePerExpert::run_local` (nn/moe.rs:301-326) without the scatter: xs device
+ * [rows, hidden] act_dtype holding, expert by expert in ascending LOCAL id, counts[e] rows;
+ * counts device [experts_local]; ys device [rows, hidden] act_dtype receives
+ * down(silu(gate x) * (up x)) per row. */
+int32_t mummu_moe_experts_grouped(MummuMoe* moe, const void* xs, const int32_t* counts,
+                                  int32_t rows, void* ys, void* stream);
+
+/* Weighted un-permute — the scatter-add of nn/moe.rs:317-325 / 1589-1602 as a gather: for every
+ * token, out = sum over its top_k slots in ASCENDING EXPERT ID of (w * y) with the product and the
+ * sum rounded separately (no fused multiply-add).  ys device [tokens*top_k, hidden] act_dtype,
+ * indexed through pos; ids, w, pos device [tokens*top_k]; out device [tokens, hidden]. */
+int32_t mummu_moe_combine(MummuMoe* moe, const void* ys, const int32_t* ids, const float* w,
+                          const int32_t* pos, int32_t tokens, int32_t top_k, void* out,
+                          void* stream);
+
+/* `ExpertExec::run(&[f32], rows, hidden) -> Vec<f32>` (nn/moe.rs:353-357) and
+ * `RoutedExperts::expert_ffn` (models/qwen4exp/experts.rs:1015-1057): one expert (LOCAL id) on
+ * `rows` f32 rows from host memory, f32 rows back to host memory. */
+int32_t mummu_expert_run(MummuMoe* moe, int32_t expert, const float* x, int32_t rows, float* y);
+
+/* -------- parity taps and counters ----------------------------------------------------------- */
+
+/* The dequantised (or widened) f32 weights of one expert of one bank, [out, in], to HOST memory.
+ * For Q4_K this is `gguf::dequant_q4_k` (gguf.rs:1701-1726) and must match it bit for bit. */
+int32_t mummu_moe_dequant_bank(MummuMoe* moe, int32_t which, int32_t expert, float* out);
+
+/* `ExpertPool::take_hits` (nn/moe.rs:1527-1535): rows served per GLOBAL expert id since the last
+ * call (accumulated by forward); per_expert is a HOST array of `experts` counters; resets them. */
+int32_t mummu_moe_take_hits(MummuMoe* moe, uint64_t* per_expert);
+
+/* Wait for everything queued on the handle's own stream (or `stream`) and report the sticky
+ * device status word: MUMMU_OK, MUMMU_ERR_NUMERIC (non-finite router logit) or
+ * MUMMU_ERR_TIMEOUT. */
+int32_t mummu_moe_sync(MummuMoe* moe, void* stream);
+
+/* Average device time (milliseconds, CUDA events on the launching stream) and launch count of
+ * each internal kernel since the last call — the (bytes, elapsed) ledger of
+ * nn/packed_gemv.rs:1260-1296.  Enable with mummu_moe_set_profiling; names is a HOST buffer that
+ * receives a ';'-separated "name=launches:ms" list. */
+int32_t mummu_moe_set_profiling(MummuMoe* moe, int32_t enabled);
+int32_t mummu_moe_take_profile(MummuMoe* moe, char* names, size_t cap);
+
+/* Number of kernels this handle has launched (for accounting in benchmarks). */
+int64_t mummu_moe_launch_count(const MummuMoe* moe);
+
+/* -------- Q4_K helpers (no counterpart in the reference: it only dequantises Q4_K) ----------- */
+
+/* Encode n_superblocks*256 f32 values (device) to n_superblocks*144 Q4_K bytes (device). */
+int32_t mummu_q4k_quantize(const float* src, void* dst, int64_t n_superblocks, int32_t device,
+                           void* stream);
+/* Decode device Q4_K bytes to device f32 exactly as gguf.rs:1701-1726 does. */
+int32_t mummu_q4k_dequantize(const void* src, float* dst, int64_t n_superblocks, int32_t device,
+                             void* stream);
+
+const char* mummu_cuda_last_error(void);
+const char* mummu_cuda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MUMMU_CUDA_H */

@@ -1,0 +1,517 @@
+// extern "C" surface of the library: handle life cycle, weight upload, the layer call and its
+// stages.  Declarations and the reference interface each call stands in for: include/mummu_cuda.h.
+#include <cstdarg>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace mummu {
+
+static thread_local std::string g_error;
+
+void set_error(const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_error = buf;
+}
+
+size_t bank_row_bytes(const MummuMoeConfig& c, int which) {
+    size_t in_dim = which == MUMMU_BANK_DOWN ? c.inter : c.hidden;
+    if (c.weight_dtype == MUMMU_Q4_K) return in_dim / Q4K_BLOCK_ELEMS * Q4K_BLOCK_BYTES;
+    return in_dim * dtype_size(c.weight_dtype);
+}
+
+size_t bank_total_bytes(const MummuMoeConfig& c, int which) {
+    size_t out_dim = which == MUMMU_BANK_DOWN ? c.hidden : c.inter;
+    return bank_row_bytes(c, which) * out_dim * (size_t)c.experts_local;
+}
+
+LaunchScope::LaunchScope(MummuMoe* m_, cudaStream_t s_, const char* name_) : m(m_), s(s_), name(name_) {
+    m->launches += 1;
+    if (!m->prof.enabled) return;
+    auto take = [&]() {
+        cudaEvent_t e;
+        if (!m->prof.pool.empty()) {
+            e = m->prof.pool.back();
+            m->prof.pool.pop_back();
+        } else {
+            cudaEventCreate(&e);
+        }
+        return e;
+    };
+    a = take();
+    b = take();
+    cudaEventRecord(a, s);
+}
+
+LaunchScope::~LaunchScope() {
+    if (!a) return;
+    cudaEventRecord(b, s);
+    m->prof.pending.push_back({name, a, b});
+}
+
+template <typename T>
+static int dev_alloc(T** p, size_t n) {
+    *p = nullptr;
+    if (n == 0) n = 1;
+    MUMMU_CUDA_TRY(cudaMalloc((void**)p, n * sizeof(T)));
+    return MUMMU_OK;
+}
+
+static void free_scratch(MummuMoe* m) {
+    cudaFree(m->logits); cudaFree(m->tile_done); cudaFree(m->ids); cudaFree(m->wts);
+    cudaFree(m->row_token); cudaFree(m->pos); cudaFree(m->xs); cudaFree(m->hact); cudaFree(m->ys);
+    cudaFree(m->io_x); cudaFree(m->io_y);
+    m->logits = nullptr; m->tile_done = nullptr; m->ids = nullptr; m->wts = nullptr;
+    m->row_token = nullptr; m->pos = nullptr; m->xs = nullptr; m->hact = nullptr; m->ys = nullptr;
+    m->io_x = nullptr; m->io_y = nullptr;
+    m->cap_tokens = 0;
+}
+
+int ensure_scratch(MummuMoe* m, int64_t tokens) {
+    if (tokens <= m->cap_tokens) return MUMMU_OK;
+    const MummuMoeConfig& c = m->cfg;
+    MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    MUMMU_CUDA_TRY(cudaDeviceSynchronize());
+    free_scratch(m);
+    int64_t T = tokens;
+    int64_t rows = T * c.top_k;
+    size_t act = dtype_size(c.act_dtype);
+    int rc;
+    if ((rc = dev_alloc(&m->logits, (size_t)T * c.experts))) return rc;
+    if ((rc = dev_alloc(&m->tile_done, (size_t)T / 4 + 2))) return rc;
+    MUMMU_CUDA_TRY(cudaMemset(m->tile_done, 0, ((size_t)T / 4 + 2) * sizeof(int32_t)));
+    if ((rc = dev_alloc(&m->ids, (size_t)rows))) return rc;
+    if ((rc = dev_alloc(&m->wts, (size_t)rows))) return rc;
+    if ((rc = dev_alloc(&m->row_token, (size_t)rows))) return rc;
+    if ((rc = dev_alloc(&m->pos, (size_t)rows))) return rc;
+    if ((rc = dev_alloc((uint8_t**)&m->xs, (size_t)rows * c.hidden * act))) return rc;
+    if ((rc = dev_alloc((float**)&m->hact, (size_t)rows * c.inter))) return rc;
+    if ((rc = dev_alloc((float**)&m->ys, (size_t)rows * c.hidden))) return rc;
+    if ((rc = dev_alloc((uint8_t**)&m->io_x, (size_t)T * c.hidden * act))) return rc;
+    if ((rc = dev_alloc((uint8_t**)&m->io_y, (size_t)T * c.hidden * act))) return rc;
+    m->cap_tokens = T;
+    return MUMMU_OK;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        cudaGetDevice(&cur);
+        if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+static int check_ready(MummuMoe* m, bool need_router, bool need_banks) {
+    if (need_router) MUMMU_REQUIRE(m->router_set, "MoE: router weight was never set (mummu_moe_set_router)");
+    if (need_banks)
+        MUMMU_REQUIRE(m->bank_set[0] && m->bank_set[1] && m->bank_set[2],
+                      "MoE: expert banks were never set (mummu_moe_set_bank gate/up/down)");
+    return MUMMU_OK;
+}
+
+static int check_top_k(const MummuMoe* m, int top_k) {
+    MUMMU_REQUIRE(top_k >= 1 && top_k <= m->cfg.experts,
+                  "MoE forward: top_k (%d) must be in 1..=num_experts (%d)", top_k, m->cfg.experts);
+    MUMMU_REQUIRE(top_k <= m->cfg.top_k,
+                  "MoE forward: top_k (%d) exceeds the num_experts_per_tok (%d) this handle was "
+                  "created for", top_k, m->cfg.top_k);
+    return MUMMU_OK;
+}
+
+static int read_status(MummuMoe* m, cudaStream_t s) {
+    int32_t st = 0;
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(&st, m->status, sizeof(st), cudaMemcpyDeviceToHost, s));
+    MUMMU_CUDA_TRY(cudaStreamSynchronize(s));
+    if (st == 0) return MUMMU_OK;
+    MUMMU_CUDA_TRY(cudaMemsetAsync(m->status, 0, sizeof(int32_t), s));
+    if (st & STATUS_TIMEOUT) {
+        set_error("a bounded device-side wait ran out");
+        return MUMMU_ERR_TIMEOUT;
+    }
+    set_error("router logit is not finite (NaN or infinity in the activations or router weight)");
+    return MUMMU_ERR_NUMERIC;
+}
+
+// router -> permute -> experts -> combine, all on stream s, device pointers
+static int forward_device(MummuMoe* m, const void* x, void* y, int64_t tokens, int top_k, int norm,
+                          cudaStream_t s) {
+    const MummuMoeConfig& c = m->cfg;
+    int rc;
+    if ((rc = launch_router(m, x, tokens, top_k, norm, m->ids, m->wts, m->counts, s))) return rc;
+    if (decode_q4k_supported(c, tokens) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
+        if ((rc = launch_decode_q4k(m, x, tokens, top_k, s))) return rc;
+    } else {
+        if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
+        int64_t max_rows = tokens;  // an expert serves a token at most once
+        if ((rc = launch_experts_simt(m, x, c.act_dtype, m->row_token, m->counts, m->offsets, max_rows,
+                                      tokens * top_k, m->ys, MUMMU_F32, -1, s)))
+            return rc;
+    }
+    return launch_combine(m, m->ys, MUMMU_F32, m->ids, m->wts, m->pos, tokens, top_k, y, s);
+}
+
+}  // namespace mummu
+
+using namespace mummu;
+
+extern "C" {
+
+const char* mummu_cuda_last_error(void) { return g_error.c_str(); }
+const char* mummu_cuda_version(void) { return "mummu-cuda 0.1 (sm_100a)"; }
+
+int32_t mummu_moe_create(const MummuMoeConfig* cfg, MummuMoe** out) {
+    MUMMU_REQUIRE(cfg && out, "mummu_moe_create: null argument");
+    *out = nullptr;
+    MUMMU_REQUIRE(cfg->experts >= 2,
+                  "MoE: num_experts must be >= 2 (got %d); use SwiGluMlp for a dense FFN", cfg->experts);
+    MUMMU_REQUIRE(cfg->top_k >= 1 && cfg->top_k <= cfg->experts,
+                  "MoE: num_experts_per_tok (%d) must be in 1..=num_experts (%d)", cfg->top_k, cfg->experts);
+    MUMMU_REQUIRE(cfg->hidden >= 1 && cfg->inter >= 1,
+                  "MoE: hidden_size and expert_intermediate_size must be >= 1");
+    MUMMU_REQUIRE(cfg->act_dtype == MUMMU_F32 || cfg->act_dtype == MUMMU_F16 || cfg->act_dtype == MUMMU_BF16,
+                  "MoE: activation dtype %d is not F32, F16 or BF16", cfg->act_dtype);
+    MUMMU_REQUIRE(cfg->weight_dtype >= MUMMU_F32 && cfg->weight_dtype <= MUMMU_Q4_K,
+                  "MoE: weight dtype %d is not F32, F16, BF16 or Q4_K", cfg->weight_dtype);
+    MUMMU_REQUIRE(cfg->experts_local >= 1 && cfg->expert_first >= 0 &&
+                      cfg->expert_first + cfg->experts_local <= cfg->experts,
+                  "MoE: local experts [%d, %d) are not inside 0..%d", cfg->expert_first,
+                  cfg->expert_first + cfg->experts_local, cfg->experts);
+    if (cfg->weight_dtype == MUMMU_Q4_K)
+        MUMMU_REQUIRE(cfg->hidden % Q4K_BLOCK_ELEMS == 0 && cfg->inter % Q4K_BLOCK_ELEMS == 0,
+                      "MoE: Q4_K rows hold whole 256-value super-blocks (hidden %d, intermediate %d)",
+                      cfg->hidden, cfg->inter);
+    int ndev = 0;
+    MUMMU_CUDA_TRY(cudaGetDeviceCount(&ndev));
+    MUMMU_REQUIRE(cfg->device >= 0 && cfg->device < ndev, "MoE: CUDA device %d of %d", cfg->device, ndev);
+    DeviceGuard guard(cfg->device);
+    MummuMoe* m = new MummuMoe();
+    m->cfg = *cfg;
+    int rc = MUMMU_OK;
+    do {
+        cudaError_t err = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
+        if (err != cudaSuccess) { set_error("cudaStreamCreate: %s", cudaGetErrorString(err)); rc = MUMMU_ERR_DEVICE; break; }
+        if ((rc = dev_alloc(&m->router_w, (size_t)cfg->hidden * cfg->experts))) break;
+        for (int b = 0; b < 3 && !rc; ++b) {
+            m->bank_bytes[b] = bank_total_bytes(*cfg, b);
+            rc = dev_alloc((uint8_t**)&m->bank[b], m->bank_bytes[b]);
+        }
+        if (rc) break;
+        if ((rc = dev_alloc(&m->counts, (size_t)cfg->experts))) break;
+        if ((rc = dev_alloc(&m->offsets, (size_t)cfg->experts + 1))) break;
+        if ((rc = dev_alloc(&m->active, (size_t)cfg->experts))) break;
+        if ((rc = dev_alloc(&m->n_active, 1))) break;
+        if ((rc = dev_alloc(&m->hits, (size_t)cfg->experts))) break;
+        if ((rc = dev_alloc(&m->status, 1))) break;
+        cudaMemset(m->hits, 0, sizeof(unsigned long long) * cfg->experts);
+        cudaMemset(m->status, 0, sizeof(int32_t));
+        if (cfg->max_tokens > 0) rc = ensure_scratch(m, cfg->max_tokens);
+    } while (0);
+    if (rc) {
+        mummu_moe_destroy(m);
+        return rc;
+    }
+    *out = m;
+    return MUMMU_OK;
+}
+
+int32_t mummu_moe_destroy(MummuMoe* m) {
+    if (!m) return MUMMU_OK;
+    {
+        DeviceGuard guard(m->cfg.device);
+        if (m->stream) cudaStreamSynchronize(m->stream);
+        free_scratch(m);
+        cudaFree(m->router_w); cudaFree(m->router_bias);
+        for (int b = 0; b < 3; ++b) cudaFree(m->bank[b]);
+        cudaFree(m->counts); cudaFree(m->offsets); cudaFree(m->hits); cudaFree(m->status);
+        cudaFree(m->active); cudaFree(m->n_active);
+        for (auto& p : m->prof.pending) { cudaEventDestroy(p.a); cudaEventDestroy(p.b); }
+        for (auto e : m->prof.pool) cudaEventDestroy(e);
+        if (m->stream) cudaStreamDestroy(m->stream);
+    }
+    delete m;
+    return MUMMU_OK;
+}
+
+int32_t mummu_moe_set_router(MummuMoe* m, const void* w, int32_t dtype, int32_t layout, const float* bias) {
+    MUMMU_REQUIRE(m && w, "mummu_moe_set_router: null argument");
+    MUMMU_REQUIRE(dtype == MUMMU_F32 || dtype == MUMMU_F16 || dtype == MUMMU_BF16,
+                  "router weight dtype %d is not F32, F16 or BF16", dtype);
+    MUMMU_REQUIRE(layout == MUMMU_ROUTER_IN_OUT || layout == MUMMU_ROUTER_OUT_IN, "router layout %d", layout);
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    const int H = m->cfg.hidden, E = m->cfg.experts;
+    std::vector<float> host((size_t)H * E);
+    for (int i = 0; i < H; ++i)
+        for (int e = 0; e < E; ++e) {
+            size_t src = layout == MUMMU_ROUTER_IN_OUT ? (size_t)i * E + e : (size_t)e * H + i;
+            float v;
+            if (dtype == MUMMU_F32) v = ((const float*)w)[src];
+            else if (dtype == MUMMU_F16) v = __half2float(((const __half*)w)[src]);
+            else v = __bfloat162float(((const __nv_bfloat16*)w)[src]);
+            host[(size_t)i * E + e] = v;
+        }
+    MUMMU_CUDA_TRY(cudaMemcpy(m->router_w, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice));
+    if (bias) {
+        if (!m->router_bias) {
+            int rc = dev_alloc(&m->router_bias, (size_t)E);
+            if (rc) return rc;
+        }
+        MUMMU_CUDA_TRY(cudaMemcpy(m->router_bias, bias, sizeof(float) * E, cudaMemcpyHostToDevice));
+    } else if (m->router_bias) {
+        MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
+        cudaFree(m->router_bias);
+        m->router_bias = nullptr;
+    }
+    m->router_set = true;
+    return MUMMU_OK;
+}
+
+int32_t mummu_moe_set_bank(MummuMoe* m, int32_t which, const void* data, size_t bytes, int32_t on_device) {
+    MUMMU_REQUIRE(m && data, "mummu_moe_set_bank: null argument");
+    MUMMU_REQUIRE(which >= 0 && which < 3, "mummu_moe_set_bank: bank %d is not gate(0), up(1) or down(2)", which);
+    MUMMU_REQUIRE(bytes == m->bank_bytes[which],
+                  "mummu_moe_set_bank: bank %d needs %zu bytes ([experts %d, out, in]), got %zu", which,
+                  m->bank_bytes[which], m->cfg.experts_local, bytes);
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    MUMMU_CUDA_TRY(cudaMemcpy(m->bank[which], data, bytes,
+                              on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+    m->bank_set[which] = true;
+    return MUMMU_OK;
+}
+
+int32_t mummu_moe_forward(MummuMoe* m, const void* x, void* y, int32_t tokens, int32_t top_k,
+                          int32_t norm, int32_t on_device, void* stream) {
+    MUMMU_REQUIRE(m, "mummu_moe_forward: null handle");
+    MUMMU_REQUIRE(tokens >= 0, "MoE forward: negative token count %d", tokens);
+    int rc;
+    if ((rc = check_top_k(m, top_k))) return rc;
+    if ((rc = check_ready(m, true, true))) return rc;
+    MUMMU_REQUIRE(m->cfg.expert_first == 0 && m->cfg.experts_local == m->cfg.experts,
+                  "MoE forward: this handle holds experts [%d, %d) of %d; the whole-layer call needs "
+                  "all of them (use the staged calls for expert parallelism)",
+                  m->cfg.expert_first, m->cfg.expert_first + m->cfg.experts_local, m->cfg.experts);
+    if (tokens == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(x && y, "MoE forward: null activation pointer");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    if ((rc = ensure_scratch(m, tokens))) return rc;
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    size_t bytes = (size_t)tokens * m->cfg.hidden * dtype_size(m->cfg.act_dtype);
+    if (on_device) return forward_device(m, x, y, tokens, top_k, norm, s);
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(m->io_x, x, bytes, cudaMemcpyHostToDevice, s));
+    if ((rc = forward_device(m, m->io_x, m->io_y, tokens, top_k, norm, s))) return rc;
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(y, m->io_y, bytes, cudaMemcpyDeviceToHost, s));
+    return read_status(m, s);
+}
+
+int32_t mummu_moe_route(MummuMoe* m, const void* x, int32_t tokens, int32_t top_k, int32_t norm,
+                        int32_t* ids_out, float* w_out, int32_t on_device, void* stream) {
+    MUMMU_REQUIRE(m, "mummu_moe_route: null handle");
+    MUMMU_REQUIRE(tokens >= 0, "MoE route: negative token count %d", tokens);
+    int rc;
+    if ((rc = check_top_k(m, top_k))) return rc;
+    if ((rc = check_ready(m, true, false))) return rc;
+    if (tokens == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(x && ids_out && w_out, "MoE route: null pointer");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    if ((rc = ensure_scratch(m, tokens))) return rc;
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    if (on_device) return launch_router(m, x, tokens, top_k, norm, ids_out, w_out, m->counts, s);
+    size_t bytes = (size_t)tokens * m->cfg.hidden * dtype_size(m->cfg.act_dtype);
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(m->io_x, x, bytes, cudaMemcpyHostToDevice, s));
+    if ((rc = launch_router(m, m->io_x, tokens, top_k, norm, m->ids, m->wts, m->counts, s))) return rc;
+    size_t n = (size_t)tokens * top_k;
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(ids_out, m->ids, n * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(w_out, m->wts, n * sizeof(float), cudaMemcpyDeviceToHost, s));
+    return read_status(m, s);
+}
+
+int32_t mummu_moe_permute(MummuMoe* m, const int32_t* ids, int32_t tokens, int32_t top_k,
+                          int32_t* counts, int32_t* offsets, int32_t* row_token, int32_t* pos,
+                          void* stream) {
+    MUMMU_REQUIRE(m && ids, "mummu_moe_permute: null argument");
+    MUMMU_REQUIRE(tokens >= 0 && top_k >= 1, "mummu_moe_permute: tokens %d, top_k %d", tokens, top_k);
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    int32_t* cnt = counts ? counts : m->counts;
+    int rc;
+    if ((rc = launch_count(m, ids, (int64_t)tokens * top_k, cnt, s))) return rc;
+    return launch_permute(m, ids, tokens, top_k, cnt, offsets, row_token, pos, s);
+}
+
+int32_t mummu_moe_experts_grouped(MummuMoe* m, const void* xs, const int32_t* counts, int32_t rows,
+                                  void* ys, void* stream) {
+    MUMMU_REQUIRE(m && counts, "mummu_moe_experts_grouped: null argument");
+    MUMMU_REQUIRE(rows >= 0, "mummu_moe_experts_grouped: negative row count %d", rows);
+    int rc;
+    if ((rc = check_ready(m, false, true))) return rc;
+    if (rows == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(xs && ys, "mummu_moe_experts_grouped: null activation pointer");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    int64_t tokens_equiv = ((int64_t)rows + m->cfg.top_k - 1) / m->cfg.top_k;
+    if ((rc = ensure_scratch(m, tokens_equiv))) return rc;
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    if ((rc = launch_offsets_from_counts(m, counts, m->cfg.experts_local, m->offsets, s))) return rc;
+    return launch_experts_simt(m, xs, m->cfg.act_dtype, nullptr, counts, m->offsets, rows, rows, ys,
+                               m->cfg.act_dtype, -1, s);
+}
+
+int32_t mummu_moe_combine(MummuMoe* m, const void* ys, const int32_t* ids, const float* w,
+                          const int32_t* pos, int32_t tokens, int32_t top_k, void* out, void* stream) {
+    MUMMU_REQUIRE(m && ys && ids && w && pos && out, "mummu_moe_combine: null argument");
+    MUMMU_REQUIRE(tokens >= 0 && top_k >= 1, "mummu_moe_combine: tokens %d, top_k %d", tokens, top_k);
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    return launch_combine(m, ys, m->cfg.act_dtype, ids, w, pos, tokens, top_k, out, s);
+}
+
+int32_t mummu_expert_run(MummuMoe* m, int32_t expert, const float* x, int32_t rows, float* y) {
+    MUMMU_REQUIRE(m, "mummu_expert_run: null handle");
+    MUMMU_REQUIRE(expert >= 0 && expert < m->cfg.experts_local, "expert %d out of range (%d)", expert,
+                  m->cfg.experts_local);
+    MUMMU_REQUIRE(rows >= 0, "mummu_expert_run: negative row count %d", rows);
+    int rc;
+    if ((rc = check_ready(m, false, true))) return rc;
+    if (rows == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(x && y, "mummu_expert_run: null pointer");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    int64_t tokens_equiv = ((int64_t)rows + m->cfg.top_k - 1) / m->cfg.top_k;
+    if ((rc = ensure_scratch(m, tokens_equiv))) return rc;
+    cudaStream_t s = m->stream;
+    float *dx = nullptr, *dy = nullptr;
+    size_t n = (size_t)rows * m->cfg.hidden;
+    if ((rc = dev_alloc(&dx, n))) return rc;
+    if ((rc = dev_alloc(&dy, n))) { cudaFree(dx); return rc; }
+    cudaError_t err = cudaMemcpyAsync(dx, x, n * sizeof(float), cudaMemcpyHostToDevice, s);
+    if (err == cudaSuccess) {
+        rc = launch_experts_simt(m, dx, MUMMU_F32, nullptr, nullptr, nullptr, rows, rows, dy, MUMMU_F32, expert, s);
+        if (!rc) err = cudaMemcpyAsync(y, dy, n * sizeof(float), cudaMemcpyDeviceToHost, s);
+    }
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    cudaFree(dx);
+    cudaFree(dy);
+    if (rc) return rc;
+    if (err != cudaSuccess) {
+        set_error("mummu_expert_run: %s", cudaGetErrorString(err));
+        return MUMMU_ERR_DEVICE;
+    }
+    return MUMMU_OK;
+}
+
+int32_t mummu_moe_dequant_bank(MummuMoe* m, int32_t which, int32_t expert, float* out) {
+    MUMMU_REQUIRE(m && out, "mummu_moe_dequant_bank: null argument");
+    MUMMU_REQUIRE(which >= 0 && which < 3, "bank %d is not gate(0), up(1) or down(2)", which);
+    MUMMU_REQUIRE(expert >= 0 && expert < m->cfg.experts_local, "expert %d out of range (%d)", expert,
+                  m->cfg.experts_local);
+    MUMMU_REQUIRE(m->bank_set[which], "bank %d was never set", which);
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    const MummuMoeConfig& c = m->cfg;
+    size_t out_dim = which == MUMMU_BANK_DOWN ? c.hidden : c.inter;
+    size_t in_dim = which == MUMMU_BANK_DOWN ? c.inter : c.hidden;
+    size_t n = out_dim * in_dim;
+    size_t ebytes = bank_row_bytes(c, which) * out_dim;
+    const uint8_t* src = (const uint8_t*)m->bank[which] + ebytes * expert;
+    float* tmp = nullptr;
+    int rc;
+    if ((rc = dev_alloc(&tmp, n))) return rc;
+    if (c.weight_dtype == MUMMU_Q4_K) rc = launch_q4k_dequant(src, tmp, (int64_t)(n / Q4K_BLOCK_ELEMS), m->stream);
+    else rc = launch_widen(src, c.weight_dtype, tmp, (int64_t)n, m->stream);
+    cudaError_t err = cudaSuccess;
+    if (!rc) err = cudaMemcpyAsync(out, tmp, n * sizeof(float), cudaMemcpyDeviceToHost, m->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(m->stream);
+    cudaFree(tmp);
+    if (rc) return rc;
+    if (err != cudaSuccess) {
+        set_error("mummu_moe_dequant_bank: %s", cudaGetErrorString(err));
+        return MUMMU_ERR_DEVICE;
+    }
+    return MUMMU_OK;
+}
+
+int32_t mummu_moe_take_hits(MummuMoe* m, uint64_t* per_expert) {
+    MUMMU_REQUIRE(m && per_expert, "mummu_moe_take_hits: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    size_t bytes = sizeof(unsigned long long) * m->cfg.experts;
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(per_expert, m->hits, bytes, cudaMemcpyDeviceToHost, m->stream));
+    MUMMU_CUDA_TRY(cudaMemsetAsync(m->hits, 0, bytes, m->stream));
+    MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return MUMMU_OK;
+}
+
+int32_t mummu_moe_sync(MummuMoe* m, void* stream) {
+    MUMMU_REQUIRE(m, "mummu_moe_sync: null handle");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    return read_status(m, s);
+}
+
+int32_t mummu_moe_set_profiling(MummuMoe* m, int32_t enabled) {
+    MUMMU_REQUIRE(m, "mummu_moe_set_profiling: null handle");
+    std::lock_guard<std::mutex> lock(m->mu);
+    m->prof.enabled = enabled != 0;
+    return MUMMU_OK;
+}
+
+int32_t mummu_moe_take_profile(MummuMoe* m, char* names, size_t cap) {
+    MUMMU_REQUIRE(m && names && cap > 0, "mummu_moe_take_profile: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    MUMMU_CUDA_TRY(cudaDeviceSynchronize());
+    for (auto& p : m->prof.pending) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, p.a, p.b) == cudaSuccess) {
+            auto& st = m->prof.stats[p.name];
+            st.launches += 1;
+            st.ms += ms;
+        }
+        m->prof.pool.push_back(p.a);
+        m->prof.pool.push_back(p.b);
+    }
+    m->prof.pending.clear();
+    std::string out;
+    for (auto& kv : m->prof.stats) {
+        char buf[160];
+        snprintf(buf, sizeof(buf), "%s=%lld:%.6f;", kv.first.c_str(), (long long)kv.second.launches,
+                 kv.second.launches ? kv.second.ms / (double)kv.second.launches : 0.0);
+        out += buf;
+    }
+    m->prof.stats.clear();
+    strncpy(names, out.c_str(), cap - 1);
+    names[cap - 1] = 0;
+    return MUMMU_OK;
+}
+
+int64_t mummu_moe_launch_count(const MummuMoe* m) { return m ? m->launches : 0; }
+
+int32_t mummu_q4k_quantize(const float* src, void* dst, int64_t n_superblocks, int32_t device, void* stream) {
+    MUMMU_REQUIRE(src && dst && n_superblocks >= 0, "mummu_q4k_quantize: bad argument");
+    DeviceGuard guard(device);
+    return launch_q4k_quantize(src, dst, n_superblocks, (cudaStream_t)stream);
+}
+
+int32_t mummu_q4k_dequantize(const void* src, float* dst, int64_t n_superblocks, int32_t device, void* stream) {
+    MUMMU_REQUIRE(src && dst && n_superblocks >= 0, "mummu_q4k_dequantize: bad argument");
+    DeviceGuard guard(device);
+    return launch_q4k_dequant(src, dst, n_superblocks, (cudaStream_t)stream);
+}
+
+}  // extern "C"

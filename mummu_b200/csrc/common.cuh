@@ -1,0 +1,200 @@
+// Shared declarations of the mummu-cuda library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/mummu_cuda.h"
+
+namespace mummu {
+
+// ---------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+
+#define MUMMU_CUDA_TRY(expr)                                                              \
+    do {                                                                                  \
+        cudaError_t err__ = (expr);                                                       \
+        if (err__ != cudaSuccess) {                                                       \
+            ::mummu::set_error("CUDA error %s at %s:%d: %s", cudaGetErrorName(err__),     \
+                               __FILE__, __LINE__, cudaGetErrorString(err__));            \
+            return MUMMU_ERR_DEVICE;                                                      \
+        }                                                                                 \
+    } while (0)
+
+#define MUMMU_REQUIRE(cond, ...)              \
+    do {                                      \
+        if (!(cond)) {                        \
+            ::mummu::set_error(__VA_ARGS__);  \
+            return MUMMU_ERR_CONTRACT;        \
+        }                                     \
+    } while (0)
+
+// device status word bits (sticky until mummu_moe_sync reads them)
+constexpr int STATUS_NONFINITE = 1;
+constexpr int STATUS_TIMEOUT = 2;
+
+// ---------------------------------------------------------------------------------------------
+// dtype helpers
+// ---------------------------------------------------------------------------------------------
+inline size_t dtype_size(int dt) {
+    switch (dt) {
+        case MUMMU_F32: return 4;
+        case MUMMU_F16: return 2;
+        case MUMMU_BF16: return 2;
+        default: return 0;
+    }
+}
+
+constexpr int Q4K_BLOCK_ELEMS = 256;
+constexpr int Q4K_BLOCK_BYTES = 144;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// Tag type for Q4_K packed weights (rows of 144-byte super-blocks).
+struct q4k_t { uint8_t b; };
+
+// One Q4_K element, decoded exactly as the reference does (crates/mummu/src/gguf.rs:1685-1726):
+// d*sc first, then *q, the min product on its own, one subtraction; every step rounded to f32.
+__device__ __forceinline__ void q4k_scale_min(const uint8_t* scales, int j, float& sc, float& m) {
+    uint32_t s, mn;
+    if (j < 4) {
+        s = scales[j] & 63u;
+        mn = scales[j + 4] & 63u;
+    } else {
+        s = (scales[j + 4] & 0x0Fu) | ((uint32_t)(scales[j - 4] >> 6) << 4);
+        mn = (uint32_t)(scales[j + 4] >> 4) | ((uint32_t)(scales[j] >> 6) << 4);
+    }
+    sc = (float)s;
+    m = (float)mn;
+}
+
+__device__ __forceinline__ float q4k_decode_elem(const uint8_t* row, int k) {
+    const uint8_t* blk = row + (size_t)(k >> 8) * Q4K_BLOCK_BYTES;
+    int within = k & 255;
+    int j = within >> 5;          // sub-block 0..7
+    int chunk = j >> 1;
+    int b = within & 31;
+    float d = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
+    float dmin = __half2float(__ushort_as_half((unsigned short)(blk[2] | (blk[3] << 8))));
+    float sc, m;
+    q4k_scale_min(blk + 4, j, sc, m);
+    uint8_t byte = blk[16 + chunk * 32 + b];
+    float q = (float)((j & 1) ? (byte >> 4) : (byte & 0x0F));
+    float product = __fmul_rn(__fmul_rn(d, sc), q);
+    return __fsub_rn(product, __fmul_rn(dmin, m));
+}
+
+// ---------------------------------------------------------------------------------------------
+// the handle
+// ---------------------------------------------------------------------------------------------
+struct KernelStat {
+    int64_t launches = 0;
+    double ms = 0.0;
+};
+
+struct Profiler {
+    bool enabled = false;
+    struct Pending { std::string name; cudaEvent_t a, b; };
+    std::vector<Pending> pending;
+    std::map<std::string, KernelStat> stats;
+    std::vector<cudaEvent_t> pool;
+};
+
+}  // namespace mummu
+
+struct MummuMoe {
+    MummuMoeConfig cfg{};
+    std::mutex mu;
+    cudaStream_t stream = nullptr;
+
+    float* router_w = nullptr;      // f32 [hidden, experts]
+    float* router_bias = nullptr;   // f32 [experts] or null
+    void* bank[3] = {nullptr, nullptr, nullptr};
+    size_t bank_bytes[3] = {0, 0, 0};
+    bool bank_set[3] = {false, false, false};
+    bool router_set = false;
+
+    // scratch, sized for cap_tokens tokens at cfg.top_k slots each
+    int64_t cap_tokens = 0;
+    float* logits = nullptr;        // [tokens, experts]
+    int32_t* tile_done = nullptr;   // router tile counters (self-resetting)
+    int32_t* ids = nullptr;         // [tokens, k]
+    float* wts = nullptr;           // [tokens, k]
+    int32_t* counts = nullptr;      // [experts]
+    int32_t* offsets = nullptr;     // [experts + 1]
+    int32_t* active = nullptr;      // [experts] ids of experts with rows this call
+    int32_t* n_active = nullptr;    // [1]
+    int32_t* row_token = nullptr;   // [tokens * k]
+    int32_t* pos = nullptr;         // [tokens * k]
+    void* xs = nullptr;             // gathered rows [tokens * k, hidden] act dtype (tensor path)
+    void* hact = nullptr;           // [tokens * k, inter] f32 (or 16-bit, path dependent)
+    void* ys = nullptr;             // [tokens * k, hidden] f32
+    void* io_x = nullptr;           // device staging for host-pointer calls
+    void* io_y = nullptr;
+    unsigned long long* hits = nullptr;  // [experts]
+    int32_t* status = nullptr;      // device status word
+    int64_t launches = 0;
+    mummu::Profiler prof;
+};
+
+namespace mummu {
+
+size_t bank_row_bytes(const MummuMoeConfig& c, int which);
+size_t bank_total_bytes(const MummuMoeConfig& c, int which);
+int ensure_scratch(MummuMoe* m, int64_t tokens);
+
+// profiling-aware launch bracket
+struct LaunchScope {
+    MummuMoe* m;
+    cudaStream_t s;
+    const char* name;
+    cudaEvent_t a = nullptr, b = nullptr;
+    LaunchScope(MummuMoe* m_, cudaStream_t s_, const char* name_);
+    ~LaunchScope();
+};
+
+// ---- kernels_basic.cu ----
+int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int norm, int32_t* ids,
+                  float* wts, int32_t* counts, cudaStream_t s);
+int launch_count(MummuMoe* m, const int32_t* ids, int64_t n, int32_t* counts, cudaStream_t s);
+int launch_permute(MummuMoe* m, const int32_t* ids, int64_t tokens, int top_k,
+                   const int32_t* counts, int32_t* offsets, int32_t* row_token, int32_t* pos,
+                   cudaStream_t s);
+int launch_combine(MummuMoe* m, const void* ys, int ys_dtype, const int32_t* ids, const float* w,
+                   const int32_t* pos, int64_t tokens, int top_k, void* out, cudaStream_t s);
+int launch_offsets_from_counts(MummuMoe* m, const int32_t* counts, int n, int32_t* offsets,
+                               cudaStream_t s);
+// generic SIMT grouped SwiGLU (all dtypes); x_dtype is the dtype of `x`, rows come through
+// row_index (may be null = identity); experts local ids 0..experts_local
+int launch_experts_simt(MummuMoe* m, const void* x, int x_dtype, const int32_t* row_index,
+                        const int32_t* counts, const int32_t* offsets, int64_t max_rows_per_expert,
+                        int64_t total_rows, void* ys, int ys_dtype, int expert_only,
+                        cudaStream_t s);
+int launch_q4k_dequant(const void* src, float* dst, int64_t n_blocks, cudaStream_t s);
+int launch_q4k_quantize(const float* src, void* dst, int64_t n_blocks, cudaStream_t s);
+int launch_widen(const void* src, int dtype, float* dst, int64_t n, cudaStream_t s);
+
+// ---- decode_q4k.cu ----
+bool decode_q4k_supported(const MummuMoeConfig& c, int64_t tokens);
+int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cudaStream_t s);
+
+}  // namespace mummu

@@ -1,0 +1,808 @@
+// Router, permute, combine, the all-format SIMT expert bank and the Q4_K encode/decode kernels.
+//
+// The router reproduces, operation for operation, the CPU oracle's arithmetic so that routing ids
+// and weights can be compared bit for bit:
+//   logit  = 8-lane dot product: lane l sums elements l, l+8, ... with the product and the sum
+//            rounded separately; lanes fold as ((a0+a4)+(a1+a5))+((a2+a6)+(a3+a7)); leftover
+//            elements are added one by one (reference: models/qwen4exp/experts.rs:463-478)
+//   p      = exp_det(logit - max) / (left-to-right sum)           (nn/moe.rs:2138-2141)
+//   top-k  = descending p, equal p in ascending expert id         (experts.rs:532-535, 562-574)
+//   weight = p, or p / (sum of the picked p in slot order)        (nn/moe.rs:146-150, 2146-2152)
+#include <cfloat>
+#include <climits>
+
+#include "common.cuh"
+
+namespace mummu {
+
+// ---------------------------------------------------------------------------------------------
+// deterministic e^x: the same IEEE operation sequence as the oracle's orc_exp
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float exp_det(float x) {
+    if (x != x) return x;
+    if (x > 88.7f) return __int_as_float(0x7F800000);
+    if (x < -104.0f) return 0.0f;
+    const float LOG2E = 1.4426950216293335f;
+    const float LN2_HI = 0.693145751953125f;
+    const float LN2_LO = 1.4286068203094172e-06f;
+    const float MAGIC = 12582912.0f;
+    float t = __fmaf_rn(x, LOG2E, MAGIC);
+    float n = __fsub_rn(t, MAGIC);
+    float r = __fmaf_rn(-n, LN2_HI, x);
+    r = __fmaf_rn(-n, LN2_LO, r);
+    float p = 1.0f / 5040.0f;
+    p = __fmaf_rn(p, r, 1.0f / 720.0f);
+    p = __fmaf_rn(p, r, 1.0f / 120.0f);
+    p = __fmaf_rn(p, r, 1.0f / 24.0f);
+    p = __fmaf_rn(p, r, 1.0f / 6.0f);
+    p = __fmaf_rn(p, r, 0.5f);
+    p = __fmaf_rn(p, r, 1.0f);
+    p = __fmaf_rn(p, r, 1.0f);
+    int ni = (int)n;
+    int a = ni / 2;
+    int b = ni - a;
+    float fa = __int_as_float((a + 127) << 23);
+    float fb = __int_as_float((b + 127) << 23);
+    return __fmul_rn(__fmul_rn(p, fa), fb);
+}
+
+// ---------------------------------------------------------------------------------------------
+// router
+// ---------------------------------------------------------------------------------------------
+constexpr int R_ES = 8;          // experts per block
+constexpr int R_THREADS = 256;   // 8 experts x 8 lanes x 4 token groups
+constexpr int R_MAXV = 8;        // probabilities per lane in the top-k stage: experts <= 256
+
+struct RouterArgs {
+    const void* x;
+    const float* w;      // [H, E]
+    const float* bias;   // [E] or null
+    float* logits;       // [T, E] scratch
+    int32_t* tile_done;  // [tiles] zero on entry, zero on exit
+    int32_t* ids;        // [T, k]
+    float* wts;          // [T, k]
+    int32_t* counts;     // [E] or null
+    unsigned long long* hits;  // [E] or null
+    int32_t* status;
+    int T, H, E, k, norm;
+};
+
+// One warp: softmax over one token's logits, then top-k.  sm_v: E floats, sm_vals: k floats,
+// sm_ids: k ints (all private to the warp).
+__device__ void warp_softmax_topk(const RouterArgs& a, int t, float* sm_v, float* sm_vals,
+                                  int32_t* sm_ids) {
+    const int lane = threadIdx.x & 31;
+    const unsigned full = 0xFFFFFFFFu;
+    const float* lrow = a.logits + (size_t)t * a.E;
+    float l[R_MAXV], p[R_MAXV];
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < R_MAXV; ++i) {
+        int e = lane + 32 * i;
+        l[i] = e < a.E ? __ldcg(lrow + e) : -FLT_MAX;
+        if (e < a.E && !isfinite(l[i])) bad = true;
+    }
+    bad = __any_sync(full, bad);
+    if (bad) {
+        // the reference's host router refuses non-finite logits (experts.rs:553-560); here the
+        // token gets experts 0..k-1 with zero weight and the sticky status word records it
+        if (lane == 0) atomicOr(a.status, STATUS_NONFINITE);
+        for (int r = lane; r < a.k; r += 32) {
+            a.ids[(size_t)t * a.k + r] = r;
+            a.wts[(size_t)t * a.k + r] = 0.0f;
+            if (a.counts) atomicAdd(a.counts + r, 1);
+            if (a.hits) atomicAdd(a.hits + r, 1ull);
+        }
+        return;
+    }
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int i = 0; i < R_MAXV; ++i) mx = fmaxf(mx, l[i]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, off));
+#pragma unroll
+    for (int i = 0; i < R_MAXV; ++i) {
+        int e = lane + 32 * i;
+        if (e < a.E) {
+            p[i] = exp_det(__fsub_rn(l[i], mx));
+            sm_v[e] = p[i];
+        }
+    }
+    __syncwarp();
+    float total = 0.0f;
+    for (int e = 0; e < a.E; ++e) total = __fadd_rn(total, sm_v[e]);
+#pragma unroll
+    for (int i = 0; i < R_MAXV; ++i) {
+        int e = lane + 32 * i;
+        p[i] = e < a.E ? __fdiv_rn(p[i], total) : -1.0f;
+    }
+    float denom = 0.0f;
+    for (int r = 0; r < a.k; ++r) {
+        float bp = -2.0f;
+        int be = INT_MAX;
+#pragma unroll
+        for (int i = 0; i < R_MAXV; ++i) {
+            if (p[i] > bp) {
+                bp = p[i];
+                be = lane + 32 * i;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            float op = __shfl_xor_sync(full, bp, off);
+            int oe = __shfl_xor_sync(full, be, off);
+            if (op > bp || (op == bp && oe < be)) {
+                bp = op;
+                be = oe;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < R_MAXV; ++i)
+            if (be == lane + 32 * i) p[i] = -1.0f;
+        denom = __fadd_rn(denom, bp);
+        if (lane == 0) {
+            sm_vals[r] = bp;
+            sm_ids[r] = be;
+        }
+    }
+    __syncwarp();
+    for (int r = lane; r < a.k; r += 32) {
+        float wv = sm_vals[r];
+        if (a.norm) wv = __fdiv_rn(wv, denom);
+        int e = sm_ids[r];
+        a.ids[(size_t)t * a.k + r] = e;
+        a.wts[(size_t)t * a.k + r] = wv;
+        if (a.counts) atomicAdd(a.counts + e, 1);
+        if (a.hits) atomicAdd(a.hits + e, 1ull);
+    }
+    __syncwarp();
+}
+
+// grid (expert slices, token tiles).  Each block stages its 8-expert slice of W and its token
+// tile of x in shared memory, computes the logits in the fixed lane order, and the block that
+// finishes a token tile last runs softmax + top-k for that tile.
+template <typename TX, int TPT>
+__global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int TT = 4 * TPT;
+    const int H = a.H, E = a.E;
+    const int H8 = H & ~7;
+    float* Ws = reinterpret_cast<float*>(smem_raw);           // [H8][8]
+    float* xs = Ws + (size_t)H8 * R_ES;                        // [TT][H]
+    float* parts = xs + (size_t)TT * H;                        // [TT][8][8]
+    float* tk = parts + TT * 64;                               // top-k scratch, 8 warps
+    const int tid = threadIdx.x;
+    const int e0 = blockIdx.x * R_ES;
+    const int t0 = blockIdx.y * TT;
+    const TX* x = reinterpret_cast<const TX*>(a.x);
+
+    for (int idx = tid; idx < H8 * R_ES; idx += R_THREADS) {
+        int i = idx >> 3, el = idx & 7;
+        int e = e0 + el;
+        Ws[idx] = e < E ? a.w[(size_t)i * E + e] : 0.0f;
+    }
+    for (int idx = tid; idx < TT * H; idx += R_THREADS) {
+        int tt = idx / H, h = idx - tt * H;
+        int t = t0 + tt;
+        xs[idx] = t < a.T ? to_f32(x[(size_t)t * H + h]) : 0.0f;
+    }
+    __syncthreads();
+
+    const int el = tid & 7, j = (tid >> 3) & 7, tg = tid >> 6;
+    float acc[TPT];
+#pragma unroll
+    for (int u = 0; u < TPT; ++u) acc[u] = 0.0f;
+    const int iters = H8 >> 3;
+#pragma unroll 4
+    for (int i = 0; i < iters; ++i) {
+        float wv = Ws[(i * 8 + j) * R_ES + el];
+#pragma unroll
+        for (int u = 0; u < TPT; ++u) {
+            float xv = xs[(size_t)(tg + 4 * u) * H + i * 8 + j];
+            acc[u] = __fadd_rn(acc[u], __fmul_rn(xv, wv));
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < TPT; ++u) parts[((tg + 4 * u) * 8 + el) * 8 + j] = acc[u];
+    __syncthreads();
+    if (tid < TT * 8) {
+        int tt = tid >> 3, el2 = tid & 7;
+        int t = t0 + tt, e = e0 + el2;
+        if (t < a.T && e < E) {
+            const float* q = parts + (tt * 8 + el2) * 8;
+            float s = __fadd_rn(__fadd_rn(__fadd_rn(q[0], q[4]), __fadd_rn(q[1], q[5])),
+                                __fadd_rn(__fadd_rn(q[2], q[6]), __fadd_rn(q[3], q[7])));
+            for (int i = H8; i < H; ++i)
+                s = __fadd_rn(s, __fmul_rn(xs[(size_t)tt * H + i], a.w[(size_t)i * E + e]));
+            if (a.bias) s = __fadd_rn(s, a.bias[e]);
+            a.logits[(size_t)t * E + e] = s;
+        }
+    }
+    // last block of this token tile does the selection
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int done = atomicAdd(a.tile_done + blockIdx.y, 1);
+        is_last = (done == (int)gridDim.x - 1);
+        if (is_last) a.tile_done[blockIdx.y] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const int warp = tid >> 5;
+    const int per_warp = E + 2 * a.k;
+    float* sm_v = tk + (size_t)warp * per_warp;
+    float* sm_vals = sm_v + E;
+    int32_t* sm_ids = reinterpret_cast<int32_t*>(sm_vals + a.k);
+    for (int tt = warp; tt < TT; tt += R_THREADS / 32) {
+        int t = t0 + tt;
+        if (t < a.T) warp_softmax_topk(a, t, sm_v, sm_vals, sm_ids);
+    }
+}
+
+static size_t router_smem(int H, int E, int k, int TT) {
+    size_t H8 = (size_t)(H & ~7);
+    return (H8 * R_ES + (size_t)TT * H + (size_t)TT * 64 + (size_t)8 * (E + 2 * k)) * 4;
+}
+
+template <typename TX>
+static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
+    int tpt = a.T >= 2048 ? 4 : (a.T >= 256 ? 2 : 1);
+    while (tpt > 1 && router_smem(a.H, a.E, a.k, 4 * tpt) > 200 * 1024) tpt >>= 1;
+    size_t smem = router_smem(a.H, a.E, a.k, 4 * tpt);
+    if (smem > 220 * 1024) {
+        set_error("router: hidden %d too wide for the shared-memory staged router", a.H);
+        return MUMMU_ERR_UNSUPPORTED;
+    }
+    dim3 grid((a.E + R_ES - 1) / R_ES, (a.T + 4 * tpt - 1) / (4 * tpt));
+    LaunchScope scope(m, s, "router");
+    switch (tpt) {
+        case 4:
+            MUMMU_CUDA_TRY(cudaFuncSetAttribute(router_kernel<TX, 4>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            router_kernel<TX, 4><<<grid, R_THREADS, smem, s>>>(a);
+            break;
+        case 2:
+            MUMMU_CUDA_TRY(cudaFuncSetAttribute(router_kernel<TX, 2>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            router_kernel<TX, 2><<<grid, R_THREADS, smem, s>>>(a);
+            break;
+        default:
+            MUMMU_CUDA_TRY(cudaFuncSetAttribute(router_kernel<TX, 1>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            router_kernel<TX, 1><<<grid, R_THREADS, smem, s>>>(a);
+            break;
+    }
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int norm, int32_t* ids,
+                  float* wts, int32_t* counts, cudaStream_t s) {
+    const MummuMoeConfig& c = m->cfg;
+    if (c.experts > 32 * R_MAXV) {
+        set_error("router: %d experts exceed the %d this build selects over", c.experts, 32 * R_MAXV);
+        return MUMMU_ERR_UNSUPPORTED;
+    }
+    if (counts) MUMMU_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int32_t) * c.experts, s));
+    RouterArgs a;
+    a.x = x;
+    a.w = m->router_w;
+    a.bias = m->router_bias;
+    a.logits = m->logits;
+    a.tile_done = m->tile_done;
+    a.ids = ids;
+    a.wts = wts;
+    a.counts = counts;
+    a.hits = m->hits;
+    a.status = m->status;
+    a.T = (int)tokens;
+    a.H = c.hidden;
+    a.E = c.experts;
+    a.k = top_k;
+    a.norm = norm;
+    switch (c.act_dtype) {
+        case MUMMU_F32: return launch_router_t<float>(m, a, s);
+        case MUMMU_F16: return launch_router_t<__half>(m, a, s);
+        case MUMMU_BF16: return launch_router_t<__nv_bfloat16>(m, a, s);
+    }
+    set_error("router: bad activation dtype %d", c.act_dtype);
+    return MUMMU_ERR_CONTRACT;
+}
+
+// ---------------------------------------------------------------------------------------------
+// histogram / offsets / permute
+// ---------------------------------------------------------------------------------------------
+__global__ void count_kernel(const int32_t* ids, int64_t n, int E, int32_t* counts, int32_t* status) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int e = ids[i];
+        if (e >= 0 && e < E) atomicAdd(counts + e, 1);
+    }
+}
+
+int launch_count(MummuMoe* m, const int32_t* ids, int64_t n, int32_t* counts, cudaStream_t s) {
+    MUMMU_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int32_t) * m->cfg.experts, s));
+    if (n == 0) return MUMMU_OK;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 1184) blocks = 1184;
+    LaunchScope scope(m, s, "count");
+    count_kernel<<<blocks, 256, 0, s>>>(ids, n, m->cfg.experts, counts, m->status);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+__global__ void offsets_kernel(const int32_t* counts, int n, int32_t* offsets) {
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < n; ++e) {
+            offsets[e] = acc;
+            acc += counts[e];
+        }
+        offsets[n] = acc;
+    }
+}
+
+int launch_offsets_from_counts(MummuMoe* m, const int32_t* counts, int n, int32_t* offsets,
+                               cudaStream_t s) {
+    LaunchScope scope(m, s, "offsets");
+    offsets_kernel<<<1, 32, 0, s>>>(counts, n, offsets);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+// One block per expert: stable compaction of the (token, slot) pairs routed to it, so rows of one
+// expert come out in ascending token order (the order nn/moe.rs:276-285 builds its lists in).
+constexpr int P_THREADS = 1024;
+__global__ void __launch_bounds__(P_THREADS) permute_kernel(const int32_t* ids, int64_t n, int top_k,
+                                                            int E, const int32_t* counts,
+                                                            int32_t* offsets, int32_t* row_token,
+                                                            int32_t* pos) {
+    __shared__ int warp_sums[P_THREADS / 32];
+    __shared__ int base_s;
+    const int e = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // exclusive prefix of counts up to e
+    int part = 0;
+    for (int i = tid; i < e; i += P_THREADS) part += counts[i];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, off);
+    if (lane == 0) warp_sums[warp] = part;
+    __syncthreads();
+    if (tid == 0) {
+        int b = 0;
+        for (int w = 0; w < P_THREADS / 32; ++w) b += warp_sums[w];
+        base_s = b;
+        if (offsets) {
+            offsets[e] = b;
+            if (e == E - 1) offsets[E] = b + counts[e];
+        }
+    }
+    __syncthreads();
+    int running = base_s;
+    if (counts[e] == 0) return;
+    for (int64_t start = 0; start < n; start += P_THREADS) {
+        int64_t i = start + tid;
+        bool hit = i < n && ids[i] == e;
+        unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
+        int before = __popc(ballot & ((1u << lane) - 1u));
+        __syncthreads();  // warp_sums reuse
+        if (lane == 0) warp_sums[warp] = __popc(ballot);
+        __syncthreads();
+        int wbase = 0, total = 0;
+        for (int w = 0; w < P_THREADS / 32; ++w) {
+            int c = warp_sums[w];
+            if (w < warp) wbase += c;
+            total += c;
+        }
+        if (hit) {
+            int p = running + wbase + before;
+            if (row_token) row_token[p] = (int32_t)(i / top_k);
+            if (pos) pos[i] = p;
+        }
+        running += total;
+    }
+}
+
+int launch_permute(MummuMoe* m, const int32_t* ids, int64_t tokens, int top_k,
+                   const int32_t* counts, int32_t* offsets, int32_t* row_token, int32_t* pos,
+                   cudaStream_t s) {
+    LaunchScope scope(m, s, "permute");
+    permute_kernel<<<m->cfg.experts, P_THREADS, 0, s>>>(ids, tokens * top_k, top_k, m->cfg.experts,
+                                                        counts, offsets, row_token, pos);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// combine: per token, ascending expert id, scaled = w * y; out += scaled (two roundings)
+// ---------------------------------------------------------------------------------------------
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256) combine_kernel(const TY* ys, const int32_t* ids, const float* w,
+                                                      const int32_t* pos, int top_k, int H, TO* out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    int32_t* s_pos = reinterpret_cast<int32_t*>(smem_raw);
+    float* s_w = reinterpret_cast<float*>(s_pos + top_k);
+    const int64_t t = blockIdx.x;
+    for (int r = threadIdx.x; r < top_k; r += blockDim.x) {
+        int id = ids[t * top_k + r];
+        int rank = 0;
+        for (int q = 0; q < top_k; ++q) {
+            int other = ids[t * top_k + q];
+            rank += (other < id || (other == id && q < r)) ? 1 : 0;
+        }
+        s_pos[rank] = pos[t * top_k + r];
+        s_w[rank] = w[t * top_k + r];
+    }
+    __syncthreads();
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float acc = 0.0f;
+        for (int r = 0; r < top_k; ++r) {
+            float v = to_f32(ys[(size_t)s_pos[r] * H + h]);
+            acc = __fadd_rn(acc, __fmul_rn(s_w[r], v));
+        }
+        out[t * H + h] = from_f32<TO>(acc);
+    }
+}
+
+template <typename TY>
+static int launch_combine_y(MummuMoe* m, const void* ys, const int32_t* ids, const float* w,
+                            const int32_t* pos, int64_t tokens, int top_k, void* out,
+                            cudaStream_t s) {
+    size_t smem = (size_t)top_k * 8;
+    const int H = m->cfg.hidden;
+    LaunchScope scope(m, s, "combine");
+    switch (m->cfg.act_dtype) {
+        case MUMMU_F32:
+            combine_kernel<TY, float><<<(unsigned)tokens, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
+            break;
+        case MUMMU_F16:
+            combine_kernel<TY, __half><<<(unsigned)tokens, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__half*)out);
+            break;
+        case MUMMU_BF16:
+            combine_kernel<TY, __nv_bfloat16><<<(unsigned)tokens, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__nv_bfloat16*)out);
+            break;
+    }
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+int launch_combine(MummuMoe* m, const void* ys, int ys_dtype, const int32_t* ids, const float* w,
+                   const int32_t* pos, int64_t tokens, int top_k, void* out, cudaStream_t s) {
+    if (tokens == 0) return MUMMU_OK;
+    switch (ys_dtype) {
+        case MUMMU_F32: return launch_combine_y<float>(m, ys, ids, w, pos, tokens, top_k, out, s);
+        case MUMMU_F16: return launch_combine_y<__half>(m, ys, ids, w, pos, tokens, top_k, out, s);
+        case MUMMU_BF16: return launch_combine_y<__nv_bfloat16>(m, ys, ids, w, pos, tokens, top_k, out, s);
+    }
+    set_error("combine: bad dtype %d", ys_dtype);
+    return MUMMU_ERR_CONTRACT;
+}
+
+// ---------------------------------------------------------------------------------------------
+// SIMT grouped SwiGLU: every weight format, f32 accumulation.  The correctness path and the
+// fallback for shapes the tensor-core kernels do not take.
+// ---------------------------------------------------------------------------------------------
+template <typename TW> __device__ __forceinline__ float load_w(const uint8_t* row, int k) {
+    return to_f32(reinterpret_cast<const TW*>(row)[k]);
+}
+template <> __device__ __forceinline__ float load_w<q4k_t>(const uint8_t* row, int k) {
+    return q4k_decode_elem(row, k);
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+struct SimtArgs {
+    const void* A;          // activations
+    int64_t lda;
+    const int32_t* row_index;   // sorted row -> source row, or null (identity)
+    const int32_t* counts;      // per local expert, or null (single expert, rows_single rows)
+    const int32_t* offsets;     // per local expert exclusive prefix, or null
+    int rows_single;
+    int expert_single;          // >= 0: only this expert
+    const uint8_t* W0;          // gate (or down)
+    const uint8_t* W1;          // up (GATEUP only)
+    size_t expert_stride;       // bytes between experts
+    size_t row_bytes;           // bytes per weight row
+    void* out;
+    int64_t ldo;
+    int N, K;
+};
+
+constexpr int S_BM = 64, S_BN = 64, S_BK = 16;
+
+template <typename TA, typename TW, bool GATEUP, typename TO>
+__global__ void __launch_bounds__(256) simt_grouped_kernel(SimtArgs a) {
+    __shared__ float As[S_BK][S_BM + 4];
+    __shared__ float B0[S_BK][S_BN + 4];
+    __shared__ float B1[GATEUP ? S_BK : 1][S_BN + 4];
+    const int e = a.expert_single >= 0 ? a.expert_single : (int)blockIdx.z;
+    const int cnt = a.counts ? a.counts[e] : a.rows_single;
+    const int m0 = blockIdx.y * S_BM;
+    if (m0 >= cnt) return;
+    const int base = a.offsets ? a.offsets[e] : 0;
+    const int n0 = blockIdx.x * S_BN;
+    const int tid = threadIdx.x;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;   // loader: row, first k
+    const int ty = tid >> 4, tx = tid & 15;
+    const TA* A = reinterpret_cast<const TA*>(a.A);
+
+    int64_t src_row = -1;
+    if (m0 + lr < cnt) {
+        int p = base + m0 + lr;
+        src_row = a.row_index ? a.row_index[p] : p;
+    }
+    const uint8_t* w0row = nullptr;
+    const uint8_t* w1row = nullptr;
+    if (n0 + lr < a.N) {
+        w0row = a.W0 + (size_t)e * a.expert_stride + (size_t)(n0 + lr) * a.row_bytes;
+        if (GATEUP) w1row = a.W1 + (size_t)e * a.expert_stride + (size_t)(n0 + lr) * a.row_bytes;
+    }
+    float acc0[4][4], acc1[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc0[i][j] = acc1[i][j] = 0.0f;
+
+    for (int k0 = 0; k0 < a.K; k0 += S_BK) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            int k = k0 + lk + u;
+            As[lk + u][lr] = (src_row >= 0 && k < a.K) ? to_f32(A[src_row * a.lda + k]) : 0.0f;
+            B0[lk + u][lr] = (w0row && k < a.K) ? load_w<TW>(w0row, k) : 0.0f;
+            if (GATEUP) B1[lk + u][lr] = (w1row && k < a.K) ? load_w<TW>(w1row, k) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < S_BK; ++kk) {
+            float av[4], b0[4], b1[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                b0[j] = B0[kk][tx * 4 + j];
+                if (GATEUP) b1[j] = B1[kk][tx * 4 + j];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc0[i][j] = fmaf(av[i], b0[j], acc0[i][j]);
+                    if (GATEUP) acc1[i][j] = fmaf(av[i], b1[j], acc1[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+    TO* out = reinterpret_cast<TO*>(a.out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int r = m0 + ty * 4 + i;
+        if (r >= cnt) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int n = n0 + tx * 4 + j;
+            if (n >= a.N) continue;
+            float v = GATEUP ? silu_f(acc0[i][j]) * acc1[i][j] : acc0[i][j];
+            out[(size_t)(base + r) * a.ldo + n] = from_f32<TO>(v);
+        }
+    }
+}
+
+template <typename TA, typename TW, bool GATEUP, typename TO>
+static int simt_launch(MummuMoe* m, SimtArgs& a, int experts, int64_t max_rows, cudaStream_t s,
+                       const char* name) {
+    if (max_rows <= 0) return MUMMU_OK;
+    dim3 grid((a.N + S_BN - 1) / S_BN, (unsigned)((max_rows + S_BM - 1) / S_BM), experts);
+    LaunchScope scope(m, s, name);
+    simt_grouped_kernel<TA, TW, GATEUP, TO><<<grid, 256, 0, s>>>(a);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+template <typename TA, typename TW>
+static int simt_two_stage(MummuMoe* m, const void* x, const int32_t* row_index,
+                          const int32_t* counts, const int32_t* offsets, int64_t max_rows,
+                          void* ys, int ys_dtype, int expert_only, int rows_single, cudaStream_t s) {
+    const MummuMoeConfig& c = m->cfg;
+    SimtArgs a{};
+    a.A = x;
+    a.lda = c.hidden;
+    a.row_index = row_index;
+    a.counts = counts;
+    a.offsets = offsets;
+    a.rows_single = rows_single;
+    a.expert_single = expert_only;
+    a.W0 = (const uint8_t*)m->bank[MUMMU_BANK_GATE];
+    a.W1 = (const uint8_t*)m->bank[MUMMU_BANK_UP];
+    a.row_bytes = bank_row_bytes(c, MUMMU_BANK_GATE);
+    a.expert_stride = a.row_bytes * c.inter;
+    a.out = m->hact;
+    a.ldo = c.inter;
+    a.N = c.inter;
+    a.K = c.hidden;
+    int experts = expert_only >= 0 ? 1 : c.experts_local;
+    int rc = simt_launch<TA, TW, true, float>(m, a, experts, max_rows, s, "simt_gate_up");
+    if (rc) return rc;
+    SimtArgs d{};
+    d.A = m->hact;
+    d.lda = c.inter;
+    d.row_index = nullptr;
+    d.counts = counts;
+    d.offsets = offsets;
+    d.rows_single = rows_single;
+    d.expert_single = expert_only;
+    d.W0 = (const uint8_t*)m->bank[MUMMU_BANK_DOWN];
+    d.W1 = nullptr;
+    d.row_bytes = bank_row_bytes(c, MUMMU_BANK_DOWN);
+    d.expert_stride = d.row_bytes * c.hidden;
+    d.out = ys;
+    d.ldo = c.hidden;
+    d.N = c.hidden;
+    d.K = c.inter;
+    switch (ys_dtype) {
+        case MUMMU_F32: return simt_launch<float, TW, false, float>(m, d, experts, max_rows, s, "simt_down");
+        case MUMMU_F16: return simt_launch<float, TW, false, __half>(m, d, experts, max_rows, s, "simt_down");
+        case MUMMU_BF16: return simt_launch<float, TW, false, __nv_bfloat16>(m, d, experts, max_rows, s, "simt_down");
+    }
+    set_error("experts: bad output dtype %d", ys_dtype);
+    return MUMMU_ERR_CONTRACT;
+}
+
+template <typename TA>
+static int simt_by_weight(MummuMoe* m, const void* x, const int32_t* row_index,
+                          const int32_t* counts, const int32_t* offsets, int64_t max_rows, void* ys,
+                          int ys_dtype, int expert_only, int rows_single, cudaStream_t s) {
+    switch (m->cfg.weight_dtype) {
+        case MUMMU_F32: return simt_two_stage<TA, float>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
+        case MUMMU_F16: return simt_two_stage<TA, __half>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
+        case MUMMU_BF16: return simt_two_stage<TA, __nv_bfloat16>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
+        case MUMMU_Q4_K: return simt_two_stage<TA, q4k_t>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
+    }
+    set_error("experts: bad weight dtype %d", m->cfg.weight_dtype);
+    return MUMMU_ERR_CONTRACT;
+}
+
+int launch_experts_simt(MummuMoe* m, const void* x, int x_dtype, const int32_t* row_index,
+                        const int32_t* counts, const int32_t* offsets, int64_t max_rows_per_expert,
+                        int64_t total_rows, void* ys, int ys_dtype, int expert_only,
+                        cudaStream_t s) {
+    int rows_single = expert_only >= 0 ? (int)total_rows : 0;
+    switch (x_dtype) {
+        case MUMMU_F32: return simt_by_weight<float>(m, x, row_index, counts, offsets, max_rows_per_expert, ys, ys_dtype, expert_only, rows_single, s);
+        case MUMMU_F16: return simt_by_weight<__half>(m, x, row_index, counts, offsets, max_rows_per_expert, ys, ys_dtype, expert_only, rows_single, s);
+        case MUMMU_BF16: return simt_by_weight<__nv_bfloat16>(m, x, row_index, counts, offsets, max_rows_per_expert, ys, ys_dtype, expert_only, rows_single, s);
+    }
+    set_error("experts: bad activation dtype %d", x_dtype);
+    return MUMMU_ERR_CONTRACT;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Q4_K decode / encode, widening
+// ---------------------------------------------------------------------------------------------
+__global__ void q4k_dequant_kernel(const uint8_t* src, float* dst, int64_t n_elems) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_elems;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const uint8_t* blk = src + (i >> 8) * Q4K_BLOCK_BYTES;
+        dst[i] = q4k_decode_elem(blk, (int)(i & 255));
+    }
+}
+
+int launch_q4k_dequant(const void* src, float* dst, int64_t n_blocks, cudaStream_t s) {
+    int64_t n = n_blocks * Q4K_BLOCK_ELEMS;
+    if (n == 0) return MUMMU_OK;
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    q4k_dequant_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint8_t*)src, dst, n);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+// One warp per super-block; lane l owns values 8l..8l+7 (sub-block l/4).  The arithmetic is the
+// host encoder's (mummu_b200/q4k.py), operation for operation, so both produce the same bytes.
+__global__ void __launch_bounds__(256) q4k_quantize_kernel(const float* src, uint8_t* dst, int64_t n_blocks) {
+    const unsigned full = 0xFFFFFFFFu;
+    const int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t blk = warp; blk < n_blocks; blk += nwarps) {
+        const float* x = src + blk * 256 + lane * 8;
+        float v[8];
+        float4 lo4 = *reinterpret_cast<const float4*>(x);
+        float4 hi4 = *reinterpret_cast<const float4*>(x + 4);
+        v[0] = lo4.x; v[1] = lo4.y; v[2] = lo4.z; v[3] = lo4.w;
+        v[4] = hi4.x; v[5] = hi4.y; v[6] = hi4.z; v[7] = hi4.w;
+        float mn = v[0], mx = v[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) { mn = fminf(mn, v[i]); mx = fmaxf(mx, v[i]); }
+        mn = fminf(mn, __shfl_xor_sync(full, mn, 1)); mx = fmaxf(mx, __shfl_xor_sync(full, mx, 1));
+        mn = fminf(mn, __shfl_xor_sync(full, mn, 2)); mx = fmaxf(mx, __shfl_xor_sync(full, mx, 2));
+        float lo = fminf(mn, 0.0f);
+        float hi = fmaxf(mx, lo);
+        float scale = __fdiv_rn(__fsub_rn(hi, lo), 15.0f);
+        float mnv = -lo;
+        float ms = scale, mm = mnv;
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            ms = fmaxf(ms, __shfl_xor_sync(full, ms, off));
+            mm = fmaxf(mm, __shfl_xor_sync(full, mm, off));
+        }
+        __half dh = __float2half_rn(__fdiv_rn(ms, 63.0f));
+        __half dminh = __float2half_rn(__fdiv_rn(mm, 63.0f));
+        float df = __half2float(dh), dminf = __half2float(dminh);
+        float sc = df > 0.0f ? fminf(fmaxf(rintf(__fdiv_rn(scale, df)), 0.0f), 63.0f) : 0.0f;
+        float mq = dminf > 0.0f ? fminf(fmaxf(rintf(__fdiv_rn(mnv, dminf)), 0.0f), 63.0f) : 0.0f;
+        float dsc = __fmul_rn(df, sc);
+        float dm = __fmul_rn(dminf, mq);
+        uint32_t packed = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float q = dsc > 0.0f ? fminf(fmaxf(rintf(__fdiv_rn(__fadd_rn(v[i], dm), dsc)), 0.0f), 15.0f) : 0.0f;
+            packed |= ((uint32_t)q) << (4 * i);
+        }
+        uint8_t* out = dst + blk * Q4K_BLOCK_BYTES;
+        uint32_t sci = (uint32_t)sc, mi = (uint32_t)mq;
+        // scale bytes: lane b < 12 builds byte b from sub-block values held by lanes 4*j
+        int b = lane < 12 ? lane : 0;
+        int j_lo = b < 4 ? b : (b < 8 ? b - 4 : b - 4);      // first source sub-block
+        int j_hi = b < 4 ? b + 4 : (b < 8 ? b : b - 4);      // second source sub-block
+        uint32_t sc_a = __shfl_sync(full, sci, 4 * j_lo), m_a = __shfl_sync(full, mi, 4 * j_lo);
+        uint32_t sc_b = __shfl_sync(full, sci, 4 * j_hi), m_b = __shfl_sync(full, mi, 4 * j_hi);
+        uint32_t byte;
+        if (b < 4) byte = sc_a | ((sc_b >> 4) << 6);
+        else if (b < 8) byte = m_a | ((m_b >> 4) << 6);
+        else byte = (sc_b & 0x0Fu) | ((m_b & 0x0Fu) << 4);
+        if (lane < 12) out[4 + lane] = (uint8_t)byte;
+        if (lane == 0) {
+            *reinterpret_cast<unsigned short*>(out) = __half_as_ushort(dh);
+            *reinterpret_cast<unsigned short*>(out + 2) = __half_as_ushort(dminh);
+        }
+        // quants: lane L with L%8 < 4 holds low nibbles of chunk L/8, lane L+4 the high nibbles
+        uint32_t partner = __shfl_down_sync(full, packed, 4);
+        if ((lane & 7) < 4) {
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t by = ((packed >> (4 * i)) & 0xFu) | (((partner >> (4 * i)) & 0xFu) << 4);
+                w0 |= by << (8 * i);
+                uint32_t by2 = ((packed >> (4 * (i + 4))) & 0xFu) | (((partner >> (4 * (i + 4))) & 0xFu) << 4);
+                w1 |= by2 << (8 * i);
+            }
+            uint32_t* q = reinterpret_cast<uint32_t*>(out + 16 + 32 * (lane >> 3) + 8 * (lane & 7));
+            q[0] = w0;
+            q[1] = w1;
+        }
+    }
+}
+
+int launch_q4k_quantize(const float* src, void* dst, int64_t n_blocks, cudaStream_t s) {
+    if (n_blocks == 0) return MUMMU_OK;
+    int64_t blocks = (n_blocks + 7) / 8;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    q4k_quantize_kernel<<<(unsigned)blocks, 256, 0, s>>>(src, (uint8_t*)dst, n_blocks);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+template <typename T>
+__global__ void widen_kernel(const T* src, float* dst, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = to_f32(src[i]);
+}
+
+int launch_widen(const void* src, int dtype, float* dst, int64_t n, cudaStream_t s) {
+    if (n == 0) return MUMMU_OK;
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    switch (dtype) {
+        case MUMMU_F32: widen_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)src, dst, n); break;
+        case MUMMU_F16: widen_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>((const __half*)src, dst, n); break;
+        case MUMMU_BF16: widen_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)src, dst, n); break;
+        default: set_error("widen: bad dtype %d", dtype); return MUMMU_ERR_CONTRACT;
+    }
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+}  // namespace mummu

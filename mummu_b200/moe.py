@@ -1,0 +1,333 @@
+"""Host-side mirror of the reference's expert-bank interface (crates/mummu/src/nn/moe.rs), over
+the C ABI of libmummu_cuda.so.
+
+Names, argument meaning and error behaviour follow the reference: `SparseMoeConfig.init`,
+`SparseMoe.forward(x, top_k, norm_topk_prob)`, `SparseMoePerExpert.{forward, route, run_local}`,
+`Routing`, `ExpertExec.run` (as `CudaExpert.run`), `ExpertPool.take_hits`.  Where the reference
+panics on a contract violation this raises `MoeContractError` with the reference's message.
+Inputs are numpy arrays (host path: copied in and out inside the call) or torch CUDA tensors
+(device path: queued on the current torch stream, nothing is copied).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional, Tuple
+
+import numpy as np
+
+from . import _lib as L
+
+_NP_DTYPES = {np.dtype(np.float32): L.F32, np.dtype(np.float16): L.F16}
+
+
+class MoeContractError(AssertionError):
+    """The reference panics here (assert!/expect); message kept."""
+
+
+class MoeDeviceError(RuntimeError):
+    pass
+
+
+class MoeNumericError(ValueError):
+    """Non-finite router logit (the reference's host router returns Err, experts.rs:553-560)."""
+
+
+def _check(rc: int) -> None:
+    if rc == L.OK:
+        return
+    msg = L.last_error()
+    if rc == L.ERR_CONTRACT:
+        raise MoeContractError(msg)
+    if rc == L.ERR_NUMERIC:
+        raise MoeNumericError(msg)
+    if rc == L.ERR_UNSUPPORTED:
+        raise NotImplementedError(msg)
+    if rc == L.ERR_TIMEOUT:
+        raise TimeoutError(msg)
+    raise MoeDeviceError(msg)
+
+
+def _is_torch(x) -> bool:
+    return type(x).__module__.startswith("torch")
+
+
+def _torch_dtype_code(t) -> int:
+    import torch
+    return {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}[t.dtype]
+
+
+def _torch_stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+@dataclass
+class Routing:
+    """`Routing` of nn/moe.rs:333-337: per expert, the token rows it serves and their weights."""
+    tokens: int
+    per_expert: List[Tuple[List[int], List[float]]] = field(default_factory=list)
+
+
+@dataclass
+class SparseMoeConfig:
+    """`SparseMoeConfig` of nn/moe.rs:42-50."""
+    hidden_size: int
+    expert_intermediate_size: int
+    num_experts: int
+    num_experts_per_tok: int
+
+    def init(self, device: int = 0, act_dtype: int = L.F32, weight_dtype: Optional[int] = None,
+             max_tokens: int = 0, expert_first: int = 0,
+             experts_local: Optional[int] = None) -> "SparseMoe":
+        """nn/moe.rs:61-99.  Weights are left undefined until set (the reference draws a uniform
+        init that every loader overwrites)."""
+        return SparseMoe(self, device, act_dtype, act_dtype if weight_dtype is None else weight_dtype,
+                         max_tokens, expert_first, experts_local)
+
+
+class SparseMoe:
+    """Router + expert bank on one B200 — `SparseMoe` (nn/moe.rs:34-39, 102-177) and, through
+    `route`/`run_local`, `SparseMoePerExpert` (nn/moe.rs:201-329)."""
+
+    def __init__(self, cfg: SparseMoeConfig, device: int, act_dtype: int, weight_dtype: int,
+                 max_tokens: int, expert_first: int, experts_local: Optional[int]):
+        self.cfg = cfg
+        self.device = device
+        self.act_dtype = act_dtype
+        self.weight_dtype = weight_dtype
+        self._h = C.c_void_p()
+        c = L.MummuMoeConfig(
+            device=device, hidden=cfg.hidden_size, inter=cfg.expert_intermediate_size,
+            experts=cfg.num_experts, top_k=cfg.num_experts_per_tok, act_dtype=act_dtype,
+            weight_dtype=weight_dtype, expert_first=expert_first,
+            experts_local=cfg.num_experts if experts_local is None else experts_local,
+            max_tokens=max_tokens)
+        self.experts_local = c.experts_local
+        self.expert_first = expert_first
+        _check(L.lib.mummu_moe_create(C.byref(c), C.byref(self._h)))
+
+    # -- life cycle -------------------------------------------------------------------------
+    def close(self) -> None:
+        if getattr(self, "_h", None) and self._h.value:
+            L.lib.mummu_moe_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- weights ----------------------------------------------------------------------------
+    def set_router(self, weight, layout: int = L.ROUTER_IN_OUT, bias=None) -> None:
+        """`gate: Linear` weight, [hidden, experts] (burn, nn/moe.rs:1642) or [experts, hidden]
+        (GGUF ffn_gate_inp, models/olmoe.rs:338-339)."""
+        w = np.ascontiguousarray(weight)
+        if w.dtype not in _NP_DTYPES:
+            w = w.astype(np.float32)
+        assert w.size == self.cfg.hidden_size * self.cfg.num_experts, "router weight size"
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        _check(L.lib.mummu_moe_set_router(self._h, w.ctypes.data, _NP_DTYPES[w.dtype], layout,
+                                          None if b is None else b.ctypes.data))
+
+    def set_bank(self, which: int, data) -> None:
+        """One of `MoeExperts::{gate, up, down}` (nn/moe.rs:22-30), [experts, out, in]; numpy
+        (f32/f16, uint16 bit patterns for bf16, uint8 Q4_K bytes) or a torch CUDA tensor."""
+        if _is_torch(data):
+            t = data.contiguous()
+            _check(L.lib.mummu_moe_set_bank(self._h, which, t.data_ptr(),
+                                            t.numel() * t.element_size(), 1))
+            return
+        a = np.ascontiguousarray(data)
+        _check(L.lib.mummu_moe_set_bank(self._h, which, a.ctypes.data, a.nbytes, 0))
+
+    def set_banks(self, gate, up, down) -> None:
+        self.set_bank(L.BANK_GATE, gate)
+        self.set_bank(L.BANK_UP, up)
+        self.set_bank(L.BANK_DOWN, down)
+
+    # -- the layer ----------------------------------------------------------------------------
+    def forward(self, x, top_k: int, norm_topk_prob: bool):
+        """[b, t, hidden] -> [b, t, hidden] (nn/moe.rs:116-177, 214-219)."""
+        shape = tuple(x.shape)
+        h = shape[-1]
+        if h != self.cfg.hidden_size:
+            raise MoeContractError(
+                f"MoE forward: input hidden {h} does not match expert hidden {self.cfg.hidden_size}")
+        tokens = int(np.prod(shape[:-1])) if len(shape) > 1 else 1
+        if _is_torch(x):
+            import torch
+            assert x.is_cuda and _torch_dtype_code(x) == self.act_dtype
+            xc = x.contiguous()
+            y = torch.empty_like(xc)
+            _check(L.lib.mummu_moe_forward(self._h, xc.data_ptr(), y.data_ptr(), tokens, top_k,
+                                           int(bool(norm_topk_prob)), 1, _torch_stream()))
+            return y.view(shape)
+        xa = self._host_act(x)
+        y = np.empty_like(xa)
+        _check(L.lib.mummu_moe_forward(self._h, xa.ctypes.data, y.ctypes.data, tokens, top_k,
+                                       int(bool(norm_topk_prob)), 0, None))
+        return y.reshape(shape)
+
+    def _host_act(self, x) -> np.ndarray:
+        want = {L.F32: np.float32, L.F16: np.float16, L.BF16: np.uint16}[self.act_dtype]
+        a = np.ascontiguousarray(x)
+        if self.act_dtype != L.BF16 and a.dtype != want:
+            a = a.astype(want)
+        assert a.dtype == want, "bf16 host activations are passed as uint16 bit patterns"
+        return a
+
+    def route_flat(self, xt, top_k: int, norm_topk_prob: bool):
+        """ids [tokens, top_k] int32 and weights [tokens, top_k] f32 (descending probability)."""
+        tokens = xt.shape[0]
+        if _is_torch(xt):
+            import torch
+            xc = xt.contiguous()
+            ids = torch.empty((tokens, top_k), dtype=torch.int32, device=xc.device)
+            w = torch.empty((tokens, top_k), dtype=torch.float32, device=xc.device)
+            _check(L.lib.mummu_moe_route(self._h, xc.data_ptr(), tokens, top_k,
+                                         int(bool(norm_topk_prob)), ids.data_ptr(), w.data_ptr(), 1,
+                                         _torch_stream()))
+            return ids, w
+        xa = self._host_act(xt)
+        ids = np.empty((tokens, max(top_k, 0)), dtype=np.int32)
+        w = np.empty((tokens, max(top_k, 0)), dtype=np.float32)
+        _check(L.lib.mummu_moe_route(self._h, xa.ctypes.data, tokens, top_k,
+                                     int(bool(norm_topk_prob)), ids.ctypes.data, w.ctypes.data, 0,
+                                     None))
+        return ids, w
+
+    def route(self, xt, top_k: int, norm_topk_prob: bool) -> Routing:
+        """`SparseMoePerExpert::route` (nn/moe.rs:247-290): the per-expert (rows, weights) lists,
+        token-major."""
+        ids, w = self.route_flat(xt, top_k, norm_topk_prob)
+        if _is_torch(ids):
+            ids, w = ids.cpu().numpy(), w.cpu().numpy()
+        routed: List[Tuple[List[int], List[float]]] = [([], []) for _ in range(self.cfg.num_experts)]
+        for token in range(ids.shape[0]):
+            for slot in range(ids.shape[1]):
+                e = int(ids[token, slot])
+                routed[e][0].append(token)
+                routed[e][1].append(float(w[token, slot]))
+        return Routing(tokens=ids.shape[0], per_expert=routed)
+
+    def run_local(self, xt: np.ndarray, routing: Routing) -> np.ndarray:
+        """`SparseMoePerExpert::run_local` (nn/moe.rs:296-328): ascending expert id, gather rows,
+        run the expert, scatter-add `y * scale` (two roundings)."""
+        xt = np.ascontiguousarray(xt, dtype=np.float32)
+        out = np.zeros_like(xt)
+        for expert, (rows, weights) in enumerate(routing.per_expert):
+            if not rows:
+                continue
+            y = CudaExpert(self, expert).run(xt[rows].reshape(-1), len(rows), xt.shape[1])
+            y = y.reshape(len(rows), xt.shape[1])
+            scaled = y * np.asarray(weights, dtype=np.float32)[:, None]
+            np.add.at(out, rows, scaled)
+        return out
+
+    # -- taps -------------------------------------------------------------------------------
+    def dequant_bank(self, which: int, expert: int) -> np.ndarray:
+        out_dim = self.cfg.hidden_size if which == L.BANK_DOWN else self.cfg.expert_intermediate_size
+        in_dim = self.cfg.expert_intermediate_size if which == L.BANK_DOWN else self.cfg.hidden_size
+        out = np.empty((out_dim, in_dim), dtype=np.float32)
+        _check(L.lib.mummu_moe_dequant_bank(self._h, which, expert, out.ctypes.data))
+        return out
+
+    def take_hits(self) -> np.ndarray:
+        """`ExpertPool::take_hits` (nn/moe.rs:1527-1535) for this layer."""
+        out = np.zeros(self.cfg.num_experts, dtype=np.uint64)
+        _check(L.lib.mummu_moe_take_hits(self._h, out.ctypes.data))
+        return out
+
+    def sync(self) -> None:
+        stream = None
+        try:
+            import torch
+            if torch.cuda.is_available():
+                stream = _torch_stream()
+        except ImportError:
+            pass
+        _check(L.lib.mummu_moe_sync(self._h, stream))
+
+    def set_profiling(self, enabled: bool) -> None:
+        _check(L.lib.mummu_moe_set_profiling(self._h, int(enabled)))
+
+    def take_profile(self) -> dict:
+        buf = C.create_string_buffer(4096)
+        _check(L.lib.mummu_moe_take_profile(self._h, buf, 4096))
+        out = {}
+        for item in buf.value.decode().split(";"):
+            if "=" in item:
+                name, rest = item.split("=")
+                n, ms = rest.split(":")
+                out[name] = (int(n), float(ms))
+        return out
+
+    def launch_count(self) -> int:
+        return int(L.lib.mummu_moe_launch_count(self._h))
+
+    # -- staged calls (device tensors), used by the expert-parallel layer -----------------------
+    def permute(self, ids, counts=None, offsets=None, row_token=None, pos=None) -> None:
+        tokens, top_k = ids.shape
+        p = lambda t: None if t is None else t.data_ptr()
+        _check(L.lib.mummu_moe_permute(self._h, ids.data_ptr(), tokens, top_k, p(counts), p(offsets),
+                                       p(row_token), p(pos), _torch_stream()))
+
+    def experts_grouped(self, xs, counts, ys) -> None:
+        _check(L.lib.mummu_moe_experts_grouped(self._h, xs.data_ptr(), counts.data_ptr(),
+                                               xs.shape[0], ys.data_ptr(), _torch_stream()))
+
+    def combine(self, ys, ids, w, pos, out) -> None:
+        tokens, top_k = ids.shape
+        _check(L.lib.mummu_moe_combine(self._h, ys.data_ptr(), ids.data_ptr(), w.data_ptr(),
+                                       pos.data_ptr(), tokens, top_k, out.data_ptr(),
+                                       _torch_stream()))
+
+
+SparseMoePerExpert = SparseMoe
+
+
+class CudaExpert:
+    """`ExpertExec` (nn/moe.rs:348-419) for one expert of a bank: `run(&[f32], rows, hidden)`."""
+
+    def __init__(self, moe: SparseMoe, expert: int):
+        self.moe = moe
+        self.expert = expert
+
+    def run(self, x: np.ndarray, rows: int, hidden: int) -> np.ndarray:
+        if hidden != self.moe.cfg.hidden_size:
+            raise MoeContractError(f"expert input hidden {hidden} != {self.moe.cfg.hidden_size}")
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+        if x.size != rows * hidden:
+            raise MoeContractError(f"expert input holds {x.size} values, wants {rows} x {hidden}")
+        y = np.empty(rows * hidden, dtype=np.float32)
+        _check(L.lib.mummu_expert_run(self.moe._h, self.expert, x.ctypes.data, rows, y.ctypes.data))
+        return y
+
+    def resident_bytes(self) -> int:
+        c = self.moe.cfg
+        per = {L.F32: 4.0, L.F16: 2.0, L.BF16: 2.0, L.Q4_K: 144.0 / 256.0}[self.moe.weight_dtype]
+        return int(3 * c.hidden_size * c.expert_intermediate_size * per)
+
+
+def q4k_quantize_device(src):
+    """f32 torch CUDA tensor (size % 256 == 0) -> uint8 tensor of Q4_K bytes, on the device."""
+    import torch
+    assert src.is_cuda and src.dtype == torch.float32 and src.numel() % 256 == 0
+    src = src.contiguous()
+    nb = src.numel() // 256
+    dst = torch.empty(nb * 144, dtype=torch.uint8, device=src.device)
+    _check(L.lib.mummu_q4k_quantize(src.data_ptr(), dst.data_ptr(), nb, src.device.index,
+                                    _torch_stream()))
+    return dst
+
+
+def q4k_dequantize_device(raw):
+    import torch
+    assert raw.is_cuda and raw.dtype == torch.uint8 and raw.numel() % 144 == 0
+    nb = raw.numel() // 144
+    dst = torch.empty(nb * 256, dtype=torch.float32, device=raw.device)
+    _check(L.lib.mummu_q4k_dequantize(raw.contiguous().data_ptr(), dst.data_ptr(), nb,
+                                      raw.device.index, _torch_stream()))
+    return dst

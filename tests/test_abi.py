@@ -1,0 +1,45 @@
+"""CPU tests of the boundary: the library loads, exports every symbol the header declares, and
+refuses contract violations with the reference's messages — no compute, no GPU."""
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "mummu_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mummu_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(cuda_lib):
+    names = header_symbols()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(cuda_lib.lib, name), f"{name} declared in mummu_cuda.h but not exported"
+    assert set(names) == set(cuda_lib.SYMBOLS), "ctypes table and header disagree"
+    assert b"sm_100a" in cuda_lib.lib.mummu_cuda_version()
+
+
+def test_config_contract_messages(cuda_lib):
+    """nn/moe.rs:62-76 and the should_panic tests at :2354-2374."""
+    from mummu_b200 import moe
+    with pytest.raises(moe.MoeContractError, match="num_experts_per_tok"):
+        moe.SparseMoeConfig(4, 3, 4, 0).init()
+    with pytest.raises(moe.MoeContractError, match="num_experts_per_tok"):
+        moe.SparseMoeConfig(4, 3, 4, 5).init()
+    with pytest.raises(moe.MoeContractError, match="num_experts must be >= 2"):
+        moe.SparseMoeConfig(4, 3, 1, 1).init()
+    with pytest.raises(moe.MoeContractError, match="hidden_size and expert_intermediate_size"):
+        moe.SparseMoeConfig(0, 3, 4, 2).init()
+    with pytest.raises(moe.MoeContractError, match="256-value super-blocks"):
+        moe.SparseMoeConfig(100, 256, 4, 2).init(weight_dtype=cuda_lib.Q4_K, act_dtype=cuda_lib.F16)
+
+
+def test_null_handle_is_refused_not_crashed(cuda_lib):
+    rc = cuda_lib.lib.mummu_moe_forward(None, None, None, 1, 1, 0, 0, None)
+    assert rc == cuda_lib.ERR_CONTRACT
+    assert "null" in cuda_lib.last_error()
+    assert cuda_lib.lib.mummu_moe_destroy(None) == cuda_lib.OK

@@ -1,0 +1,323 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on the same
+seeded inputs.  Bars: routing ids, routing weights and dequantised weights bit-exact; layer
+outputs within 1e-4 (f32) / 2e-2 (f16, bf16, Q4_K) relative, measured as max|a-b| / max|b|
+(the reference's convention, crates/mummu/src/nn/packed_gemv.rs:1610-1622)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+
+import toy  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+from mummu_b200 import q4k, synth  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-4
+TOL_16 = 2e-2
+
+
+def rel_err(a, b):
+    return float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max() / max(np.abs(b).max(), 1e-30))
+
+
+@pytest.fixture(scope="module")
+def M(cuda_lib):
+    from mummu_b200 import moe
+    return moe
+
+
+def make_layer(M, L, H, I, E, K, act, wdt, router, gate, up, down, bias=None, max_tokens=0):
+    m = M.SparseMoeConfig(H, I, E, K).init(act_dtype=act, weight_dtype=wdt, max_tokens=max_tokens)
+    m.set_router(router, bias=bias)
+    m.set_banks(gate, up, down)
+    return m
+
+
+def bf16_bits(a):
+    """f32 -> bf16 bit patterns, round to nearest even."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return r
+
+
+def bf16_to_f32(bits):
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+# ---- toy layer: the reference's own unit-test shapes --------------------------------------------
+
+@pytest.mark.parametrize("t,seed,norm,k", [(5, 2.0, False, 2), (5, 2.0, True, 2), (1, 2.0, False, 2),
+                                            (1, 2.0, True, 2), (5, 7.0, True, 2), (3, 0.5, False, 4)])
+def test_toy_layer(M, cuda_lib, t, seed, norm, k):
+    """nn/moe.rs:2177-2230 on HIDDEN=4, INTER=3, EXPERTS=4 (ragged: nothing divides a tile)."""
+    L = cuda_lib
+    rw = toy.router()
+    g, u, d = toy.banks()
+    x = toy.inputs(t, seed)
+    m = make_layer(M, L, toy.HIDDEN, toy.INTER, toy.EXPERTS, toy.EXPERTS, L.F32, L.F32, rw, g, u, d)
+    y = m.forward(x.reshape(1, t, toy.HIDDEN), k, norm).reshape(t, toy.HIDDEN)
+    ids, w = m.route_flat(x, k, norm)
+    want, wid, ww = O.moe_forward(x, rw, g, u, d, k, norm)
+    assert np.array_equal(ids, wid)
+    assert np.array_equal(w.view(np.uint32), ww.view(np.uint32))
+    assert np.abs(y - want).max() < 1e-5
+    gold = np.load(os.path.join(HERE, "golden", "toy_moe.npz"))
+    key = f"t{t}_s{seed}_n{int(norm)}_k{k}"
+    assert np.array_equal(ids, gold[key + "_ids"])
+    assert np.abs(y - gold[key + "_y"]).max() < 1e-5
+    m.close()
+
+
+def test_toy_properties(M, cuda_lib):
+    """Position independence bit-exact, zero in -> zero out, renorm changes the mixture, top_k
+    contract (nn/moe.rs:2297-2361)."""
+    L = cuda_lib
+    rw = toy.router()
+    g, u, d = toy.banks()
+    m = make_layer(M, L, toy.HIDDEN, toy.INTER, toy.EXPERTS, toy.EXPERTS, L.F32, L.F32, rw, g, u, d)
+    row = toy.inputs(1, 11.0)
+    s = m.forward(row, 2, False)
+    dd = m.forward(np.concatenate([row, row]), 2, False)
+    assert np.array_equal(s[0], dd[0]) and np.array_equal(s[0], dd[1])
+    z = m.forward(np.zeros((2, toy.HIDDEN), np.float32), 2, False)
+    assert (z == 0).all()
+    x = toy.inputs(4, 7.0)
+    assert (np.abs(m.forward(x, 2, False) - m.forward(x, 2, True)) > 1e-7).any()
+    with pytest.raises(M.MoeContractError, match="top_k"):
+        m.forward(row, toy.EXPERTS + 1, False)
+    with pytest.raises(M.MoeContractError, match="top_k"):
+        m.forward(row, 0, False)
+    with pytest.raises(M.MoeContractError, match="hidden"):
+        m.forward(np.zeros((1, 5), np.float32), 2, False)
+    assert m.forward(np.zeros((0, toy.HIDDEN), np.float32), 2, False).shape == (0, toy.HIDDEN)
+    m.close()
+
+
+def test_router_known_answers_on_device(M, cuda_lib):
+    """The reference's router vectors (models/qwen4exp/experts.rs:1366-1408) through the CUDA
+    router: an identity-like router weight turns activations into the listed logits."""
+    L = cuda_lib
+    E = 8
+    eye = np.eye(E, dtype=np.float32)
+    z = np.zeros((E, 1, E), np.float32)
+    m = make_layer(M, L, E, 1, E, E, L.F32, L.F32, eye, z, z, np.zeros((E, E, 1), np.float32))
+    ids, w = m.route_flat(np.array([[0.0, 3.0, 1.0, 2.5, -2.0, 2.0, 0.5, 2.9]], np.float32), 3, True)
+    assert ids.tolist() == [[1, 7, 3]]
+    assert abs(w.sum() - 1.0) < 1e-6
+    ids, w = m.route_flat(np.full((1, E), 0.5, np.float32), 3, True)
+    assert ids.tolist() == [[0, 1, 2]]
+    assert np.allclose(w, 1 / 3, atol=1e-6)
+    m.close()
+    m = make_layer(M, L, 4, 1, 4, 4, L.F32, L.F32, np.eye(4, dtype=np.float32), np.zeros((4, 1, 4), np.float32),
+                   np.zeros((4, 1, 4), np.float32), np.zeros((4, 4, 1), np.float32))
+    ids, _ = m.route_flat(np.array([[1.0, 0.0, 2.0, 1.0]], np.float32), 2, False)
+    assert ids.tolist() == [[2, 0]]
+    m.close()
+    m = make_layer(M, L, 16, 1, 16, 16, L.F32, L.F32, np.eye(16, dtype=np.float32), np.zeros((16, 1, 16), np.float32),
+                   np.zeros((16, 1, 16), np.float32), np.zeros((16, 16, 1), np.float32))
+    logits = np.full((3, 16), -1000.0, np.float32)
+    logits[0, 5], logits[1, 9], logits[1, 3], logits[2, 15] = 1000.0, 999.0, 998.0, 30.0
+    ids, w = m.route_flat(logits, 2, True)
+    oid, ow = O.route(logits, 2, True)
+    assert np.array_equal(ids, oid) and np.array_equal(w.view(np.uint32), ow.view(np.uint32))
+    assert ids[0, 0] == 5 and ids[1].tolist() == [9, 3] and ids[2, 0] == 15
+    # non-finite logits are refused (experts.rs:1411-1417)
+    bad = logits.copy()
+    bad[1, 1] = np.nan
+    with pytest.raises(M.MoeNumericError):
+        m.route_flat(bad, 2, True)
+    ids, _ = m.route_flat(logits, 2, True)      # the handle stays usable
+    assert np.array_equal(ids, oid)
+    m.close()
+
+
+# ---- routing bit-exactness at the benchmark shapes ---------------------------------------------
+
+@pytest.mark.parametrize("T,H,E,K,norm,act", [(16, 2048, 64, 8, False, "f32"), (333, 2048, 64, 8, True, "f32"),
+                                              (4096, 2048, 64, 8, False, "bf16"), (64, 2048, 64, 8, False, "f16"),
+                                              (257, 2048, 128, 8, False, "f32"), (7, 100, 20, 5, True, "f32")])
+def test_routing_bit_exact(M, cuda_lib, T, H, E, K, norm, act):
+    L = cuda_lib
+    router = synth.normal(synth.layer_seed(1, 0, 0), (H, E), 0.02)
+    x = synth.normal(synth.layer_seed(1, 0, 4), (T, H), 1.0)
+    bias = synth.zipf_router_bias(E, 1.0) if T == 4096 else None
+    code = {"f32": L.F32, "f16": L.F16, "bf16": L.BF16}[act]
+    if act == "f16":
+        xin = x.astype(np.float16)
+        x = xin.astype(np.float32)
+    elif act == "bf16":
+        xin = bf16_bits(x)
+        x = bf16_to_f32(xin)
+    else:
+        xin = x
+    z = np.zeros((E, 1, H), np.float32)
+    m = M.SparseMoeConfig(H, 1, E, K).init(act_dtype=code, weight_dtype=L.F32)
+    m.set_router(router, bias=bias)
+    ids, w = m.route_flat(xin, K, norm)
+    oid, ow = O.route(O.router_logits(x, router, bias), K, norm)
+    assert np.array_equal(ids, oid)
+    assert np.array_equal(w.view(np.uint32), ow.view(np.uint32))
+    hits = m.take_hits()
+    assert np.array_equal(hits, np.bincount(oid.reshape(-1), minlength=E).astype(np.uint64))
+    assert m.take_hits().sum() == 0
+    m.close()
+
+
+# ---- Q4_K -----------------------------------------------------------------------------------
+
+def test_q4k_dequant_bit_exact_and_quantiser_parity(M, cuda_lib):
+    import torch
+    L = cuda_lib
+    H, I, E = 512, 256, 3
+    _, gate, up, down, _ = synth.moe_layer(H, I, E, 1, cfg_seed=2)
+    gq, uq, dq = (q4k.quantize(b) for b in (gate, up, down))
+    m = M.SparseMoeConfig(H, I, E, 2).init(act_dtype=L.F16, weight_dtype=L.Q4_K)
+    m.set_banks(gq, uq, dq)
+    for which, raw, shape in ((L.BANK_GATE, gq, (E, I, H)), (L.BANK_UP, uq, (E, I, H)), (L.BANK_DOWN, dq, (E, H, I))):
+        want = O.dequant_q4_k(raw).reshape(shape)
+        for e in range(E):
+            got = m.dequant_bank(which, e)
+            assert np.array_equal(got.view(np.uint32), want[e].view(np.uint32))
+    m.close()
+    # random bytes (every scale/nibble pattern), sane f16 scales as the reference's synthetic blocks
+    rng = np.random.default_rng(9)
+    raw = rng.integers(0, 256, size=(4096, 144), dtype=np.uint8)
+    raw[:, 0:2] = np.frombuffer(rng.uniform(0.0005, 0.003, 4096).astype(np.float16).tobytes(), np.uint8).reshape(4096, 2)
+    raw[:, 2:4] = np.frombuffer(rng.uniform(0.0005, 0.003, 4096).astype(np.float16).tobytes(), np.uint8).reshape(4096, 2)
+    got = M.q4k_dequantize_device(torch.from_numpy(raw.reshape(-1)).cuda()).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), O.dequant_q4_k(raw).view(np.uint32))
+    # device encoder == host encoder, byte for byte
+    w = synth.normal(77, (2048, 256), 0.02)
+    dev = M.q4k_quantize_device(torch.from_numpy(w).cuda()).cpu().numpy()
+    assert np.array_equal(dev, q4k.quantize(w))
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 7, 8, 9, 16, 17, 33, 64])
+def test_q4k_decode_layer(M, cuda_lib, T):
+    """Decode regime, Q4_K experts, f16 activations, the ragged token counts included."""
+    L = cuda_lib
+    H, I, E, K = 1024, 512, 16, 4
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=4)
+    gq, uq, dq = (q4k.quantize(b) for b in (gate, up, down))
+    xh = x.astype(np.float16)
+    m = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, gq, uq, dq)
+    y = m.forward(xh, K, False).astype(np.float32)
+    want, oid, ow = O.moe_forward(xh.astype(np.float32), router, gq, uq, dq, K, False, q4k=True)
+    ids, w = m.route_flat(xh, K, False)
+    assert np.array_equal(ids, oid) and np.array_equal(w.view(np.uint32), ow.view(np.uint32))
+    assert rel_err(y, want) < TOL_16
+    # position independence, bit-exact: token 0 alone == token 0 in the batch (nn/moe.rs:2318-2338)
+    alone = m.forward(xh[:1], K, False)
+    assert np.array_equal(alone[0], m.forward(xh, K, False)[0])
+    m.close()
+
+
+def test_q4k_decode_all_tokens_one_expert(M, cuda_lib):
+    """Collision edge: every token routed to the same experts (more rows than one token tile)."""
+    L = cuda_lib
+    H, I, E, K, T = 512, 256, 8, 2, 40
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=6)
+    bias = np.zeros(E, np.float32)
+    bias[3], bias[5] = 50.0, 40.0
+    gq, uq, dq = (q4k.quantize(b) for b in (gate, up, down))
+    xh = x.astype(np.float16)
+    m = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, gq, uq, dq, bias=bias)
+    y = m.forward(xh, K, True).astype(np.float32)
+    want, oid, _ = O.moe_forward(xh.astype(np.float32), router, gq, uq, dq, K, True, bias=bias, q4k=True)
+    assert set(oid.reshape(-1).tolist()) == {3, 5}
+    assert rel_err(y, want) < TOL_16
+    m.close()
+
+
+def test_q4k_small_golden(M, cuda_lib):
+    L = cuda_lib
+    gold = np.load(os.path.join(HERE, "golden", "q4k_small.npz"))
+    m = make_layer(M, L, 256, 256, 4, 2, L.F16, L.Q4_K, gold["router"], gold["gate_q"], gold["up_q"], gold["down_q"])
+    xh = gold["x"].astype(np.float16)
+    ids, w = m.route_flat(xh, 2, False)
+    assert np.array_equal(ids, gold["ids"]) and np.array_equal(w.view(np.uint32), gold["w"].view(np.uint32))
+    assert rel_err(m.forward(xh, 2, False).astype(np.float32), gold["y"]) < TOL_16
+    assert np.array_equal(m.dequant_bank(L.BANK_GATE, 0)[:4].reshape(-1).view(np.uint32),
+                          gold["gate_deq_rows"].view(np.uint32))
+    m.close()
+
+
+# ---- float banks ------------------------------------------------------------------------------
+
+def test_config1_f32_layer(M, cuda_lib):
+    """T=16, hidden 2048, 64 experts, top-8 without renormalisation, intermediate 1024, f32
+    N(0, 0.02) weights, N(0, 1) activations, seed 0; checked against both the routed and the
+    dense-mask form of the reference (nn/moe.rs:116-177, 296-328)."""
+    L = cuda_lib
+    H, I, E, K, T = 2048, 1024, 64, 8, 16
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=0)
+    m = make_layer(M, L, H, I, E, K, L.F32, L.F32, router, gate, up, down)
+    y = m.forward(x.reshape(1, T, H), K, False).reshape(T, H)
+    want, oid, ow = O.moe_forward(x, router, gate, up, down, K, False)
+    ids, w = m.route_flat(x, K, False)
+    assert np.array_equal(ids, oid) and np.array_equal(w.view(np.uint32), ow.view(np.uint32))
+    assert rel_err(y, want) < TOL_F32
+    dense, _, _ = O.moe_forward(x, router, gate, up, down, K, False, dense_mask=True)
+    assert rel_err(y, dense) < TOL_F32
+    # ExpertExec::run and SparseMoePerExpert::{route, run_local}
+    e = int(oid[0, 0])
+    got = M.CudaExpert(m, e).run(x[:3].reshape(-1), 3, H).reshape(3, H)
+    assert rel_err(got, O.expert_ffn(gate[e], up[e], down[e], x[:3])) < TOL_F32
+    routing = m.route(x, K, False)
+    assert sum(len(r) for r, _ in routing.per_expert) == T * K
+    assert rel_err(m.run_local(x, routing), want) < TOL_F32
+    m.close()
+
+
+@pytest.mark.parametrize("act", ["f16", "bf16"])
+def test_half_precision_layer(M, cuda_lib, act):
+    L = cuda_lib
+    H, I, E, K, T = 512, 256, 16, 4, 50
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=8)
+    if act == "f16":
+        conv = lambda a: a.astype(np.float16)
+        back = lambda a: a.astype(np.float32)
+        code = L.F16
+    else:
+        conv, back, code = bf16_bits, bf16_to_f32, L.BF16
+    gq, uq, dq, xq = conv(gate), conv(up), conv(down), conv(x)
+    m = make_layer(M, L, H, I, E, K, code, code, router, gq, uq, dq)
+    y = back(m.forward(xq, K, False))
+    want, _, _ = O.moe_forward(back(xq), router, back(gq), back(uq), back(dq), K, False)
+    assert rel_err(y, want) < TOL_16
+    m.close()
+
+
+def test_staged_calls_match_whole_layer(M, cuda_lib):
+    """permute -> experts_grouped -> combine on device tensors == forward."""
+    import torch
+    L = cuda_lib
+    H, I, E, K, T = 256, 128, 8, 2, 37
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=12)
+    m = make_layer(M, L, H, I, E, K, L.F32, L.F32, router, gate, up, down)
+    xd = torch.from_numpy(x).cuda()
+    whole = m.forward(xd, K, False)
+    ids, w = m.route_flat(xd, K, False)
+    counts = torch.zeros(E, dtype=torch.int32, device="cuda")
+    offsets = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    row_token = torch.zeros(T * K, dtype=torch.int32, device="cuda")
+    pos = torch.zeros(T * K, dtype=torch.int32, device="cuda")
+    m.permute(ids, counts, offsets, row_token, pos)
+    idn = ids.cpu().numpy()
+    assert np.array_equal(counts.cpu().numpy(), np.bincount(idn.reshape(-1), minlength=E))
+    order = np.argsort(idn.reshape(-1), kind="stable")
+    assert np.array_equal(row_token.cpu().numpy(), order // K)
+    assert np.array_equal(pos.cpu().numpy()[order], np.arange(T * K))
+    xs = xd[row_token.long()]
+    ys = torch.empty_like(xs)
+    m.experts_grouped(xs, counts, ys)
+    out = torch.empty_like(xd)
+    m.combine(ys, ids, w, pos, out)
+    m.sync()
+    assert torch.equal(out, whole)
+    m.close()

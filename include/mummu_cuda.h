@@ -97,8 +97,9 @@ int32_t mummu_moe_set_bank(MummuMoe* moe, int32_t which, const void* data, size_
  * flattened [tokens, hidden] input: router -> softmax over all experts (f32) -> top_k of the
  * probabilities (ties: lowest expert id) -> optional renormalisation -> routed SwiGLU experts ->
  * weighted sum in ascending expert order.  x and y hold tokens*hidden values of act_dtype;
- * `on_device` != 0: both are device pointers and the work is queued on `stream` (a cudaStream_t,
- * NULL = the handle's own stream) without waiting; otherwise both are host pointers and the call
+ * `on_device` != 0: both are device pointers and the work is queued on `stream` (a cudaStream_t;
+ * NULL = the handle's own non-blocking stream, so pass cudaStreamLegacy / cudaStreamPerThread to
+ * name a default stream) without waiting; otherwise both are host pointers and the call
  * returns when y is written.  Requires expert_first == 0 and experts_local == experts. */
 int32_t mummu_moe_forward(MummuMoe* moe, const void* x, void* y, int32_t tokens, int32_t top_k,
                           int32_t norm_topk_prob, int32_t on_device, void* stream);

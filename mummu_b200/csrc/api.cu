@@ -18,6 +18,24 @@ void set_error(const char* fmt, ...) {
     g_error = buf;
 }
 
+cudaError_t allow_big_smem_impl(const void* kernel, int device) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, bool> done;
+    std::lock_guard<std::mutex> lock(mu);
+    auto key = std::make_pair(kernel, device);
+    if (done.count(key)) return cudaSuccess;
+    int optin = 0;
+    cudaError_t err = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    if (err != cudaSuccess) return err;
+    cudaFuncAttributes fa;
+    err = cudaFuncGetAttributes(&fa, kernel);
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               optin - (int)fa.sharedSizeBytes);
+    if (err == cudaSuccess) done[key] = true;
+    return err;
+}
+
 size_t bank_row_bytes(const MummuMoeConfig& c, int which) {
     size_t in_dim = which == MUMMU_BANK_DOWN ? c.inter : c.hidden;
     if (c.weight_dtype == MUMMU_Q4_K) return in_dim / Q4K_BLOCK_ELEMS * Q4K_BLOCK_BYTES;

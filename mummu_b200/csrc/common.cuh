@@ -162,6 +162,14 @@ size_t bank_row_bytes(const MummuMoeConfig& c, int which);
 size_t bank_total_bytes(const MummuMoeConfig& c, int which);
 int ensure_scratch(MummuMoe* m, int64_t tokens);
 
+// Opt a kernel into the full 227 KB of dynamic shared memory, once per (kernel, device): the
+// attribute call is kept out of the steady state so that a layer call can be stream-captured.
+cudaError_t allow_big_smem_impl(const void* kernel, int device);
+template <typename Kernel>
+cudaError_t allow_big_smem(Kernel kernel, int device) {
+    return allow_big_smem_impl(reinterpret_cast<const void*>(kernel), device);
+}
+
 // profiling-aware launch bracket
 struct LaunchScope {
     MummuMoe* m;

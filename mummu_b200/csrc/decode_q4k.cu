@@ -8,20 +8,23 @@
 //  models/qwen4exp/experts.rs:781-806, 401-457).
 //
 // How a weight reaches the tensor core.  A Q4_K value is d*sc_j*q - dmin*m_j with q a 4-bit
-// integer and (sc_j, m_j) per 32-value sub-block.  A dot product over one sub-block is therefore
-//     d*sc_j * sum(q*x)  -  dmin*m_j * sum(x).
-// sum(q*x) is an m16n8k16 f16 MMA whose A operand is the raw nibbles turned into exact f16
-// integers (one LOP3 per two values: 0x6400|q is the half 1024+q; the high nibble gives
-// 1024+16q), whose B operand is the token tile, and whose C operand starts at -1024*sum(x) so
-// the bias of that trick cancels.  The sub-block scale is applied in f32 after every 32-wide
-// slice, so no weight is ever rounded to 16 bits.  The min term is one m16n8k8 MMA per
-// super-block over (m_j) x (sub-block sums of x).
+// integer and (sc_j, m_j) 6-bit integers per 32-value sub-block, so over one 256-value super-block
+//     dot = d * sum_j sum_k (sc_j*q_k) x_k  -  dmin * sum_j m_j * (sum of x over sub-block j).
+// sc_j*q_k <= 945 is an integer an f16 holds exactly.  One LOP3 turns two nibbles of a word into
+// the halves 1024+q (low nibble: 0x6400|q) or 1024+16q (high nibble), and one HFMA2 with the
+// lane's (sc, -1024*sc) or (sc/16, -64*sc) turns those into sc*q with no rounding at all.  These
+// feed m16n8k16 f16 MMAs against the token tile with f32 accumulation over the whole super-block;
+// d and dmin are applied in f32 once per super-block.  No weight is rounded to 16 bits.  The min
+// term is one m16n8k8 MMA per super-block over (m_j) x (sub-block sums of x).
 //
+// Lane mapping: the four lanes that share a weight row (the MMA "quad") each own one 32-byte
+// quant chunk = two whole sub-blocks, so a lane needs only its own two (sc, m) pairs, loads its
+// chunk with two 128-bit loads, and the quad reads one whole 144-byte super-block contiguously.
 // Work split: one CTA = (active expert, a run of 16-row tiles); its 8 warps split K by
 // super-block (and, when K has fewer than 8 super-blocks, take several row tiles at once); the
-// token tile (fragments in MMA register order) and the sub-block sums of x sit in shared memory.
-// A lane loads 8 contiguous bytes of each 32-byte quant chunk, so the four lanes that share a
-// weight row read whole 32-byte sectors, and each 144-byte super-block is read exactly once.
+// token tile sits in shared memory already in MMA fragment order.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace mummu {
@@ -48,6 +51,7 @@ struct DecodeArgs {
     void* out;                  // gate/up: __half hact; down: float ys
 };
 
+// D = A*B + C with C given separately (zero registers for the first MMA of a chain)
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -57,74 +61,192 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ void mma_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+__device__ __forceinline__ void mma_1688_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm volatile(
         "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(b0));
+        "{%7,%7,%7,%7};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "f"(0.0f));
 }
 
-// two nibbles of a word -> half2 of exact integers: (w & mask) | 0x6400 in each half
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// two nibbles of a word -> half2 (1024+q) resp. (1024+16q)
 __device__ __forceinline__ uint32_t nib_lo(uint32_t w) { return (w & 0x000F000Fu) | 0x64006400u; }
 __device__ __forceinline__ uint32_t nib_hi(uint32_t w) { return (w & 0x00F000F0u) | 0x64006400u; }
 
-struct RowScales {
-    float dsc[8];     // even j: d*sc_j ; odd j: d*sc_j / 16 (the high-nibble MMA carries 16q)
-    float dmin;
-    uint32_t m_h2;    // half2 (m_{2t}, m_{2t+1})
+// What one lane needs from the 16-byte super-block header (f16 d, f16 dmin, 12 packed scale
+// bytes; crates/mummu/src/gguf.rs:1685-1698) for its two sub-blocks 2t and 2t+1.
+struct LaneScales {
+    uint32_t sc_lo, c_lo;   // half2 (sc_2t, sc_2t)        and (-1024*sc_2t) x2
+    uint32_t sc_hi, c_hi;   // half2 (sc_2t+1/16) x2       and (-64*sc_2t+1) x2
+    uint32_t m_h2;          // half2 (m_2t, m_2t+1)
+    float d, dmin;
 };
 
-// header = the first 16 bytes of a super-block: f16 d, f16 dmin, 12 packed scale bytes
-// (crates/mummu/src/gguf.rs:1685-1698 unpacked four bytes at a time)
-__device__ __forceinline__ void decode_scales(const uint4& h, int t, RowScales& r) {
-    float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu)));
+__device__ __forceinline__ void lane_scales(const uint4& h, bool upper, uint32_t sel, LaneScales& r) {
+    r.d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu)));
     r.dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-    uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
-    uint32_t sc_lo = s0 & 0x3F3F3F3Fu;
-    uint32_t m_lo = s1 & 0x3F3F3F3Fu;
-    uint32_t sc_hi = (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u);
-    uint32_t m_hi = ((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u);
-    const float d16 = d * 0.0625f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float a = (float)((sc_lo >> (8 * i)) & 0xFFu);
-        float b = (float)((sc_hi >> (8 * i)) & 0xFFu);
-        r.dsc[i] = (i & 1) ? d16 * a : d * a;
-        r.dsc[4 + i] = (i & 1) ? d16 * b : d * b;
-    }
-    uint32_t msel = (t < 2) ? m_lo : m_hi;
-    uint32_t pair = (msel >> (16 * (t & 1))) & 0xFFFFu;
-    uint32_t spread = (pair & 0xFFu) | ((pair & 0xFF00u) << 8);
-    uint32_t bits = spread | 0x64006400u;   // half2 (1024 + m_a, 1024 + m_b)
-    __half2 mh = __hsub2(*reinterpret_cast<__half2*>(&bits),
-                         __half2half2(__ushort_as_half((unsigned short)0x6400)));
-    r.m_h2 = *reinterpret_cast<uint32_t*>(&mh);
+    const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
+    // upper (sub-blocks 4..7): sc = (s2 & 0xF) | ((s0 >> 6) << 4), m = (s2 >> 4) | ((s1 >> 6) << 4)
+    const uint32_t scw = upper ? ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u)) : (s0 & 0x3F3F3F3Fu);
+    const uint32_t mw = upper ? (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u)) : (s1 & 0x3F3F3F3Fu);
+    const uint32_t k1024 = 0x64006400u;
+    // bytes (a, 0x64, b, 0x64) = half2 (1024+a, 1024+b); minus 1024 -> the integers as halves
+    const uint32_t sc2 = hsub2_u32(__byte_perm(scw, 0x64646464u, sel), k1024);
+    r.m_h2 = hsub2_u32(__byte_perm(mw, 0x64646464u, sel), k1024);
+    r.sc_lo = __byte_perm(sc2, 0, 0x1010);
+    const uint32_t hi2 = __byte_perm(sc2, 0, 0x3232);
+    r.c_lo = hmul2_u32(r.sc_lo, 0xE400E400u);    // * -1024
+    r.sc_hi = hmul2_u32(hi2, 0x2C002C00u);       // * 1/16
+    r.c_hi = hmul2_u32(hi2, 0xD400D400u);        // * -64
 }
 
-// shared-memory carve-up for one CTA
-struct SmemLayout {
-    uint4* frag;      // [nsb*8][NT][8 tok][4 t]  B fragments (16 B each)
-    float* negs;      // [nsb*8][NT][8 tok]       -1024 * sub-block sum of x
-    __half* sxh;      // [nsb][NT][8 tok][8 j]    sub-block sums of x, f16
-    float4* part;     // [2][8 warps][2 mats][NT][32 lanes]
+
+// Stage one pass of a CTA's token tile in shared memory: the activations of up to 8*NT sorted
+// rows, already in MMA B-fragment order, plus the f16 sums of x over each 32-value sub-block.
+//   s_frag [nsb][NT][8 words][8 tokens][4 lanes-of-quad] x 16 B  (lo sub-block | hi sub-block)
+//   s_sxh  [nsb][NT][8 tokens][8 sub-blocks]
+template <int NT>
+__device__ __forceinline__ void stage_token_tile(const DecodeArgs& a, uint4* s_frag, __half* s_sxh,
+                                                 int first_row, int npass, int nt_count, int tid) {
+    const int groups_per_row = a.K >> 3;   // 16-byte groups of 8 halves; a multiple of 32
+    for (int idx = tid; idx < 8 * nt_count * groups_per_row; idx += DQ_THREADS) {
+        const int i = idx / groups_per_row;          // token slot in this pass
+        const int q = idx - i * groups_per_row;      // 8-value group along K
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (i < npass) {
+            const int p = first_row + i;
+            const int64_t src = a.row_token ? a.row_token[p] : p;
+            v = *reinterpret_cast<const uint4*>(a.x + src * a.K + (size_t)q * 8);
+        }
+        const int sb = q >> 5, j = (q >> 2) & 7, u = q & 3;
+        const int nt = i >> 3, c = i & 7;
+        // elements 8u..8u+7 of sub-block j: words 2u and 2u+1 of the owning lane (j>>1),
+        // low (j even) or high (j odd) half of the 16-byte record; halves (e0,e2,e1,e3)
+        uint2* dst = reinterpret_cast<uint2*>(
+            s_frag + ((((size_t)sb * NT + nt) * 8 + 2 * u) * 8 + c) * 4 + (j >> 1)) + (j & 1);
+        dst[0] = make_uint2(__byte_perm(v.x, v.y, 0x5410), __byte_perm(v.x, v.y, 0x7632));
+        dst[2 * 32] = make_uint2(__byte_perm(v.z, v.w, 0x5410), __byte_perm(v.z, v.w, 0x7632));
+        const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 f2 = __half22float2(h2[k]);
+            s += f2.x;
+            s += f2.y;
+        }
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+        if (u == 0) s_sxh[(((size_t)sb * NT + nt) * 8 + c) * 8 + j] = __float2half_rn(s);
+    }
+}
+
+// One (super-block, matrix) unit of a 16-row tile: the lane's two rows (g, g+8), each the
+// 16-byte header and the lane's 32-byte quant chunk.
+struct UnitRegs {
+    uint4 hdr[2], qa[2], qb[2];
 };
+
+__device__ __forceinline__ void load_unit(UnitRegs& r, const uint8_t* row0, const uint8_t* row1, int t) {
+    r.hdr[0] = __ldcs(reinterpret_cast<const uint4*>(row0));
+    r.qa[0] = __ldcs(reinterpret_cast<const uint4*>(row0 + 16 + 32 * t));
+    r.qb[0] = __ldcs(reinterpret_cast<const uint4*>(row0 + 32 + 32 * t));
+    r.hdr[1] = __ldcs(reinterpret_cast<const uint4*>(row1));
+    r.qa[1] = __ldcs(reinterpret_cast<const uint4*>(row1 + 16 + 32 * t));
+    r.qb[1] = __ldcs(reinterpret_cast<const uint4*>(row1 + 32 + 32 * t));
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// The unit's contribution to y: for each of the NTC token tiles in use,
+// p = d*sum(sc*q*x) - dmin*sum(m*Sx) (rounded in that order), then y += p.  Every
+// kernel variant adds the super-blocks in ascending order with exactly these roundings, so a
+// token's result does not depend on its batch-mates or on which variant ran (the reference
+// asserts this bit for bit, nn/moe.rs:2318-2338).
+// frag_addr / sxh_addr: shared-space byte addresses of this lane's first B fragment of the
+// super-block and of its sub-block sums; NT is the tile stride of the shared layout.
+template <int NT, int NTC>
+__device__ __forceinline__ void unit_terms(const UnitRegs& r, bool upper, uint32_t sel, uint32_t frag_addr,
+                                           uint32_t sxh_addr, float (&y)[NTC][4]) {
+    LaneScales r0, r1;
+    lane_scales(r.hdr[0], upper, sel, r0);
+    lane_scales(r.hdr[1], upper, sel, r1);
+    float acc[NTC][4];
+#pragma unroll
+    for (int nt = 0; nt < NTC; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+    const uint32_t wq0[8] = {r.qa[0].x, r.qa[0].y, r.qa[0].z, r.qa[0].w, r.qb[0].x, r.qb[0].y, r.qb[0].z, r.qb[0].w};
+    const uint32_t wq1[8] = {r.qa[1].x, r.qa[1].y, r.qa[1].z, r.qa[1].w, r.qb[1].x, r.qb[1].y, r.qb[1].z, r.qb[1].w};
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        const uint32_t u0 = wq0[w], u1 = wq1[w];
+        const uint32_t a0 = hfma2_u32(nib_lo(u0), r0.sc_lo, r0.c_lo);
+        const uint32_t a1 = hfma2_u32(nib_lo(u1), r1.sc_lo, r1.c_lo);
+        const uint32_t a2 = hfma2_u32(nib_lo(u0 >> 8), r0.sc_lo, r0.c_lo);
+        const uint32_t a3 = hfma2_u32(nib_lo(u1 >> 8), r1.sc_lo, r1.c_lo);
+        const uint32_t h0 = hfma2_u32(nib_hi(u0), r0.sc_hi, r0.c_hi);
+        const uint32_t h1 = hfma2_u32(nib_hi(u1), r1.sc_hi, r1.c_hi);
+        const uint32_t h2 = hfma2_u32(nib_hi(u0 >> 8), r0.sc_hi, r0.c_hi);
+        const uint32_t h3 = hfma2_u32(nib_hi(u1 >> 8), r1.sc_hi, r1.c_hi);
+#pragma unroll
+        for (int nt = 0; nt < NTC; ++nt) {
+            const uint4 b = lds128(frag_addr + (uint32_t)((nt * 8 + w) * 32 * 16));
+            mma_16816(acc[nt], a0, a1, a2, a3, b.x, b.y);
+            mma_16816(acc[nt], h0, h1, h2, h3, b.z, b.w);
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NTC; ++nt) {
+        float mn[4];
+        mma_1688_zero(mn, r0.m_h2, r1.m_h2, lds32(sxh_addr + (uint32_t)(nt * 64 * 2)));
+        y[nt][0] = __fadd_rn(y[nt][0], __fmaf_rn(-r0.dmin, mn[0], __fmul_rn(r0.d, acc[nt][0])));
+        y[nt][1] = __fadd_rn(y[nt][1], __fmaf_rn(-r0.dmin, mn[1], __fmul_rn(r0.d, acc[nt][1])));
+        y[nt][2] = __fadd_rn(y[nt][2], __fmaf_rn(-r1.dmin, mn[2], __fmul_rn(r1.d, acc[nt][2])));
+        y[nt][3] = __fadd_rn(y[nt][3], __fmaf_rn(-r1.dmin, mn[3], __fmul_rn(r1.d, acc[nt][3])));
+    }
+}
 
 template <int NT>
 __host__ __device__ inline size_t dq_smem_bytes(int nsb) {
-    return (size_t)nsb * 8 * NT * 8 * 4 * 16 + (size_t)nsb * 8 * NT * 8 * 4 + (size_t)nsb * NT * 8 * 8 * 2 +
-           (size_t)2 * DQ_WARPS * 2 * NT * 32 * 16;
+    return (size_t)nsb * NT * 4096 + (size_t)nsb * NT * 128 + (size_t)2 * DQ_WARPS * 2 * NT * 32 * 16;
 }
 
 template <int NT, bool GATEUP>
 __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_kernel(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int nsb = a.K >> 8;
-    SmemLayout sm;
-    sm.frag = reinterpret_cast<uint4*>(smem_raw);
-    sm.negs = reinterpret_cast<float*>(sm.frag + (size_t)nsb * 8 * NT * 32);
-    sm.sxh = reinterpret_cast<__half*>(sm.negs + (size_t)nsb * 8 * NT * 8);
-    sm.part = reinterpret_cast<float4*>(sm.sxh + (size_t)nsb * NT * 64);
+    // [nsb][NT][8 words][8 tokens][4 lanes-of-quad] x 16 B: (lo sub-block 4 halves | hi sub-block 4 halves)
+    uint4* s_frag = reinterpret_cast<uint4*>(smem_raw);
+    // [nsb][NT][8 tokens][8 sub-blocks] f16 sums of x
+    __half* s_sxh = reinterpret_cast<__half*>(s_frag + (size_t)nsb * NT * 256);
+    float4* s_part = reinterpret_cast<float4*>(s_sxh + (size_t)nsb * NT * 64);
+    const uint32_t frag_base = (uint32_t)__cvta_generic_to_shared(s_frag);
+    const uint32_t sxh_base = (uint32_t)__cvta_generic_to_shared(s_sxh);
 
     const int ai = blockIdx.x / a.ctas_per_expert;
     const int cb = blockIdx.x - ai * a.ctas_per_expert;
@@ -135,6 +257,8 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_kernel(DecodeArgs a)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const bool upper = t >= 2;
+    const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
     const int KS = nsb < DQ_WARPS ? nsb : DQ_WARPS;   // K slices (warps per row tile)
     const int RG = DQ_WARPS / KS;                     // row tiles in flight per CTA
     const int ks = warp % KS, rg = warp / KS;
@@ -147,41 +271,9 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_kernel(DecodeArgs a)
 
     for (int pass0 = 0; pass0 < cnt; pass0 += 8 * NT) {
         const int npass = min(8 * NT, cnt - pass0);
+        const int nt_count = (npass + 7) >> 3;
         __syncthreads();   // previous pass finished reading the token tile
-        // ---- stage the token tile: fragments in MMA order + sub-block sums ----
-        for (int idx = tid; idx < 8 * NT * groups_per_row; idx += DQ_THREADS) {
-            int i = idx / groups_per_row;          // token slot in this pass
-            int q = idx - i * groups_per_row;      // 8-value group along K
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (i < npass) {
-                int p = base + pass0 + i;
-                int64_t src = a.row_token ? a.row_token[p] : p;
-                v = *reinterpret_cast<const uint4*>(a.x + src * a.K + (size_t)q * 8);
-            }
-            // halves e0..e7 -> [e0,e2,e1,e3 | e4,e6,e5,e7]
-            uint4 f;
-            f.x = __byte_perm(v.x, v.y, 0x5410);
-            f.y = __byte_perm(v.x, v.y, 0x7632);
-            f.z = __byte_perm(v.z, v.w, 0x5410);
-            f.w = __byte_perm(v.z, v.w, 0x7632);
-            int sb = q >> 5, j = (q >> 2) & 7, tt = q & 3;
-            int nt = i >> 3, c = i & 7;
-            sm.frag[(((size_t)(sb * 8 + j) * NT + nt) * 8 + c) * 4 + tt] = f;
-            const __half2* h2 = reinterpret_cast<const __half2*>(&v);
-            float s = 0.0f;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                float2 f2 = __half22float2(h2[u]);
-                s += f2.x;
-                s += f2.y;
-            }
-            s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-            s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-            if (tt == 0) {
-                sm.negs[((size_t)(sb * 8 + j) * NT + nt) * 8 + c] = -1024.0f * s;
-                sm.sxh[(((size_t)sb * NT + nt) * 8 + c) * 8 + j] = __float2half_rn(s);
-            }
-        }
+        stage_token_tile<NT>(a, s_frag, s_sxh, base + pass0, npass, nt_count, tid);
         __syncthreads();
 
         int it = 0;
@@ -197,79 +289,28 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_kernel(DecodeArgs a)
 
             if (warp_active && rt < rt_end) {
                 for (int sb = ks; sb < nsb; sb += KS) {
-                    // rows of this lane: (mat, half) -> weight row pointer at this super-block
-                    const uint8_t* rowp[2][2];
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                        for (int hf = 0; hf < 2; ++hf) {
-                            int row = GATEUP ? rt * 16 + g + 8 * hf : rt * 32 + 16 * mt + g + 8 * hf;
-                            const uint8_t* bank = mt == 0 ? w0e : w1e;
-                            rowp[mt][hf] = bank + (size_t)row * a.row_bytes + (size_t)sb * Q4K_BLOCK_BYTES;
-                        }
-                    uint4 hdr[2][2];
-                    uint2 qw[2][2][4];
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                        for (int hf = 0; hf < 2; ++hf) {
-                            hdr[mt][hf] = __ldcs(reinterpret_cast<const uint4*>(rowp[mt][hf]));
-#pragma unroll
-                            for (int c = 0; c < 4; ++c)
-                                qw[mt][hf][c] = __ldcs(reinterpret_cast<const uint2*>(rowp[mt][hf] + 16 + 32 * c + 8 * t));
-                        }
+                    UnitRegs un[2];
 #pragma unroll
                     for (int mt = 0; mt < 2; ++mt) {
-                        RowScales rs[2];
-                        decode_scales(hdr[mt][0], t, rs[0]);
-                        decode_scales(hdr[mt][1], t, rs[1]);
-                        // min term: (m_j) x (sum x over sub-block j)
+                        const int row = GATEUP ? rt * 16 + g : rt * 32 + 16 * mt + g;
+                        const uint8_t* row0 = (mt == 0 ? w0e : w1e) + (size_t)row * a.row_bytes +
+                                              (size_t)sb * Q4K_BLOCK_BYTES;
+                        load_unit(un[mt], row0, row0 + (size_t)8 * a.row_bytes, t);
+                    }
+                    const uint32_t frag_addr = frag_base + (uint32_t)(((sb * NT * 64 + g) * 4 + t) * 16);
+                    const uint32_t sxh_addr = sxh_base + (uint32_t)((((sb * NT * 8 + g) * 8) + 2 * t) * 2);
 #pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            float mn[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                            uint32_t b = *reinterpret_cast<const uint32_t*>(
-                                sm.sxh + (((size_t)sb * NT + nt) * 8 + g) * 8 + 2 * t);
-                            mma_1688(mn, rs[0].m_h2, rs[1].m_h2, b);
-                            y[mt][nt][0] -= rs[0].dmin * mn[0];
-                            y[mt][nt][1] -= rs[0].dmin * mn[1];
-                            y[mt][nt][2] -= rs[1].dmin * mn[2];
-                            y[mt][nt][3] -= rs[1].dmin * mn[3];
-                        }
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const uint32_t w00 = qw[mt][0][c].x, w01 = qw[mt][0][c].y;   // row g
-                            const uint32_t w10 = qw[mt][1][c].x, w11 = qw[mt][1][c].y;   // row g+8
-#pragma unroll
-                            for (int hi = 0; hi < 2; ++hi) {
-                                const int j = 2 * c + hi;
-                                uint32_t a0, a1, a2, a3, a4, a5, a6, a7;
-                                if (hi == 0) {
-                                    a0 = nib_lo(w00); a1 = nib_lo(w10); a2 = nib_lo(w00 >> 8); a3 = nib_lo(w10 >> 8);
-                                    a4 = nib_lo(w01); a5 = nib_lo(w11); a6 = nib_lo(w01 >> 8); a7 = nib_lo(w11 >> 8);
-                                } else {
-                                    a0 = nib_hi(w00); a1 = nib_hi(w10); a2 = nib_hi(w00 >> 8); a3 = nib_hi(w10 >> 8);
-                                    a4 = nib_hi(w01); a5 = nib_hi(w11); a6 = nib_hi(w01 >> 8); a7 = nib_hi(w11 >> 8);
-                                }
-#pragma unroll
-                                for (int nt = 0; nt < NT; ++nt) {
-                                    const size_t rec = ((size_t)(sb * 8 + j) * NT + nt) * 8;
-                                    const uint4 b = sm.frag[(rec + g) * 4 + t];
-                                    const float2 ns = *reinterpret_cast<const float2*>(sm.negs + rec + 2 * t);
-                                    float acc[4] = {ns.x, ns.y, ns.x, ns.y};
-                                    mma_16816(acc, a0, a1, a2, a3, b.x, b.y);
-                                    mma_16816(acc, a4, a5, a6, a7, b.z, b.w);
-                                    y[mt][nt][0] = fmaf(rs[0].dsc[j], acc[0], y[mt][nt][0]);
-                                    y[mt][nt][1] = fmaf(rs[0].dsc[j], acc[1], y[mt][nt][1]);
-                                    y[mt][nt][2] = fmaf(rs[1].dsc[j], acc[2], y[mt][nt][2]);
-                                    y[mt][nt][3] = fmaf(rs[1].dsc[j], acc[3], y[mt][nt][3]);
-                                }
-                            }
-                        }
+                    for (int mt = 0; mt < 2; ++mt) {
+                        if (NT == 1 || nt_count == 1)
+                            unit_terms<NT, 1>(un[mt], upper, sel, frag_addr, sxh_addr,
+                                              *reinterpret_cast<float(*)[1][4]>(&y[mt][0][0]));
+                        else
+                            unit_terms<NT, NT>(un[mt], upper, sel, frag_addr, sxh_addr, y[mt]);
                     }
                 }
             }
             // ---- fold the K slices and write out ----
-            float4* part = sm.part + (size_t)(it & 1) * DQ_WARPS * 2 * NT * 32;
+            float4* part = s_part + (size_t)(it & 1) * DQ_WARPS * 2 * NT * 32;
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -279,26 +320,26 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_kernel(DecodeArgs a)
             __syncthreads();
             const float* pf = reinterpret_cast<const float*>(part);
             for (int o = tid; o < RG * NT * 128; o += DQ_THREADS) {
-                int rgo = o / (NT * 128);
-                int rem = o - rgo * NT * 128;
-                int nt = rem >> 7;
-                int li = rem & 127;          // lane*4 + i
-                int ln = li >> 2, i = li & 3;
-                int rto = rt0 + rgo;
+                const int rgo = o / (NT * 128);
+                const int rem = o - rgo * NT * 128;
+                const int nt = rem >> 7;
+                const int li = rem & 127;          // lane*4 + i
+                const int ln = li >> 2, i = li & 3;
+                const int rto = rt0 + rgo;
                 if (rto >= rt_end) continue;
-                int col = (ln & 3) * 2 + (i & 1);          // token within the n-tile
-                int row = (ln >> 2) + ((i >> 1) << 3);     // weight row within the 16-row tile
-                int slot = nt * 8 + col;
+                const int col = (ln & 3) * 2 + (i & 1);          // token within the n-tile
+                const int row = (ln >> 2) + ((i >> 1) << 3);     // weight row within the 16-row tile
+                const int slot = nt * 8 + col;
                 if (slot >= npass) continue;
-                float s0 = 0.0f, s1 = 0.0f;
+                float s0 = 0.0f, s1 = 0.0f;     // ascending super-block order (see unit_terms)
                 for (int w = 0; w < KS; ++w) {
-                    int wp = rgo * KS + w;
-                    s0 += pf[(((size_t)(wp * 2 + 0) * NT + nt) * 32 + ln) * 4 + i];
-                    s1 += pf[(((size_t)(wp * 2 + 1) * NT + nt) * 32 + ln) * 4 + i];
+                    const int wp = rgo * KS + w;
+                    s0 = __fadd_rn(s0, pf[(((size_t)(wp * 2 + 0) * NT + nt) * 32 + ln) * 4 + i]);
+                    s1 = __fadd_rn(s1, pf[(((size_t)(wp * 2 + 1) * NT + nt) * 32 + ln) * 4 + i]);
                 }
-                size_t orow = (size_t)(base + pass0 + slot);
+                const size_t orow = (size_t)(base + pass0 + slot);
                 if (GATEUP) {
-                    float v = (s0 / (1.0f + expf(-s0))) * s1;
+                    const float v = (s0 / (1.0f + expf(-s0))) * s1;
                     reinterpret_cast<__half*>(a.out)[orow * a.ld_out + rto * 16 + row] = __float2half_rn(v);
                 } else {
                     float* o32 = reinterpret_cast<float*>(a.out);
@@ -310,13 +351,106 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_kernel(DecodeArgs a)
     }
 }
 
-// active-expert list: experts with at least one row, ascending id
-__global__ void active_list_kernel(const int32_t* counts, int E, int32_t* active, int32_t* n_active) {
-    if (threadIdx.x == 0 && blockIdx.x == 0) {
-        int n = 0;
-        for (int e = 0; e < E; ++e)
-            if (counts[e] > 0) active[n++] = e;
-        *n_active = n;
+
+// Row-tile loop of the streaming variant for NTC token tiles in use (a compile-time count, so
+// the inner loop carries no per-tile branches).
+template <int NT, int NTC, bool GATEUP>
+__device__ __forceinline__ void stream_rows(const DecodeArgs& a, uint32_t frag_base, uint32_t sxh_base,
+                                            const uint8_t* w0e, const uint8_t* w1e, int rt_first, int rt_end,
+                                            int nsb, int g, int t, bool upper, uint32_t sel, int first_row,
+                                            int npass) {
+    const size_t half_tile = (size_t)8 * a.row_bytes;
+    for (int rt = rt_first; rt < rt_end; rt += DQ_WARPS) {
+        // row g of matrix 0 / matrix 1 at super-block 0
+        const uint8_t* r0p = w0e + (size_t)(GATEUP ? rt * 16 + g : rt * 32 + g) * a.row_bytes;
+        const uint8_t* r1p = w1e + (size_t)(GATEUP ? rt * 16 + g : rt * 32 + 16 + g) * a.row_bytes;
+        float y[2][NTC][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NTC; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) y[mt][nt][i] = 0.0f;
+        UnitRegs ua, ub;
+        load_unit(ua, r0p, r0p + half_tile, t);
+        uint32_t frag_addr = frag_base + (uint32_t)((g * 4 + t) * 16);
+        uint32_t sxh_addr = sxh_base + (uint32_t)((g * 8 + 2 * t) * 2);
+        for (int sb = 0; sb < nsb; ++sb) {
+            load_unit(ub, r1p, r1p + half_tile, t);
+            r1p += Q4K_BLOCK_BYTES;
+            r0p += Q4K_BLOCK_BYTES;
+            unit_terms<NT, NTC>(ua, upper, sel, frag_addr, sxh_addr, y[0]);
+            if (sb + 1 < nsb) load_unit(ua, r0p, r0p + half_tile, t);
+            unit_terms<NT, NTC>(ub, upper, sel, frag_addr, sxh_addr, y[1]);
+            frag_addr += (uint32_t)(NT * 64 * 4 * 16);
+            sxh_addr += (uint32_t)(NT * 8 * 8 * 2);
+        }
+        // epilogue from registers: lane (g, t) holds rows g, g+8 x tokens 2t, 2t+1
+#pragma unroll
+        for (int nt = 0; nt < NTC; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int slot = nt * 8 + 2 * t + (i & 1);
+                const int row = g + ((i >> 1) << 3);
+                if (slot < npass) {
+                    const size_t orow = (size_t)(first_row + slot);
+                    if (GATEUP) {
+                        const float s0 = y[0][nt][i], s1 = y[1][nt][i];
+                        const float v = (s0 / (1.0f + expf(-s0))) * s1;
+                        reinterpret_cast<__half*>(a.out)[orow * a.ld_out + rt * 16 + row] = __float2half_rn(v);
+                    } else {
+                        float* o32 = reinterpret_cast<float*>(a.out);
+                        o32[orow * a.ld_out + rt * 32 + row] = y[0][nt][i];
+                        o32[orow * a.ld_out + rt * 32 + 16 + row] = y[1][nt][i];
+                    }
+                }
+            }
+    }
+}
+
+
+// Streaming variant for large work: one warp owns a 16-row tile over ALL of K, so nothing is
+// folded across warps and the epilogue runs from registers.  The (super-block, matrix) units are
+// software pipelined through two register buffers: the loads of unit u+1 are in flight while
+// unit u is decoded and multiplied.
+template <int NT, bool GATEUP>
+__global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_stream_kernel(DecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int nsb = a.K >> 8;
+    uint4* s_frag = reinterpret_cast<uint4*>(smem_raw);
+    __half* s_sxh = reinterpret_cast<__half*>(s_frag + (size_t)nsb * NT * 256);
+    const uint32_t frag_base = (uint32_t)__cvta_generic_to_shared(s_frag);
+    const uint32_t sxh_base = (uint32_t)__cvta_generic_to_shared(s_sxh);
+
+    const int ai = blockIdx.x / a.ctas_per_expert;
+    const int cb = blockIdx.x - ai * a.ctas_per_expert;
+    if (ai >= *a.n_active) return;
+    const int e = a.active[ai];
+    const int cnt = a.counts[e];
+    const int base = a.offsets[e];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const bool upper = t >= 2;
+    const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
+    const int rt_begin = cb * a.rb;
+    const int rt_end = min(a.n_rt, rt_begin + a.rb);
+    const uint8_t* w0e = a.w0 + (size_t)e * a.expert_stride;
+    const uint8_t* w1e = GATEUP ? a.w1 + (size_t)e * a.expert_stride : w0e;
+
+    for (int pass0 = 0; pass0 < cnt; pass0 += 8 * NT) {
+        const int npass = min(8 * NT, cnt - pass0);
+        const int nt_count = (npass + 7) >> 3;
+        __syncthreads();
+        stage_token_tile<NT>(a, s_frag, s_sxh, base + pass0, npass, nt_count, tid);
+        __syncthreads();
+
+        if (NT == 1 || nt_count == 1)
+            stream_rows<NT, 1, GATEUP>(a, frag_base, sxh_base, w0e, w1e, rt_begin + warp, rt_end, nsb, g, t, upper,
+                                       sel, base + pass0, npass);
+        else
+            stream_rows<NT, NT, GATEUP>(a, frag_base, sxh_base, w0e, w1e, rt_begin + warp, rt_end, nsb, g, t, upper,
+                                        sel, base + pass0, npass);
     }
 }
 
@@ -326,38 +460,51 @@ bool decode_q4k_supported(const MummuMoeConfig& c, int64_t tokens) {
 }
 
 template <int NT, bool GATEUP>
-static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, cudaStream_t s, const char* name) {
-    size_t smem = dq_smem_bytes<NT>(a.K >> 8);
+static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream, cudaStream_t s,
+                      const char* name) {
+    const int nsb = a.K >> 8;
+    size_t smem = dq_smem_bytes<NT>(nsb);
+    if (stream) smem = (size_t)nsb * NT * 4096 + (size_t)nsb * NT * 128;
     if (smem > 200 * 1024) {
         set_error("decode_q4k: %zu bytes of shared memory needed for K=%d", smem, a.K);
         return MUMMU_ERR_UNSUPPORTED;
     }
-    MUMMU_CUDA_TRY(cudaFuncSetAttribute(decode_q4k_kernel<NT, GATEUP>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     LaunchScope scope(m, s, name);
-    decode_q4k_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a);
+    if (stream) {
+        MUMMU_CUDA_TRY(allow_big_smem(decode_q4k_stream_kernel<NT, GATEUP>, m->cfg.device));
+        decode_q4k_stream_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a);
+    } else {
+        MUMMU_CUDA_TRY(allow_big_smem(decode_q4k_kernel<NT, GATEUP>, m->cfg.device));
+        decode_q4k_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a);
+    }
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }
 
-static int pick_rb(int n_rt, int rg, int experts_est) {
-    // aim for ~4 CTAs per SM over the active experts, but keep each CTA's weight stream long
-    int rb = rg;
-    while (rb * 2 <= n_rt && (int64_t)experts_est * (n_rt / (rb * 2)) >= 148 * 3) rb *= 2;
-    return rb;
+// Work split for one projection.  Streaming (one warp per row tile over all of K) needs enough
+// row tiles to fill the GPU: experts * n_rt warp tasks against 148 SMs x 16 resident warps.
+// Otherwise the split-K variant spreads each row tile over up to 8 warps.
+static void plan(DecodeArgs& a, int experts_est, bool& stream) {
+    const int nsb = a.K >> 8;
+    stream = (int64_t)experts_est * a.n_rt >= 148 * 16;
+    if (stream) {
+        a.rb = DQ_WARPS;                       // one row tile per warp
+        while (a.rb * 2 <= a.n_rt && (int64_t)experts_est * (a.n_rt / (a.rb * 2)) >= 148 * 3) a.rb *= 2;
+    } else {
+        const int ks = nsb < DQ_WARPS ? nsb : DQ_WARPS, rg = DQ_WARPS / ks;
+        a.rb = rg;
+        while (a.rb * 2 <= a.n_rt && (int64_t)experts_est * (a.n_rt / (a.rb * 2)) >= 148 * 3) a.rb *= 2;
+    }
+    a.ctas_per_expert = (a.n_rt + a.rb - 1) / a.rb;
 }
 
 int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cudaStream_t s) {
     const MummuMoeConfig& c = m->cfg;
     int32_t* active = m->active;
     int32_t* n_active = m->n_active;
-    {
-        LaunchScope scope(m, s, "active_list");
-        active_list_kernel<<<1, 32, 0, s>>>(m->counts, c.experts, active, n_active);
-        MUMMU_CUDA_TRY(cudaGetLastError());
-    }
     int experts_est = (int)std::min<int64_t>(c.experts, tokens * top_k);
-    const bool nt2 = tokens > 8;
+    bool nt2 = tokens > 8;
+    if (const char* env = getenv("MUMMU_CUDA_DECODE_NT")) nt2 = nt2 && atoi(env) >= 2;
 
     DecodeArgs g{};
     g.x = (const __half*)x;
@@ -372,15 +519,12 @@ int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cud
     g.expert_stride = (size_t)g.row_bytes * c.inter;
     g.K = c.hidden;
     g.n_rt = c.inter / 16;
-    {
-        int nsb = g.K >> 8, ks = nsb < DQ_WARPS ? nsb : DQ_WARPS, rg = DQ_WARPS / ks;
-        g.rb = pick_rb(g.n_rt, rg, experts_est);
-    }
-    g.ctas_per_expert = (g.n_rt + g.rb - 1) / g.rb;
+    bool g_stream;
+    plan(g, experts_est, g_stream);
     g.ld_out = c.inter;
     g.out = m->hact;
-    int rc = nt2 ? launch_one<2, true>(m, g, experts_est, s, "q4k_gate_up")
-                 : launch_one<1, true>(m, g, experts_est, s, "q4k_gate_up");
+    int rc = nt2 ? launch_one<2, true>(m, g, experts_est, g_stream, s, "q4k_gate_up")
+                 : launch_one<1, true>(m, g, experts_est, g_stream, s, "q4k_gate_up");
     if (rc) return rc;
 
     DecodeArgs d{};
@@ -396,15 +540,12 @@ int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cud
     d.expert_stride = (size_t)d.row_bytes * c.hidden;
     d.K = c.inter;
     d.n_rt = c.hidden / 32;
-    {
-        int nsb = d.K >> 8, ks = nsb < DQ_WARPS ? nsb : DQ_WARPS, rg = DQ_WARPS / ks;
-        d.rb = pick_rb(d.n_rt, rg, experts_est);
-    }
-    d.ctas_per_expert = (d.n_rt + d.rb - 1) / d.rb;
+    bool d_stream;
+    plan(d, experts_est, d_stream);
     d.ld_out = c.hidden;
     d.out = m->ys;
-    return nt2 ? launch_one<2, false>(m, d, experts_est, s, "q4k_down")
-               : launch_one<1, false>(m, d, experts_est, s, "q4k_down");
+    return nt2 ? launch_one<2, false>(m, d, experts_est, d_stream, s, "q4k_down")
+               : launch_one<1, false>(m, d, experts_est, d_stream, s, "q4k_down");
 }
 
 }  // namespace mummu

@@ -110,6 +110,7 @@ __device__ void warp_softmax_topk(const RouterArgs& a, int t, float* sm_v, float
     }
     __syncwarp();
     float total = 0.0f;
+#pragma unroll 8
     for (int e = 0; e < a.E; ++e) total = __fadd_rn(total, sm_v[e]);
 #pragma unroll
     for (int i = 0; i < R_MAXV; ++i) {
@@ -176,15 +177,40 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
     const int t0 = blockIdx.y * TT;
     const TX* x = reinterpret_cast<const TX*>(a.x);
 
-    for (int idx = tid; idx < H8 * R_ES; idx += R_THREADS) {
-        int i = idx >> 3, el = idx & 7;
-        int e = e0 + el;
-        Ws[idx] = e < E ? a.w[(size_t)i * E + e] : 0.0f;
+    if ((E & 3) == 0 && e0 + R_ES <= E) {
+        // 8 experts of one row = two aligned float4
+        const float4* w4 = reinterpret_cast<const float4*>(a.w);
+        float4* Ws4 = reinterpret_cast<float4*>(Ws);
+        const int e4 = E >> 2, o4 = e0 >> 2;
+#pragma unroll 8
+        for (int idx = tid; idx < H8 * 2; idx += R_THREADS)
+            Ws4[idx] = __ldg(w4 + (size_t)(idx >> 1) * e4 + o4 + (idx & 1));
+    } else {
+        for (int idx = tid; idx < H8 * R_ES; idx += R_THREADS) {
+            int i = idx >> 3, el = idx & 7;
+            int e = e0 + el;
+            Ws[idx] = e < E ? a.w[(size_t)i * E + e] : 0.0f;
+        }
     }
-    for (int idx = tid; idx < TT * H; idx += R_THREADS) {
-        int tt = idx / H, h = idx - tt * H;
-        int t = t0 + tt;
-        xs[idx] = t < a.T ? to_f32(x[(size_t)t * H + h]) : 0.0f;
+    if (sizeof(TX) == 2 && (H & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const int groups = H >> 3;
+#pragma unroll 4
+        for (int idx = tid; idx < TT * groups; idx += R_THREADS) {
+            int tt = idx / groups, q = idx - tt * groups;
+            int t = t0 + tt;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (t < a.T) v = *reinterpret_cast<const uint4*>(x + (size_t)t * H + (size_t)q * 8);
+            const TX* hv = reinterpret_cast<const TX*>(&v);
+            float* dst = xs + (size_t)tt * H + (size_t)q * 8;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) dst[u] = to_f32(hv[u]);
+        }
+    } else {
+        for (int idx = tid; idx < TT * H; idx += R_THREADS) {
+            int tt = idx / H, h = idx - tt * H;
+            int t = t0 + tt;
+            xs[idx] = t < a.T ? to_f32(x[(size_t)t * H + h]) : 0.0f;
+        }
     }
     __syncthreads();
 
@@ -259,18 +285,15 @@ static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
     LaunchScope scope(m, s, "router");
     switch (tpt) {
         case 4:
-            MUMMU_CUDA_TRY(cudaFuncSetAttribute(router_kernel<TX, 4>,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 4>, m->cfg.device));
             router_kernel<TX, 4><<<grid, R_THREADS, smem, s>>>(a);
             break;
         case 2:
-            MUMMU_CUDA_TRY(cudaFuncSetAttribute(router_kernel<TX, 2>,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 2>, m->cfg.device));
             router_kernel<TX, 2><<<grid, R_THREADS, smem, s>>>(a);
             break;
         default:
-            MUMMU_CUDA_TRY(cudaFuncSetAttribute(router_kernel<TX, 1>,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 1>, m->cfg.device));
             router_kernel<TX, 1><<<grid, R_THREADS, smem, s>>>(a);
             break;
     }
@@ -358,26 +381,45 @@ constexpr int P_THREADS = 1024;
 __global__ void __launch_bounds__(P_THREADS) permute_kernel(const int32_t* ids, int64_t n, int top_k,
                                                             int E, const int32_t* counts,
                                                             int32_t* offsets, int32_t* row_token,
-                                                            int32_t* pos) {
+                                                            int32_t* pos, int32_t* active,
+                                                            int32_t* n_active) {
     __shared__ int warp_sums[P_THREADS / 32];
+    __shared__ int warp_nz[P_THREADS / 32];
     __shared__ int base_s;
     const int e = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // exclusive prefix of counts up to e
-    int part = 0;
-    for (int i = tid; i < e; i += P_THREADS) part += counts[i];
+    int part = 0, nz = 0;
+    for (int i = tid; i < e; i += P_THREADS) {
+        int c = counts[i];
+        part += c;
+        nz += c > 0;
+    }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, off);
-    if (lane == 0) warp_sums[warp] = part;
+    for (int off = 16; off > 0; off >>= 1) {
+        part += __shfl_xor_sync(0xFFFFFFFFu, part, off);
+        nz += __shfl_xor_sync(0xFFFFFFFFu, nz, off);
+    }
+    if (lane == 0) {
+        warp_sums[warp] = part;
+        warp_nz[warp] = nz;
+    }
     __syncthreads();
     if (tid == 0) {
-        int b = 0;
-        for (int w = 0; w < P_THREADS / 32; ++w) b += warp_sums[w];
+        int b = 0, z = 0;
+        for (int w = 0; w < P_THREADS / 32; ++w) {
+            b += warp_sums[w];
+            z += warp_nz[w];
+        }
         base_s = b;
+        const int mine = counts[e];
         if (offsets) {
             offsets[e] = b;
-            if (e == E - 1) offsets[E] = b + counts[e];
+            if (e == E - 1) offsets[E] = b + mine;
         }
+        // experts with rows, ascending id: this expert's rank among them
+        if (active && mine > 0) active[z] = e;
+        if (n_active && e == E - 1) *n_active = z + (mine > 0);
     }
     __syncthreads();
     int running = base_s;
@@ -410,7 +452,8 @@ int launch_permute(MummuMoe* m, const int32_t* ids, int64_t tokens, int top_k,
                    cudaStream_t s) {
     LaunchScope scope(m, s, "permute");
     permute_kernel<<<m->cfg.experts, P_THREADS, 0, s>>>(ids, tokens * top_k, top_k, m->cfg.experts,
-                                                        counts, offsets, row_token, pos);
+                                                        counts, offsets, row_token, pos, m->active,
+                                                        m->n_active);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }
@@ -436,11 +479,16 @@ __global__ void __launch_bounds__(256) combine_kernel(const TY* ys, const int32_
         s_w[rank] = w[t * top_k + r];
     }
     __syncthreads();
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    for (int h = blockIdx.y * blockDim.x + threadIdx.x; h < H; h += gridDim.y * blockDim.x) {
         float acc = 0.0f;
-        for (int r = 0; r < top_k; ++r) {
-            float v = to_f32(ys[(size_t)s_pos[r] * H + h]);
-            acc = __fadd_rn(acc, __fmul_rn(s_w[r], v));
+        for (int r0 = 0; r0 < top_k; r0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)      // independent loads first, then the ordered sum
+                v[u] = r0 + u < top_k ? to_f32(ys[(size_t)s_pos[r0 + u] * H + h]) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (r0 + u < top_k) acc = __fadd_rn(acc, __fmul_rn(s_w[r0 + u], v[u]));
         }
         out[t * H + h] = from_f32<TO>(acc);
     }
@@ -452,16 +500,17 @@ static int launch_combine_y(MummuMoe* m, const void* ys, const int32_t* ids, con
                             cudaStream_t s) {
     size_t smem = (size_t)top_k * 8;
     const int H = m->cfg.hidden;
+    const dim3 grid((unsigned)tokens, tokens < 512 ? (unsigned)((H + 255) / 256) : 1u);
     LaunchScope scope(m, s, "combine");
     switch (m->cfg.act_dtype) {
         case MUMMU_F32:
-            combine_kernel<TY, float><<<(unsigned)tokens, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
+            combine_kernel<TY, float><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
             break;
         case MUMMU_F16:
-            combine_kernel<TY, __half><<<(unsigned)tokens, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__half*)out);
+            combine_kernel<TY, __half><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__half*)out);
             break;
         case MUMMU_BF16:
-            combine_kernel<TY, __nv_bfloat16><<<(unsigned)tokens, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__nv_bfloat16*)out);
+            combine_kernel<TY, __nv_bfloat16><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__nv_bfloat16*)out);
             break;
     }
     MUMMU_CUDA_TRY(cudaGetLastError());

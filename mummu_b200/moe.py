@@ -58,8 +58,10 @@ def _torch_dtype_code(t) -> int:
 
 
 def _torch_stream():
+    """The current torch stream as a cudaStream_t.  torch's default stream has handle 0, which the
+    C ABI reads as "the handle's own stream", so it is passed as cudaStreamLegacy (0x1)."""
     import torch
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream or 1)
 
 
 @dataclass

@@ -175,6 +175,33 @@ int32_t mummu_q4k_quantize(const float* src, void* dst, int64_t n_superblocks, i
 int32_t mummu_q4k_dequantize(const void* src, float* dst, int64_t n_superblocks, int32_t device,
                              void* stream);
 
+/* -------- for callers that cannot allocate device memory ------------------------------------ */
+
+/* The router of mummu_moe_route as a free function that allocates nothing and needs no handle.
+ * It has no counterpart in the reference.  It exists for code that runs where device allocation is
+ * off limits: inside a real-time or latency-critical serving loop that has fixed its memory plan,
+ * under a framework that owns every byte of device memory and forbids cudaMalloc from plug-ins,
+ * or in a process that has already committed the GPU's memory to weights and KV cache.
+ *
+ * All device pointers are the caller's: x [tokens, hidden] of act_dtype, router_w [hidden,
+ * experts] f32 (the order mummu_moe_set_router stores), bias NULL or [experts] f32,
+ * ids_out / w_out [tokens, top_k].  Results equal mummu_moe_route's bit for bit.  The work is
+ * queued on `stream` (a cudaStream_t; 0 is the default stream) and the call does not wait.
+ *
+ * The kernel's scratch (the logits it hands from its expert-slice blocks to the block that
+ * selects, plus a few counters; about 1 MiB) is a fixed array inside the library's device image,
+ * held by every GPU that loads the library until the process exits.  Limits, refused with
+ * MUMMU_ERR_CONTRACT and a message: tokens <= 1024, tokens * experts <= 262144, experts <= 256.
+ * The first call on a device looks the array's address up (cudaGetSymbolAddress); make that first
+ * call before any stream capture.  All calls on a device share the one array: two calls whose
+ * kernels may overlap on the GPU (different streams, no dependency) race on it and give wrong
+ * routing — order them.  A non-finite logit is not reported here (there is no handle to carry
+ * the status): that token gets experts 0..top_k-1 with zero weights. */
+int32_t mummu_moe_route_noalloc(const void* x, int32_t act_dtype, const float* router_w,
+                                const float* bias, int32_t tokens, int32_t hidden,
+                                int32_t experts, int32_t top_k, int32_t norm_topk_prob,
+                                int32_t* ids_out, float* w_out, int32_t device, void* stream);
+
 const char* mummu_cuda_last_error(void);
 const char* mummu_cuda_version(void);
 

@@ -51,6 +51,9 @@ SYMBOLS = {
     "mummu_moe_launch_count": (C.c_int64, [C.c_void_p]),
     "mummu_q4k_quantize": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "mummu_q4k_dequantize": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
+    "mummu_moe_route_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
+                                            C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                            C.c_void_p, C.c_int32, C.c_void_p]),
     "mummu_cuda_last_error": (C.c_char_p, []),
     "mummu_cuda_version": (C.c_char_p, []),
 }

@@ -854,4 +854,123 @@ int launch_widen(const void* src, int dtype, float* dst, int64_t n, cudaStream_t
     return MUMMU_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Router for callers that must not allocate (mummu_moe_route_noalloc)
+// ---------------------------------------------------------------------------------------------
+// The router kernel needs scratch beyond its inputs and outputs: the [tokens, experts] logits that
+// its expert-slice blocks hand to the block that selects, one arrival counter per token tile, and a
+// status word.  Here that scratch is a fixed array in the library's device image, so the call
+// allocates nothing.  Every GPU that loads the library holds the array (about 1 MiB) until exit.
+constexpr int NOALLOC_MAX_TOKENS = 1024;
+constexpr int NOALLOC_MAX_LOGITS = 256 * 1024;                 // tokens * experts
+constexpr int NOALLOC_TILES = NOALLOC_MAX_TOKENS / 4 + 8;
+
+struct NoAllocScratch {
+    float logits[NOALLOC_MAX_LOGITS];
+    int32_t tile_done[NOALLOC_TILES];
+    int32_t status;
+};
+
+static __device__ __align__(256) unsigned char g_route_scratch[sizeof(NoAllocScratch)];
+
+// In host code `g_route_scratch` is only a stand-in for the symbol, never a device address: the
+// address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that
+// device current.
+static NoAllocScratch* route_scratch_for(int device, cudaError_t* err) {
+    static std::mutex mu;
+    static NoAllocScratch* ptrs[64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    *err = cudaSuccess;
+    if (device < 0 || device >= 64) {
+        *err = cudaErrorInvalidDevice;
+        return nullptr;
+    }
+    if (!ptrs[device]) {
+        void* p = nullptr;
+        *err = cudaGetSymbolAddress(&p, g_route_scratch);
+        if (*err != cudaSuccess) return nullptr;
+        ptrs[device] = static_cast<NoAllocScratch*>(p);
+    }
+    return ptrs[device];
+}
+
+template <typename TX>
+static int route_noalloc_launch(RouterArgs& a, int device, cudaStream_t s) {
+    const size_t smem = router_smem(a.H, a.E, a.k, 4);
+    if (smem > 220 * 1024) {
+        set_error("mummu_moe_route_noalloc: hidden %d too wide for the shared-memory staged router", a.H);
+        return MUMMU_ERR_UNSUPPORTED;
+    }
+    MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 1>, device));
+    dim3 grid((a.E + R_ES - 1) / R_ES, (a.T + 3) / 4);
+    router_kernel<TX, 1><<<grid, R_THREADS, smem, s>>>(a);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
 }  // namespace mummu
+
+extern "C" int32_t mummu_moe_route_noalloc(const void* x, int32_t act_dtype, const float* router_w,
+                                           const float* bias, int32_t tokens, int32_t hidden,
+                                           int32_t experts, int32_t top_k, int32_t norm_topk_prob,
+                                           int32_t* ids_out, float* w_out, int32_t device, void* stream) {
+    using namespace mummu;
+    MUMMU_REQUIRE(tokens >= 0, "mummu_moe_route_noalloc: negative token count %d", tokens);
+    MUMMU_REQUIRE(hidden >= 1 && experts >= 2 && experts <= 32 * R_MAXV,
+                  "mummu_moe_route_noalloc: hidden %d, experts %d (2..=%d)", hidden, experts, 32 * R_MAXV);
+    MUMMU_REQUIRE(top_k >= 1 && top_k <= experts,
+                  "MoE forward: top_k (%d) must be in 1..=num_experts (%d)", top_k, experts);
+    MUMMU_REQUIRE(tokens <= NOALLOC_MAX_TOKENS && (int64_t)tokens * experts <= NOALLOC_MAX_LOGITS,
+                  "mummu_moe_route_noalloc: %d tokens x %d experts exceed the fixed scratch "
+                  "(at most %d tokens and %d tokens*experts); use mummu_moe_route",
+                  tokens, experts, NOALLOC_MAX_TOKENS, NOALLOC_MAX_LOGITS);
+    if (tokens == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(x && router_w && ids_out && w_out, "mummu_moe_route_noalloc: null pointer");
+    int prev = -1;
+    MUMMU_CUDA_TRY(cudaGetDevice(&prev));
+    if (prev != device) MUMMU_CUDA_TRY(cudaSetDevice(device));
+    int rc = MUMMU_OK;
+    do {
+        cudaError_t err;
+        NoAllocScratch* sc = route_scratch_for(device, &err);
+        if (!sc) {
+            set_error("mummu_moe_route_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+            rc = MUMMU_ERR_DEVICE;
+            break;
+        }
+        cudaStream_t s = (cudaStream_t)stream;
+        // the array keeps the previous call's contents: counters and status must start at zero
+        err = cudaMemsetAsync(sc->tile_done, 0, sizeof(sc->tile_done) + sizeof(sc->status), s);
+        if (err != cudaSuccess) {
+            set_error("mummu_moe_route_noalloc: cudaMemsetAsync: %s", cudaGetErrorString(err));
+            rc = MUMMU_ERR_DEVICE;
+            break;
+        }
+        RouterArgs a;
+        a.x = x;
+        a.w = router_w;
+        a.bias = bias;
+        a.logits = sc->logits;
+        a.tile_done = sc->tile_done;
+        a.ids = ids_out;
+        a.wts = w_out;
+        a.counts = nullptr;
+        a.hits = nullptr;
+        a.status = &sc->status;
+        a.T = tokens;
+        a.H = hidden;
+        a.E = experts;
+        a.k = top_k;
+        a.norm = norm_topk_prob;
+        switch (act_dtype) {
+            case MUMMU_F32: rc = route_noalloc_launch<float>(a, device, s); break;
+            case MUMMU_F16: rc = route_noalloc_launch<__half>(a, device, s); break;
+            case MUMMU_BF16: rc = route_noalloc_launch<__nv_bfloat16>(a, device, s); break;
+            default:
+                set_error("mummu_moe_route_noalloc: activation dtype %d is not F32, F16 or BF16", act_dtype);
+                rc = MUMMU_ERR_CONTRACT;
+        }
+    } while (0);
+    if (prev != device) cudaSetDevice(prev);
+    return rc;
+}

@@ -366,6 +366,114 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------------
+# prefill workload: T=4096, bf16, Zipf-skewed routing, tensor-core grouped GEMMs
+# ----------------------------------------------------------------------------------------------
+def measured_peak_tflops():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+        except Exception:
+            pass
+    return 1590.0, 1400.0, "fallback"
+
+
+def run_prefill(args, rank: int, world: int, local_rank: int):
+    import torch
+    from mummu_b200 import _lib as L, moe, synth
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    stream = torch.cuda.Stream(device)
+    torch.cuda.set_stream(stream)
+    T = args.tokens if args.tokens != 64 else 4096
+    NL = min(args.layers, 4)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4321 + rank)
+    layers = []
+    for l in range(NL):
+        m = moe.SparseMoeConfig(H, I, E, K).init(device=device.index, act_dtype=L.BF16, weight_dtype=L.BF16,
+                                                 max_tokens=T)
+        m._router_np = (torch.randn(H, E, generator=gen, device=device) * 0.02).cpu().numpy()
+        m.set_router(m._router_np)
+        for which, shape in ((L.BANK_GATE, (E, I, H)), (L.BANK_UP, (E, I, H)), (L.BANK_DOWN, (E, H, I))):
+            m.set_bank(which, (torch.randn(shape, generator=gen, device=device) * 0.02).to(torch.bfloat16))
+        layers.append(m)
+    xs = [torch.randn(T, H, generator=gen, device=device).to(torch.bfloat16) for _ in range(NL)]
+    # router-logit bias b_e = -alpha * 1.1 * ln(rank_e): alpha calibrated so hottest / mean load ~ 8
+    alpha, ratio = None, None
+    for cand in (0.5, 1.0, 1.5, 2.0, 2.5, 3.0, 4.0, 6.0):
+        bias = synth.zipf_router_bias(E, cand)
+        layers[0].set_router(layers[0]._router_np, bias=bias)
+        ids, _ = layers[0].route_flat(xs[0], K, False)
+        load = torch.bincount(ids.reshape(-1).long(), minlength=E).float()
+        r = float(load.max() / load.mean())
+        alpha, ratio = cand, r
+        if r >= 7.6:
+            break
+    for m in layers:
+        m.set_router(m._router_np, bias=synth.zipf_router_bias(E, alpha))
+    torch.cuda.synchronize()
+
+    def step():
+        for m, x in zip(layers, xs):
+            m.forward(x, K, False)
+    l0 = sum(m.launch_count() for m in layers)
+    step()
+    launches_per_step = sum(m.launch_count() for m in layers) - l0
+    with ClockSampler(local_rank) as clocks:
+        ms = time_steps(torch, layers, xs, args.steps, max(args.warmup, 3), lambda: None, graph=False)
+        if ms * args.steps < 800:
+            time_steps(torch, layers, xs, int(800 / max(ms, 1e-3)) + 1, 0, lambda: None, graph=False)
+    for m in layers:
+        m.set_profiling(True)
+    step()
+    torch.cuda.synchronize()
+    for m in layers:
+        m.take_profile()
+    torch.cuda._sleep(100_000_000)
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    prof = {}
+    for m in layers:
+        for name, (n, avg_ms) in m.take_profile().items():
+            cur = prof.setdefault(name, [0, 0.0])
+            cur[0] += n
+            cur[1] += avg_ms * n
+    kern = {name: {"launches": n, "avg_us": 1e3 * tot / n} for name, (n, tot) in prof.items() if n}
+    burst, sustained, kind = measured_peak_tflops()
+    flops_gu = T * K * 2 * 2 * H * I
+    flops_dn = T * K * 2 * H * I
+    roof = None
+    if "tc_gate_up" in kern:
+        ach = flops_gu / (kern["tc_gate_up"]["avg_us"] * 1e-6) / 1e12
+        roof = {"bound": "tensor", "kernel": "tc_gate_up", "achieved": ach, "peak": burst, "unit": "TFLOP/s",
+                "frac": ach / burst, "frac_of_sustained_peak": ach / sustained, "peak_kind": kind, "traffic": None,
+                "flops_per_launch": flops_gu}
+        if "tc_down" in kern:
+            roof["down_TFLOPs"] = flops_dn / (kern["tc_down"]["avg_us"] * 1e-6) / 1e12
+            both = (flops_gu + flops_dn) / ((kern["tc_gate_up"]["avg_us"] + kern["tc_down"]["avg_us"]) * 1e-6) / 1e12
+            roof["both_gemms_TFLOPs"] = both
+    layer_tflops = (flops_gu + flops_dn) * NL / (ms * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": T * NL / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 x bf16, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"olmoe_bf16_prefill_T{T}", "hidden": H, "intermediate": I, "experts": E, "top_k": K,
+                   "tokens": T, "layers_per_step": NL, "zipf_alpha": alpha, "hottest_over_mean_load": ratio,
+                   "l2": "inputs larger than L2: %.2f GB of bf16 banks per layer" % (3 * E * H * I * 2 / 1e9)},
+        "gpu_launches": int(launches_per_step * args.steps), "gpu_launches_per_step": int(launches_per_step),
+        "clocks": clocks.summary(), "roofline": roof,
+        "layer": {"us": 1e3 * ms / NL, "TFLOPs_whole_layer": layer_tflops, "frac_of_burst_peak": layer_tflops / burst},
+        "kernels": kern,
+    }
+    print(json.dumps(line), flush=True)
+    for m in layers:
+        m.close()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -373,6 +481,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "olmoe_bf16_prefill":
+        run_prefill(args, rank, world, local_rank)
         return
     run_ours(args, rank, world, local_rank)
 

@@ -1,6 +1,7 @@
 // extern "C" surface of the library: handle life cycle, weight upload, the layer call and its
 // stages.  Declarations and the reference interface each call stands in for: include/mummu_cuda.h.
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -168,6 +169,14 @@ static int forward_device(MummuMoe* m, const void* x, void* y, int64_t tokens, i
     if (decode_q4k_supported(c, tokens) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
         if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
         if ((rc = launch_decode_q4k(m, x, tokens, top_k, s))) return rc;
+    } else if (prefill_tc_supported(c, tokens * top_k) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+               !getenv("MUMMU_CUDA_NO_TC")) {
+        // tensor-core path: sorted copy of the routed rows, two grouped GEMMs, 16-bit expert outputs
+        if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
+        if ((rc = launch_gather_rows(m, x, m->row_token, m->xs, tokens * top_k, s))) return rc;
+        if ((rc = launch_experts_tc(m, m->xs, m->cap_tokens * c.top_k, m->counts, m->offsets, m->ys, c.act_dtype, s)))
+            return rc;
+        return launch_combine(m, m->ys, c.act_dtype, m->ids, m->wts, m->pos, tokens, top_k, y, s);
     } else {
         if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
         int64_t max_rows = tokens;  // an expert serves a token at most once
@@ -384,6 +393,8 @@ int32_t mummu_moe_experts_grouped(MummuMoe* m, const void* xs, const int32_t* co
     if ((rc = ensure_scratch(m, tokens_equiv))) return rc;
     cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
     if ((rc = launch_offsets_from_counts(m, counts, m->cfg.experts_local, m->offsets, s))) return rc;
+    if (prefill_tc_supported(m->cfg, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !getenv("MUMMU_CUDA_NO_TC"))
+        return launch_experts_tc(m, xs, rows, counts, m->offsets, ys, m->cfg.act_dtype, s);
     return launch_experts_simt(m, xs, m->cfg.act_dtype, nullptr, counts, m->offsets, rows, rows, ys,
                                m->cfg.act_dtype, -1, s);
 }

@@ -201,6 +201,13 @@ int launch_q4k_dequant(const void* src, float* dst, int64_t n_blocks, cudaStream
 int launch_q4k_quantize(const float* src, void* dst, int64_t n_blocks, cudaStream_t s);
 int launch_widen(const void* src, int dtype, float* dst, int64_t n, cudaStream_t s);
 
+// ---- prefill_tc.cu ----
+bool prefill_tc_supported(const MummuMoeConfig& c, int64_t rows_total);
+int launch_gather_rows(MummuMoe* m, const void* x, const int32_t* row_token, void* xs, int64_t rows,
+                       cudaStream_t s);
+int launch_experts_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts,
+                      const int32_t* offsets, void* ys, int ys_dtype, cudaStream_t s);
+
 // ---- decode_q4k.cu ----
 bool decode_q4k_supported(const MummuMoeConfig& c, int64_t tokens);
 int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cudaStream_t s);

@@ -267,7 +267,6 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_kernel(DecodeArgs a)
     const int rt_end = min(a.n_rt, rt_begin + a.rb);
     const uint8_t* w0e = a.w0 + (size_t)e * a.expert_stride;
     const uint8_t* w1e = GATEUP ? a.w1 + (size_t)e * a.expert_stride : w0e;
-    const int groups_per_row = a.K >> 3;   // 16-byte groups of 8 halves
 
     for (int pass0 = 0; pass0 < cnt; pass0 += 8 * NT) {
         const int npass = min(8 * NT, cnt - pass0);

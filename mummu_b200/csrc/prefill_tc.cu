@@ -1,0 +1,527 @@
+// Prefill-regime expert bank on the 5th-generation tensor cores (tcgen05 + TMEM), bf16 / f16.
+//
+// Two grouped GEMMs over rows already sorted by expert (reference math:
+// crates/mummu/src/nn/moe.rs:312-316):
+//   GEMM1  hact[p, n] = silu(xs[p,:] . Wg[e,n,:]) * (xs[p,:] . Wu[e,n,:])     (16-bit out)
+//   GEMM2  ys[p, h]   = hact[p,:] . Wd[e,h,:]                                   (16-bit or f32 out)
+// Every operand is K-major ("[rows, K]" with K contiguous), which is what tcgen05.mma wants.
+//
+// One persistent CTA per SM walks a tile list built on the device from the per-expert row counts:
+// tile = (expert, 128 sorted rows, one N tile).  Each tile's accumulator is 128 TMEM lanes x 256
+// f32 columns, written by two M=128,N=128,K=16 MMAs per K step: for GEMM1 the two halves are the
+// gate and the up rows of the same 128 intermediate columns (so silu(g)*u happens in the
+// epilogue, in registers), for GEMM2 they are two adjacent 128-column blocks of the output.
+// Warp roles: warp 0 issues TMA loads (plain tiled loads, 128-byte swizzle) into a 4-stage
+// shared-memory ring; warp 1 allocates TMEM and issues the MMAs from one elected thread,
+// signalling stage reuse and accumulator completion with tcgen05.commit; warps 2-5 drain the
+// accumulator (tcgen05.ld, one TMEM lane = one output row per thread) while the MMAs of the next
+// tile fill the other accumulator stage (2 x 256 columns = all 512 TMEM columns).
+// Ragged segments: a 128-row tile may run past its expert's rows; those rows are computed (they
+// belong to the next expert or are zero fill) and masked at the store.
+//
+// Every wait on an mbarrier is bounded: when it runs out the CTA raises the handle's status word
+// (MUMMU_ERR_TIMEOUT), stops issuing work, waits (bounded) for its own copies, frees its TMEM and
+// returns.
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace mummu {
+
+constexpr int TC_BM = 128;           // rows per tile
+constexpr int TC_BK = 64;            // K per stage: 64 x 2 B = one 128-byte swizzle row
+constexpr int TC_STAGES = 4;
+constexpr int TC_THREADS = 192;      // 6 warps
+constexpr uint32_t TC_STAGE_BYTES = 3 * TC_BM * TC_BK * 2;   // A + B0 + B1 = 48 KiB
+constexpr uint32_t TC_TMEM_COLS = 512;
+constexpr uint32_t TC_SPIN_LIMIT = 4u << 20;                 // bounded waits (about a second)
+
+struct TcArgs {
+    const int32_t* counts;     // [E] rows per expert
+    const int32_t* offsets;    // [E] first sorted row per expert
+    int E;
+    int K;                     // contraction width
+    int n_tiles;               // N tiles per expert
+    int b_rows_per_expert;     // rows of the weight view per expert
+    int b_tile_rows;           // weight rows consumed by one tile in map B0 (GEMM1: 128, GEMM2: 256)
+    int b1_row_offset;         // extra row offset of the second half in map B1 (GEMM1: 0, GEMM2: 128)
+    void* out;
+    int ld_out;
+    int32_t* status;
+};
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait.  Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 64) {
+            __nanosleep(64);
+            if ((i & 255u) == 0 && *abort_flag) return false;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c_inner, int c_outer,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
+            "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c_inner), "r"(c_outer)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]^T, M = 128, N and the operand formats in idesc
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on an mbarrier once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+                 : "memory");
+}
+
+// 32 consecutive f32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row
+// groups 1024 bytes apart (the layout a tiled TMA load with SWIZZLE_128B and a 64 x 2-byte inner
+// box writes).  Stepping K by 16 elements inside the swizzle row = +32 bytes on the start address.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);      // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024u >> 4) << 32;            // stride byte offset: 8 rows x 128 B
+    d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                       // layout: 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: f32 accumulate, A and B both `fmt` (0 = f16, 1 = bf16), both K-major
+__device__ __forceinline__ uint32_t make_idesc(uint32_t fmt, uint32_t m, uint32_t n) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// ------------------------------------------------------------------------------------------------
+// tile list
+// ------------------------------------------------------------------------------------------------
+struct TileCursor {
+    int e = 0;
+    // tile index -> (expert, first sorted row, rows end of the expert, n tile)
+    __device__ __forceinline__ void locate(const int* tile_start, const int32_t* counts, const int32_t* offsets,
+                                           int tile, int n_tiles, int& expert, int& row0, int& row_end, int& nt) {
+        while (tile >= tile_start[e + 1]) ++e;
+        const int local = tile - tile_start[e];
+        const int cnt = counts[e];
+        const int m_tiles = (cnt + TC_BM - 1) / TC_BM;
+        nt = local / m_tiles;
+        const int mt = local - nt * m_tiles;
+        expert = e;
+        row0 = offsets[e] + mt * TC_BM;
+        row_end = offsets[e] + cnt;
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// the kernel
+// ------------------------------------------------------------------------------------------------
+// FUSED: GEMM1 (silu(D0)*D1 -> 128 output columns); otherwise GEMM2 (D0 | D1 -> 256 columns).
+template <typename TIN, typename TOUT, bool FUSED>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+                       const __grid_constant__ CUtensorMap map_b1, TcArgs a) {
+    extern __shared__ unsigned char smem_dyn[];
+    // 1024-byte alignment for the swizzled tiles
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    unsigned char* tiles = smem;                                           // TC_STAGES x 48 KiB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TC_STAGES * TC_STAGE_BYTES);
+    // bars: full[S], empty[S], tmem_full[2], tmem_empty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* tile_start = reinterpret_cast<int*>(tmem_slot + 2);               // [E + 1]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES);
+    const uint32_t tfull0 = smem_u32(bars + 2 * TC_STAGES), tempty0 = smem_u32(bars + 2 * TC_STAGES + 2);
+
+    // tile prefix over experts (every CTA builds the same list)
+    if (tid == 0) {
+        int acc = 0;
+        for (int e = 0; e < a.E; ++e) {
+            tile_start[e] = acc;
+            acc += ((a.counts[e] + TC_BM - 1) / TC_BM) * a.n_tiles;
+        }
+        tile_start[a.E] = acc;
+        *abort_flag = 0;
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(tfull0 + 8 * s, 1);
+            mbar_init(tempty0 + 8 * s, 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TC_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = tile_start[a.E];
+    const int k_blocks = a.K / TC_BK;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            TileCursor cur;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                int e, row0, row_end, nt;
+                cur.locate(tile_start, a.counts, a.offsets, tile, a.n_tiles, e, row0, row_end, nt);
+                const int brow0 = e * a.b_rows_per_expert + nt * a.b_tile_rows;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % TC_STAGES, ph = (it / TC_STAGES) & 1u;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t dst = smem_u32(tiles + s * TC_STAGE_BYTES);
+                    mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
+                    tma_load_2d(dst, &map_a, kb * TC_BK, row0, full0 + 8 * s);
+                    tma_load_2d(dst + TC_BM * TC_BK * 2, &map_b0, kb * TC_BK, brow0, full0 + 8 * s);
+                    tma_load_2d(dst + 2 * TC_BM * TC_BK * 2, &map_b1, kb * TC_BK, brow0 + a.b1_row_offset, full0 + 8 * s);
+                }
+            }
+            if (!ok) {
+                // gave up: let the copies already issued land before the CTA's shared memory goes away
+                for (uint32_t back = 1; back <= TC_STAGES && back <= it; ++back) {
+                    const uint32_t j = it - back, s = j % TC_STAGES, ph = (j / TC_STAGES) & 1u;
+                    for (uint32_t spin = 0; spin < (1u << 16) && !mbar_test(full0 + 8 * s, ph); ++spin) __nanosleep(64);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t fmt = sizeof(TIN) == 2 && std::is_same<TIN, __nv_bfloat16>::value ? 1u : 0u;
+            const uint32_t idesc = make_idesc(fmt, 128, 128);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tcount) {
+                const uint32_t as = tcount & 1u, aph = (tcount >> 1) & 1u;
+                if (!mbar_wait(tempty0 + 8 * as, aph ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d0 = tmem_base + as * 256u;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % TC_STAGES, ph = (it / TC_STAGES) & 1u;
+                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(tiles + s * TC_STAGE_BYTES);
+                    const uint64_t da = smem_desc_sw128(sa);
+                    const uint64_t db0 = smem_desc_sw128(sa + TC_BM * TC_BK * 2);
+                    const uint64_t db1 = smem_desc_sw128(sa + 2 * TC_BM * TC_BK * 2);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
+                        umma_f16(d0, da + 2 * k, db0 + 2 * k, idesc, acc);
+                        umma_f16(d0 + 128u, da + 2 * k, db1 + 2 * k, idesc, acc);
+                    }
+                    umma_commit(empty0 + 8 * s);          // stage reusable once these MMAs have read it
+                }
+                if (ok) umma_commit(tfull0 + 8 * as);      // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
+        const uint32_t quarter = warp & 3u;
+        TileCursor cur;
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tcount) {
+            int e, row0, row_end, nt;
+            cur.locate(tile_start, a.counts, a.offsets, tile, a.n_tiles, e, row0, row_end, nt);
+            const uint32_t as = tcount & 1u, aph = (tcount >> 1) & 1u;
+            if (!mbar_wait(tfull0 + 8 * as, aph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int row = row0 + (int)quarter * 32 + lane;
+            const bool valid = row < row_end;
+            const uint32_t t0 = tmem_base + ((quarter * 32u) << 16) + as * 256u;
+            if constexpr (FUSED) {
+                TOUT* orow = reinterpret_cast<TOUT*>(a.out) + (size_t)row * a.ld_out + (size_t)nt * 128;
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(t0 + c, g);
+                    tmem_ld32(t0 + 128 + c, u);
+                    tmem_ld_wait();
+                    if (valid) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 v;
+                            v.x = pack2<TOUT>(silu_fast(__uint_as_float(g[j + 0])) * __uint_as_float(u[j + 0]),
+                                              silu_fast(__uint_as_float(g[j + 1])) * __uint_as_float(u[j + 1]));
+                            v.y = pack2<TOUT>(silu_fast(__uint_as_float(g[j + 2])) * __uint_as_float(u[j + 2]),
+                                              silu_fast(__uint_as_float(g[j + 3])) * __uint_as_float(u[j + 3]));
+                            v.z = pack2<TOUT>(silu_fast(__uint_as_float(g[j + 4])) * __uint_as_float(u[j + 4]),
+                                              silu_fast(__uint_as_float(g[j + 5])) * __uint_as_float(u[j + 5]));
+                            v.w = pack2<TOUT>(silu_fast(__uint_as_float(g[j + 6])) * __uint_as_float(u[j + 6]),
+                                              silu_fast(__uint_as_float(g[j + 7])) * __uint_as_float(u[j + 7]));
+                            *reinterpret_cast<uint4*>(orow + c + j) = v;
+                        }
+                    }
+                }
+            } else {
+                TOUT* orow = reinterpret_cast<TOUT*>(a.out) + (size_t)row * a.ld_out + (size_t)nt * 256;
+#pragma unroll 1
+                for (int c = 0; c < 256; c += 32) {
+                    uint32_t d[32];
+                    tmem_ld32(t0 + c, d);
+                    tmem_ld_wait();
+                    if (valid) {
+                        if constexpr (sizeof(TOUT) == 4) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<uint4*>(reinterpret_cast<float*>(orow) + c + j) =
+                                    make_uint4(d[j], d[j + 1], d[j + 2], d[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 v;
+                                v.x = pack2<TIN>(__uint_as_float(d[j + 0]), __uint_as_float(d[j + 1]));
+                                v.y = pack2<TIN>(__uint_as_float(d[j + 2]), __uint_as_float(d[j + 3]));
+                                v.z = pack2<TIN>(__uint_as_float(d[j + 4]), __uint_as_float(d[j + 5]));
+                                v.w = pack2<TIN>(__uint_as_float(d[j + 6]), __uint_as_float(d[j + 7]));
+                                *reinterpret_cast<uint4*>(reinterpret_cast<TIN*>(orow) + c + j) = v;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tempty0 + 8 * as);
+        }
+    }
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag) atomicOr(a.status, STATUS_TIMEOUT);
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TC_TMEM_COLS);
+    }
+}
+
+// gather the routed rows in sorted order: xs[p, :] = x[row_token[p], :]   (16-bit rows)
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* x, const int32_t* row_token, uint4* xs,
+                                                          int64_t rows, int vec_per_row) {
+    for (int64_t p = blockIdx.x; p < rows; p += gridDim.x) {
+        const uint4* src = x + (size_t)row_token[p] * vec_per_row;
+        uint4* dst = xs + (size_t)p * vec_per_row;
+        for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// [rows, K] 16-bit row-major view, box = 64 (K) x 128 (rows), 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t k) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return MUMMU_ERR_DEVICE;
+    }
+    cuuint64_t dims[2] = {k, rows};
+    cuuint64_t strides[1] = {k * 2};
+    cuuint32_t box[2] = {TC_BK, TC_BM};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dtype == MUMMU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed (%d) for a [%llu, %llu] view", (int)r, (unsigned long long)rows,
+                  (unsigned long long)k);
+        return MUMMU_ERR_DEVICE;
+    }
+    return MUMMU_OK;
+}
+
+bool prefill_tc_supported(const MummuMoeConfig& c, int64_t rows_total) {
+    return (c.weight_dtype == MUMMU_BF16 || c.weight_dtype == MUMMU_F16) && c.act_dtype == c.weight_dtype &&
+           c.hidden % 256 == 0 && c.inter % 128 == 0 && rows_total >= 1;
+}
+
+static size_t tc_smem_bytes(int E) {
+    return 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (2 * TC_STAGES + 4) * 8 + 16 + (size_t)(E + 1) * 4 + 64;
+}
+
+template <typename TIN>
+static int launch_tc_typed(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts,
+                           const int32_t* offsets, void* ys, int ys_dtype, cudaStream_t s) {
+    const MummuMoeConfig& c = m->cfg;
+    CUtensorMap map_x, map_h, map_g, map_u, map_d;
+    int rc;
+    if ((rc = make_map(&map_x, xs, c.act_dtype, (uint64_t)rows_cap, c.hidden))) return rc;
+    if ((rc = make_map(&map_h, m->hact, c.act_dtype, (uint64_t)rows_cap, c.inter))) return rc;
+    if ((rc = make_map(&map_g, m->bank[MUMMU_BANK_GATE], c.weight_dtype, (uint64_t)c.experts_local * c.inter, c.hidden))) return rc;
+    if ((rc = make_map(&map_u, m->bank[MUMMU_BANK_UP], c.weight_dtype, (uint64_t)c.experts_local * c.inter, c.hidden))) return rc;
+    if ((rc = make_map(&map_d, m->bank[MUMMU_BANK_DOWN], c.weight_dtype, (uint64_t)c.experts_local * c.hidden, c.inter))) return rc;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c.device);
+    const size_t smem = tc_smem_bytes(c.experts_local);
+
+    TcArgs g{};
+    g.counts = counts;
+    g.offsets = offsets;
+    g.E = c.experts_local;
+    g.K = c.hidden;
+    g.n_tiles = c.inter / 128;
+    g.b_rows_per_expert = c.inter;
+    g.b_tile_rows = 128;
+    g.b1_row_offset = 0;
+    g.out = m->hact;
+    g.ld_out = c.inter;
+    g.status = m->status;
+    {
+        MUMMU_CUDA_TRY(allow_big_smem(grouped_gemm_tc_kernel<TIN, TIN, true>, c.device));
+        LaunchScope scope(m, s, "tc_gate_up");
+        grouped_gemm_tc_kernel<TIN, TIN, true><<<sms, TC_THREADS, smem, s>>>(map_x, map_g, map_u, g);
+        MUMMU_CUDA_TRY(cudaGetLastError());
+    }
+    TcArgs d{};
+    d.counts = counts;
+    d.offsets = offsets;
+    d.E = c.experts_local;
+    d.K = c.inter;
+    d.n_tiles = c.hidden / 256;
+    d.b_rows_per_expert = c.hidden;
+    d.b_tile_rows = 256;
+    d.b1_row_offset = 128;
+    d.out = ys;
+    d.ld_out = c.hidden;
+    d.status = m->status;
+    LaunchScope scope(m, s, "tc_down");
+    if (ys_dtype == MUMMU_F32) {
+        MUMMU_CUDA_TRY(allow_big_smem(grouped_gemm_tc_kernel<TIN, float, false>, c.device));
+        grouped_gemm_tc_kernel<TIN, float, false><<<sms, TC_THREADS, smem, s>>>(map_h, map_d, map_d, d);
+    } else {
+        MUMMU_CUDA_TRY(allow_big_smem(grouped_gemm_tc_kernel<TIN, TIN, false>, c.device));
+        grouped_gemm_tc_kernel<TIN, TIN, false><<<sms, TC_THREADS, smem, s>>>(map_h, map_d, map_d, d);
+    }
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+// xs: sorted rows [rows_cap, hidden] in the activation dtype (rows_cap = allocated rows, used as
+// the tensor-map bound); ys: [rows, hidden] in ys_dtype (F32 or the activation dtype)
+int launch_experts_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts,
+                      const int32_t* offsets, void* ys, int ys_dtype, cudaStream_t s) {
+    if (m->cfg.act_dtype == MUMMU_BF16)
+        return launch_tc_typed<__nv_bfloat16>(m, xs, rows_cap, counts, offsets, ys, ys_dtype, s);
+    return launch_tc_typed<__half>(m, xs, rows_cap, counts, offsets, ys, ys_dtype, s);
+}
+
+int launch_gather_rows(MummuMoe* m, const void* x, const int32_t* row_token, void* xs, int64_t rows,
+                       cudaStream_t s) {
+    if (rows == 0) return MUMMU_OK;
+    const int vec = m->cfg.hidden * 2 / 16;
+    int64_t blocks = rows < 148 * 16 ? rows : 148 * 16;
+    LaunchScope scope(m, s, "gather_rows");
+    gather_rows_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint4*)x, row_token, (uint4*)xs, rows, vec);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+}  // namespace mummu

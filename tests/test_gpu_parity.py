@@ -321,3 +321,72 @@ def test_staged_calls_match_whole_layer(M, cuda_lib):
     m.sync()
     assert torch.equal(out, whole)
     m.close()
+
+
+# ---- tensor-core (tcgen05) prefill path ---------------------------------------------------------
+
+@pytest.mark.parametrize("act,T,H,I,E,K", [("bf16", 300, 512, 256, 8, 2), ("f16", 129, 256, 128, 4, 2),
+                                           ("bf16", 1, 256, 128, 4, 2), ("bf16", 700, 1024, 512, 16, 4)])
+def test_tensor_core_layer_against_oracle(M, cuda_lib, act, T, H, I, E, K):
+    """Ragged per-expert segments (not multiples of the 128-row tile), several tiles per expert,
+    experts with no rows; outputs against the f32 oracle on the same 16-bit inputs."""
+    L = cuda_lib
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=31)
+    if act == "f16":
+        conv, back, code = (lambda a: a.astype(np.float16)), (lambda a: a.astype(np.float32)), L.F16
+    else:
+        conv, back, code = bf16_bits, bf16_to_f32, L.BF16
+    bias = np.zeros(E, np.float32)
+    bias[1] = -1000.0                      # an expert nobody picks
+    bias[0] = 3.0                          # a hot one
+    gq, uq, dq, xq = conv(gate), conv(up), conv(down), conv(x)
+    m = make_layer(M, L, H, I, E, K, code, code, router, gq, uq, dq, bias=bias)
+    y = back(m.forward(xq, K, False))
+    want, oid, _ = O.moe_forward(back(xq), router, back(gq), back(uq), back(dq), K, False, bias=bias)
+    assert 1 not in set(oid.reshape(-1).tolist())
+    assert rel_err(y, want) < TOL_16
+    prof_names = None
+    m.set_profiling(True)
+    m.forward(xq, K, False)
+    prof_names = set(m.take_profile())
+    assert "tc_gate_up" in prof_names and "tc_down" in prof_names, prof_names   # the tensor-core path ran
+    m.close()
+
+
+def test_tensor_core_prefill_config_shape(M, cuda_lib):
+    """The prefill configuration's shape (T=4096, hidden 2048, 64 experts, top-8, intermediate 1024,
+    bf16, Zipf-skewed router bias): tensor-core path against the SIMT path of the same library on
+    the same inputs, routing against the oracle, and per-token position independence."""
+    import torch
+    L = cuda_lib
+    H, I, E, K, T = 2048, 1024, 64, 8, 4096
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rnd = lambda *s: torch.randn(*s, generator=g, device="cuda") * 0.02
+    router = rnd(H, E).cpu().numpy()
+    bias = synth.zipf_router_bias(E, alpha=1.0)
+    m = M.SparseMoeConfig(H, I, E, K).init(act_dtype=L.BF16, weight_dtype=L.BF16, max_tokens=T)
+    m.set_router(router, bias=bias)
+    m.set_bank(L.BANK_GATE, rnd(E, I, H).to(torch.bfloat16))
+    m.set_bank(L.BANK_UP, rnd(E, I, H).to(torch.bfloat16))
+    m.set_bank(L.BANK_DOWN, rnd(E, H, I).to(torch.bfloat16))
+    x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
+    x[7] = x[3000]                                   # same row at two positions
+    y = m.forward(x, K, False)
+    m.sync()
+    ids, w = m.route_flat(x, K, False)
+    xf = x.float().cpu().numpy()
+    oid, ow = O.route(O.router_logits(xf, router, bias), K, False)
+    assert np.array_equal(ids.cpu().numpy(), oid)
+    assert np.array_equal(w.cpu().numpy().view(np.uint32), ow.view(np.uint32))
+    load = np.bincount(oid.reshape(-1), minlength=E)
+    assert load.max() > 3 * load.mean()              # skewed: ragged, many-tile segments
+    assert torch.equal(y[7], y[3000])
+    os.environ["MUMMU_CUDA_NO_TC"] = "1"
+    try:
+        y_simt = m.forward(x, K, False)
+        m.sync()
+    finally:
+        del os.environ["MUMMU_CUDA_NO_TC"]
+    err = (y.float() - y_simt.float()).abs().max().item() / y_simt.float().abs().max().item()
+    assert err < TOL_16
+    m.close()

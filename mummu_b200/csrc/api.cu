@@ -395,6 +395,12 @@ int32_t mummu_moe_experts_grouped(MummuMoe* m, const void* xs, const int32_t* co
     if ((rc = launch_offsets_from_counts(m, counts, m->cfg.experts_local, m->offsets, s))) return rc;
     if (prefill_tc_supported(m->cfg, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !getenv("MUMMU_CUDA_NO_TC"))
         return launch_experts_tc(m, xs, rows, counts, m->offsets, ys, m->cfg.act_dtype, s);
+    if (m->cfg.weight_dtype == MUMMU_Q4_K && m->cfg.act_dtype == MUMMU_F16 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 &&
+        rows <= 64 * m->cfg.top_k && m->cfg.hidden <= 8192 && m->cfg.inter <= 8192) {
+        // decode regime: packed-weight kernels (f32 out), then narrowed to the activation dtype
+        if ((rc = launch_decode_q4k_rows(m, xs, nullptr, counts, m->offsets, rows, (float*)m->ys, s))) return rc;
+        return launch_narrow((const float*)m->ys, ys, m->cfg.act_dtype, (int64_t)rows * m->cfg.hidden, s);
+    }
     return launch_experts_simt(m, xs, m->cfg.act_dtype, nullptr, counts, m->offsets, rows, rows, ys,
                                m->cfg.act_dtype, -1, s);
 }

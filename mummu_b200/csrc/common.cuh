@@ -211,5 +211,8 @@ int launch_experts_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32
 // ---- decode_q4k.cu ----
 bool decode_q4k_supported(const MummuMoeConfig& c, int64_t tokens);
 int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cudaStream_t s);
+int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token, const int32_t* counts,
+                           const int32_t* offsets, int64_t rows_total, float* ys, cudaStream_t s);
+int launch_narrow(const float* src, void* dst, int dtype, int64_t n, cudaStream_t s);
 
 }  // namespace mummu

@@ -497,19 +497,23 @@ static void plan(DecodeArgs& a, int experts_est, bool& stream) {
     a.ctas_per_expert = (a.n_rt + a.rb - 1) / a.rb;
 }
 
-int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cudaStream_t s) {
+// x: gate/up input rows (f16); row_token: sorted row -> row of x, or null when x is already sorted;
+// counts/offsets/active/n_active: per local expert; rows_total bounds the number of sorted rows.
+// Writes m->hact (f16) and ys (f32, [rows, hidden]).
+int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token, const int32_t* counts,
+                           const int32_t* offsets, int64_t rows_total, float* ys, cudaStream_t s) {
     const MummuMoeConfig& c = m->cfg;
     int32_t* active = m->active;
     int32_t* n_active = m->n_active;
-    int experts_est = (int)std::min<int64_t>(c.experts, tokens * top_k);
-    bool nt2 = tokens > 8;
+    int experts_est = (int)std::min<int64_t>(c.experts_local, rows_total);
+    bool nt2 = rows_total > 8;
     if (const char* env = getenv("MUMMU_CUDA_DECODE_NT")) nt2 = nt2 && atoi(env) >= 2;
 
     DecodeArgs g{};
     g.x = (const __half*)x;
-    g.row_token = m->row_token;
-    g.counts = m->counts;
-    g.offsets = m->offsets;
+    g.row_token = row_token;
+    g.counts = counts;
+    g.offsets = offsets;
     g.active = active;
     g.n_active = n_active;
     g.w0 = (const uint8_t*)m->bank[MUMMU_BANK_GATE];
@@ -529,8 +533,8 @@ int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cud
     DecodeArgs d{};
     d.x = (const __half*)m->hact;
     d.row_token = nullptr;
-    d.counts = m->counts;
-    d.offsets = m->offsets;
+    d.counts = counts;
+    d.offsets = offsets;
     d.active = active;
     d.n_active = n_active;
     d.w0 = (const uint8_t*)m->bank[MUMMU_BANK_DOWN];
@@ -542,9 +546,13 @@ int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cud
     bool d_stream;
     plan(d, experts_est, d_stream);
     d.ld_out = c.hidden;
-    d.out = m->ys;
+    d.out = ys;
     return nt2 ? launch_one<2, false>(m, d, experts_est, d_stream, s, "q4k_down")
                : launch_one<1, false>(m, d, experts_est, d_stream, s, "q4k_down");
+}
+
+int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cudaStream_t s) {
+    return launch_decode_q4k_rows(m, x, m->row_token, m->counts, m->offsets, tokens * top_k, (float*)m->ys, s);
 }
 
 }  // namespace mummu

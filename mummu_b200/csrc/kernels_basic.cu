@@ -267,6 +267,98 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
     }
 }
 
+
+// Large-T router: one block owns ALL experts of a tile of 8 tokens (thread = (expert, lane) of the
+// 8-lane dot), so the router weight is read once per 8 tokens, the logits never leave shared memory
+// and the selection runs in the same block.  Same arithmetic, same order as router_kernel.
+constexpr int RW_TT = 8;
+template <typename TX>
+__global__ void __launch_bounds__(1024) router_wide_kernel(RouterArgs a, int e_pad) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = a.H, E = a.E;
+    const int H8 = H & ~7;
+    const int row = (H8 >> 3) + 4;                               // padded length of one (token, lane) row
+    float* xs = reinterpret_cast<float*>(smem_raw);              // [TT][8][row]: element k = 8i+j at [j][i]
+    float* parts = xs + (size_t)RW_TT * 8 * row;                 // [TT][e_pad][8]
+    float* logit_s = parts + (size_t)RW_TT * e_pad * 8;          // [TT][E]
+    float* tk = logit_s + (size_t)RW_TT * E;                     // top-k scratch per warp
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int t0 = blockIdx.x * RW_TT;
+    const TX* x = reinterpret_cast<const TX*>(a.x);
+    for (int tt = 0; tt < RW_TT; ++tt) {
+        const int t = t0 + tt;
+        for (int k = tid; k < H8; k += nthreads)
+            xs[((size_t)tt * 8 + (k & 7)) * row + (k >> 3)] = t < a.T ? to_f32(x[(size_t)t * H + k]) : 0.0f;
+    }
+    __syncthreads();
+    const int e = tid % e_pad, j = tid / e_pad;                  // a warp = 32 experts of one lane j
+    float acc[RW_TT];
+#pragma unroll
+    for (int tt = 0; tt < RW_TT; ++tt) acc[tt] = 0.0f;
+    if (e < E) {
+        const float* wcol = a.w + e;
+        const int quads = H8 >> 5;                               // 4 lane-steps (32 k) per iteration
+        float wn[2][4];                                          // weights of the next two iterations, in flight
+#pragma unroll
+        for (int d = 0; d < 2; ++d)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) wn[d][u] = d < quads ? __ldg(wcol + (size_t)(8 * (4 * d + u) + j) * E) : 0.0f;
+#pragma unroll 2
+        for (int q = 0; q < quads; ++q) {
+            float w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                w[u] = wn[q & 1][u];
+                if (q + 2 < quads) wn[q & 1][u] = __ldg(wcol + (size_t)(8 * (4 * (q + 2) + u) + j) * E);
+            }
+#pragma unroll
+            for (int tt = 0; tt < RW_TT; ++tt) {
+                const float4 xv = *reinterpret_cast<const float4*>(xs + ((size_t)tt * 8 + j) * row + 4 * q);
+                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xv.x, w[0]));
+                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xv.y, w[1]));
+                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xv.z, w[2]));
+                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xv.w, w[3]));
+            }
+        }
+        for (int i = quads * 4; i < (H8 >> 3); ++i) {            // lane-steps left when H8 % 32 != 0
+            const float wv = __ldg(wcol + (size_t)(8 * i + j) * E);
+#pragma unroll
+            for (int tt = 0; tt < RW_TT; ++tt)
+                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xs[((size_t)tt * 8 + j) * row + i], wv));
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < RW_TT; ++tt) parts[((size_t)tt * e_pad + e) * 8 + j] = acc[tt];
+    __syncthreads();
+    for (int o = tid; o < RW_TT * E; o += nthreads) {
+        const int tt = o / E, e2 = o - tt * E;
+        const int t = t0 + tt;
+        if (t < a.T) {
+            const float* q = parts + ((size_t)tt * e_pad + e2) * 8;
+            float sacc = __fadd_rn(__fadd_rn(__fadd_rn(q[0], q[4]), __fadd_rn(q[1], q[5])),
+                                   __fadd_rn(__fadd_rn(q[2], q[6]), __fadd_rn(q[3], q[7])));
+            for (int i = H8; i < H; ++i)
+                sacc = __fadd_rn(sacc, __fmul_rn(to_f32(x[(size_t)t * H + i]), a.w[(size_t)i * E + e2]));
+            if (a.bias) sacc = __fadd_rn(sacc, a.bias[e2]);
+            a.logits[(size_t)t * E + e2] = sacc;                 // selection below reads them back (L1 bypass)
+        }
+    }
+    __threadfence_block();
+    __syncthreads();
+    const int warp = tid >> 5, nwarps = nthreads >> 5;
+    const int per_warp = E + 2 * a.k;
+    for (int tt = warp; tt < RW_TT; tt += nwarps) {
+        const int t = t0 + tt;
+        float* sm_v = tk + (size_t)warp * per_warp;
+        if (t < a.T) warp_softmax_topk(a, t, sm_v, sm_v + E, reinterpret_cast<int32_t*>(sm_v + E + a.k));
+    }
+}
+
+static size_t router_wide_smem(int H, int E, int e_pad, int k, int nwarps) {
+    const size_t row = (size_t)((H & ~7) >> 3) + 4;
+    return (RW_TT * 8 * row + (size_t)RW_TT * e_pad * 8 + (size_t)RW_TT * E + (size_t)nwarps * (E + 2 * k)) * 4;
+}
+
 static size_t router_smem(int H, int E, int k, int TT) {
     size_t H8 = (size_t)(H & ~7);
     return (H8 * R_ES + (size_t)TT * H + (size_t)TT * 64 + (size_t)8 * (E + 2 * k)) * 4;
@@ -274,6 +366,18 @@ static size_t router_smem(int H, int E, int k, int TT) {
 
 template <typename TX>
 static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
+    const int e_pad = (a.E + 31) & ~31;
+    if (a.T >= 256 && e_pad <= 128) {
+        const int threads = e_pad * 8;
+        const size_t smem = router_wide_smem(a.H, a.E, e_pad, a.k, threads / 32);
+        if (smem <= 200 * 1024) {
+            MUMMU_CUDA_TRY(allow_big_smem(router_wide_kernel<TX>, m->cfg.device));
+            LaunchScope scope(m, s, "router");
+            router_wide_kernel<TX><<<(a.T + RW_TT - 1) / RW_TT, threads, smem, s>>>(a, e_pad);
+            MUMMU_CUDA_TRY(cudaGetLastError());
+            return MUMMU_OK;
+        }
+    }
     int tpt = a.T >= 2048 ? 4 : (a.T >= 256 ? 2 : 1);
     while (tpt > 1 && router_smem(a.H, a.E, a.k, 4 * tpt) > 200 * 1024) tpt >>= 1;
     size_t smem = router_smem(a.H, a.E, a.k, 4 * tpt);
@@ -356,21 +460,38 @@ int launch_count(MummuMoe* m, const int32_t* ids, int64_t n, int32_t* counts, cu
     return MUMMU_OK;
 }
 
-__global__ void offsets_kernel(const int32_t* counts, int n, int32_t* offsets) {
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int e = 0; e < n; ++e) {
-            offsets[e] = acc;
-            acc += counts[e];
+__global__ void offsets_kernel(const int32_t* counts, int n, int32_t* offsets, int32_t* active,
+                               int32_t* n_active) {
+    // one warp: 32 counts at a time, prefix by shuffles
+    const int lane = threadIdx.x;
+    int acc = 0, nz = 0;
+    for (int e0 = 0; e0 < n; e0 += 32) {
+        const int e = e0 + lane;
+        const int c = e < n ? counts[e] : 0;
+        int incl = c, zincl = c > 0;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int up = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+            const int zup = __shfl_up_sync(0xFFFFFFFFu, zincl, off);
+            if (lane >= off) { incl += up; zincl += zup; }
         }
+        if (e < n) {
+            offsets[e] = acc + incl - c;
+            if (c > 0 && active) active[nz + zincl - 1] = e;
+        }
+        acc += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        nz += __shfl_sync(0xFFFFFFFFu, zincl, 31);
+    }
+    if (lane == 0) {
         offsets[n] = acc;
+        if (n_active) *n_active = nz;
     }
 }
 
 int launch_offsets_from_counts(MummuMoe* m, const int32_t* counts, int n, int32_t* offsets,
                                cudaStream_t s) {
     LaunchScope scope(m, s, "offsets");
-    offsets_kernel<<<1, 32, 0, s>>>(counts, n, offsets);
+    offsets_kernel<<<1, 32, 0, s>>>(counts, n, offsets, m->active, m->n_active);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }
@@ -424,24 +545,41 @@ __global__ void __launch_bounds__(P_THREADS) permute_kernel(const int32_t* ids, 
     __syncthreads();
     int running = base_s;
     if (counts[e] == 0) return;
-    for (int64_t start = 0; start < n; start += P_THREADS) {
-        int64_t i = start + tid;
-        bool hit = i < n && ids[i] == e;
-        unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
-        int before = __popc(ballot & ((1u << lane) - 1u));
+    // four consecutive entries per thread per step (in order, so the compaction stays stable)
+    for (int64_t start = 0; start < n; start += 4 * P_THREADS) {
+        const int64_t i0 = start + 4 * (int64_t)tid;
+        int v[4];
+        if (i0 + 3 < n && (reinterpret_cast<uintptr_t>(ids) & 15) == 0) {
+            const int4 q = *reinterpret_cast<const int4*>(ids + i0);
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = i0 + u < n ? ids[i0 + u] : -1;
+        }
+        const int mine = (v[0] == e) + (v[1] == e) + (v[2] == e) + (v[3] == e);
+        int incl = mine;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int up = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+            if (lane >= off) incl += up;
+        }
         __syncthreads();  // warp_sums reuse
-        if (lane == 0) warp_sums[warp] = __popc(ballot);
+        if (lane == 31) warp_sums[warp] = incl;
         __syncthreads();
         int wbase = 0, total = 0;
         for (int w = 0; w < P_THREADS / 32; ++w) {
-            int c = warp_sums[w];
+            const int c = warp_sums[w];
             if (w < warp) wbase += c;
             total += c;
         }
-        if (hit) {
-            int p = running + wbase + before;
-            if (row_token) row_token[p] = (int32_t)(i / top_k);
-            if (pos) pos[i] = p;
+        int p = running + wbase + incl - mine;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (v[u] == e) {
+                if (row_token) row_token[p] = (int32_t)((i0 + u) / top_k);
+                if (pos) pos[i0 + u] = p;
+                ++p;
+            }
         }
         running += total;
     }
@@ -494,14 +632,84 @@ __global__ void __launch_bounds__(256) combine_kernel(const TY* ys, const int32_
     }
 }
 
+// 8 outputs per thread: the k source rows are read with 16-byte loads before the ordered sum
+template <typename T> struct Vec8 { uint4 raw[sizeof(T) * 8 / 16]; };
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]) {
+    Vec8<T> r = *reinterpret_cast<const Vec8<T>*>(p);
+    const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = to_f32(e[i]);
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]) {
+    Vec8<T> r;
+    T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(v[i]);
+    *reinterpret_cast<Vec8<T>*>(p) = r;
+}
+
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256) combine_vec8_kernel(const TY* ys, const int32_t* ids, const float* w,
+                                                           const int32_t* pos, int top_k, int H, TO* out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    int32_t* s_pos = reinterpret_cast<int32_t*>(smem_raw);
+    float* s_w = reinterpret_cast<float*>(s_pos + top_k);
+    const int64_t t = blockIdx.x;
+    for (int r = threadIdx.x; r < top_k; r += blockDim.x) {
+        int id = ids[t * top_k + r];
+        int rank = 0;
+        for (int q = 0; q < top_k; ++q) {
+            int other = ids[t * top_k + q];
+            rank += (other < id || (other == id && q < r)) ? 1 : 0;
+        }
+        s_pos[rank] = pos[t * top_k + r];
+        s_w[rank] = w[t * top_k + r];
+    }
+    __syncthreads();
+    for (int h = (blockIdx.y * blockDim.x + threadIdx.x) * 8; h < H; h += gridDim.y * blockDim.x * 8) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int r0 = 0; r0 < top_k; r0 += 4) {
+            float v[4][8];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (r0 + u < top_k) load8(ys + (size_t)s_pos[r0 + u] * H + h, v[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (r0 + u < top_k) {
+                    const float wv = s_w[r0 + u];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(wv, v[u][i]));
+                }
+        }
+        store8(out + t * H + h, acc);
+    }
+}
+
 template <typename TY>
 static int launch_combine_y(MummuMoe* m, const void* ys, const int32_t* ids, const float* w,
                             const int32_t* pos, int64_t tokens, int top_k, void* out,
                             cudaStream_t s) {
     size_t smem = (size_t)top_k * 8;
     const int H = m->cfg.hidden;
-    const dim3 grid((unsigned)tokens, tokens < 512 ? (unsigned)((H + 255) / 256) : 1u);
+    const bool vec = (H & 7) == 0 && (reinterpret_cast<uintptr_t>(ys) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    const dim3 grid((unsigned)tokens, vec ? (tokens < 512 ? (unsigned)((H / 8 + 255) / 256) : 1u)
+                                          : (tokens < 512 ? (unsigned)((H + 255) / 256) : 1u));
     LaunchScope scope(m, s, "combine");
+    if (vec) {
+        switch (m->cfg.act_dtype) {
+            case MUMMU_F32:
+                combine_vec8_kernel<TY, float><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
+                break;
+            case MUMMU_F16:
+                combine_vec8_kernel<TY, __half><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__half*)out);
+                break;
+            case MUMMU_BF16:
+                combine_vec8_kernel<TY, __nv_bfloat16><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__nv_bfloat16*)out);
+                break;
+        }
+        MUMMU_CUDA_TRY(cudaGetLastError());
+        return MUMMU_OK;
+    }
     switch (m->cfg.act_dtype) {
         case MUMMU_F32:
             combine_kernel<TY, float><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
@@ -829,6 +1037,27 @@ int launch_q4k_quantize(const float* src, void* dst, int64_t n_blocks, cudaStrea
     int64_t blocks = (n_blocks + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
     q4k_quantize_kernel<<<(unsigned)blocks, 256, 0, s>>>(src, (uint8_t*)dst, n_blocks);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+template <typename T>
+__global__ void narrow_kernel(const float* src, T* dst, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = from_f32<T>(src[i]);
+}
+
+int launch_narrow(const float* src, void* dst, int dtype, int64_t n, cudaStream_t s) {
+    if (n == 0) return MUMMU_OK;
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    switch (dtype) {
+        case MUMMU_F32: narrow_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(src, (float*)dst, n); break;
+        case MUMMU_F16: narrow_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>(src, (__half*)dst, n); break;
+        case MUMMU_BF16: narrow_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(src, (__nv_bfloat16*)dst, n); break;
+        default: set_error("narrow: bad dtype %d", dtype); return MUMMU_ERR_CONTRACT;
+    }
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }

@@ -1,0 +1,120 @@
+"""Expert-parallel form of the MoE layer: experts sharded in contiguous blocks over the ranks of a
+`torch.distributed` group, token rows exchanged with two all-to-alls per layer.
+
+The reference has no collectives (its devices exchange through host memory,
+crates/mummu/src/backend.rs:128-143, nn/moe.rs:1219-1272); expert parallelism is how this path
+shards on an NVLink box.  Per layer and rank:
+  1. route the rank's own tokens (replicated router)                     mummu_moe_route
+  2. group (token, slot) pairs by GLOBAL expert id = by destination rank mummu_moe_permute
+  3. all-gather the per-expert row counts, plan the exchange             plan_exchange (host)
+  4. all-to-all the routed rows to the ranks that own their experts      all_to_all_single
+  5. re-order received rows (source-major -> expert-major), run the local experts
+                                                                         mummu_moe_experts_grouped
+  6. all-to-all the outputs back, weighted un-permute on the owner       mummu_moe_combine
+`plan_exchange` and the index arithmetic are plain numpy so that they run (and are tested) on CPU
+ranks with the gloo backend; only steps 1, 2, 5 and 6 touch the CUDA library.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+
+@dataclass
+class ExchangePlan:
+    send_splits: list          # rows this rank sends to each rank (sorted rows are already in that order)
+    recv_splits: list          # rows this rank receives from each rank
+    local_counts: np.ndarray   # [experts_local] rows per local expert, all sources together
+    to_expert_major: np.ndarray  # index: expert-major position -> position in the received (source-major) buffer
+
+
+def plan_exchange(all_counts: np.ndarray, rank: int, world: int) -> ExchangePlan:
+    """all_counts[src, e] = rows rank `src` routes to global expert e.  Experts are sharded in
+    contiguous blocks of E / world.  Rows arrive source-major (per source: ascending local expert,
+    ascending token); the expert bank wants them expert-major, sources in rank order inside an
+    expert, which keeps every expert's rows in a fixed, reproducible order."""
+    all_counts = np.asarray(all_counts, dtype=np.int64)
+    assert all_counts.shape[0] == world and all_counts.shape[1] % world == 0
+    el = all_counts.shape[1] // world
+    mine = all_counts[rank].reshape(world, el)
+    send_splits = mine.sum(axis=1).tolist()
+    recv = all_counts[:, rank * el:(rank + 1) * el]            # [src, e_local]
+    recv_splits = recv.sum(axis=1).tolist()
+    local_counts = recv.sum(axis=0)
+    # start of (src, e) block in the received buffer
+    flat = recv.reshape(-1)
+    starts = np.concatenate([[0], np.cumsum(flat)[:-1]]).reshape(world, el)
+    order = []
+    for e in range(el):
+        for src in range(world):
+            n = int(recv[src, e])
+            if n:
+                order.append(np.arange(starts[src, e], starts[src, e] + n))
+    to_expert_major = np.concatenate(order) if order else np.zeros(0, dtype=np.int64)
+    return ExchangePlan(send_splits, recv_splits, local_counts.astype(np.int32), to_expert_major.astype(np.int64))
+
+
+class ExpertParallelMoe:
+    """One MoE layer sharded over `group`; each rank calls forward on its own tokens."""
+
+    def __init__(self, cfg, group=None, device: Optional[int] = None, act_dtype: int = 2,
+                 weight_dtype: Optional[int] = None, max_tokens: int = 0):
+        import torch
+        import torch.distributed as dist
+        from . import moe
+        self.dist = dist
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        assert cfg.num_experts % self.world == 0, "experts must divide evenly over the ranks"
+        self.el = cfg.num_experts // self.world
+        self.cfg = cfg
+        dev = torch.cuda.current_device() if device is None else device
+        self.device = torch.device("cuda", dev)
+        # scratch for the local experts must hold the rows that can arrive: every rank's tokens * k
+        self.moe = moe.SparseMoeConfig(cfg.hidden_size, cfg.expert_intermediate_size, cfg.num_experts,
+                                       cfg.num_experts_per_tok).init(
+            device=dev, act_dtype=act_dtype, weight_dtype=weight_dtype, max_tokens=max_tokens * self.world,
+            expert_first=self.rank * self.el, experts_local=self.el)
+
+    def set_router(self, weight, layout: int = 0, bias=None):
+        self.moe.set_router(weight, layout, bias)
+
+    def set_local_banks(self, gate, up, down):
+        """Banks of this rank's experts only: [experts / world, out, in]."""
+        self.moe.set_banks(gate, up, down)
+
+    def forward(self, x, top_k: int, norm_topk_prob: bool):
+        import torch
+        dist, m = self.dist, self.moe
+        T, H = x.shape
+        E, R = self.cfg.num_experts, self.world
+        ids, w = m.route_flat(x, top_k, norm_topk_prob)
+        counts = torch.empty(E, dtype=torch.int32, device=x.device)
+        row_token = torch.empty(T * top_k, dtype=torch.int32, device=x.device)
+        pos = torch.empty(T * top_k, dtype=torch.int32, device=x.device)
+        m.permute(ids, counts, None, row_token, pos)
+        send = x.index_select(0, row_token.long())                   # rows sorted by destination expert
+        all_counts = torch.empty(R, E, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(all_counts, counts, group=self.group)
+        plan = plan_exchange(all_counts.cpu().numpy(), self.rank, R)  # host sync: split sizes are host integers
+        n_recv = int(sum(plan.recv_splits))
+        recv = torch.empty(n_recv, H, dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(recv, send, plan.recv_splits, plan.send_splits, group=self.group)
+        order = torch.from_numpy(plan.to_expert_major).to(x.device)
+        xs = recv.index_select(0, order)                              # expert-major
+        ys = torch.empty_like(xs)
+        if n_recv:
+            m.experts_grouped(xs, torch.from_numpy(plan.local_counts).to(x.device), ys)
+        back = torch.empty_like(recv)
+        back.index_copy_(0, order, ys)                                # source-major again
+        out_rows = torch.empty(T * top_k, H, dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(out_rows, back, plan.send_splits, plan.recv_splits, group=self.group)
+        y = torch.empty_like(x)
+        m.combine(out_rows, ids, w, pos, y)
+        return y
+
+    def close(self):
+        self.moe.close()

@@ -39,7 +39,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="olmoe_q4k_decode")
     ap.add_argument("--tokens", type=int, default=64)
-    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--sweep", action="store_true", help="also time T in 1,2,4,...,64 (extra key)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -474,16 +474,172 @@ def run_prefill(args, rank: int, world: int, local_rank: int):
         m.close()
 
 
+# ----------------------------------------------------------------------------------------------
+# expert-parallel runs (N > 1 of the default workload, and the Qwen3-30B-A3B-shaped stack at any N)
+# ----------------------------------------------------------------------------------------------
+def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
+    import torch
+    from mummu_b200 import _lib as L, moe
+    from mummu_b200.ep import ExpertParallelMoe
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+    stream = torch.cuda.Stream(device)
+    torch.cuda.set_stream(stream)
+    h, i, e, k = shape["hidden"], shape["inter"], shape["experts"], shape["top_k"]
+    T, NL, q4 = shape["tokens_per_rank"], shape["layers"], shape["q4k"]
+    act = L.F16 if q4 else L.BF16
+    wdt = L.Q4_K if q4 else L.BF16
+    tdt = torch.float16 if q4 else torch.bfloat16
+    el = e // world
+    cfg = moe.SparseMoeConfig(h, i, e, k)
+    gen = torch.Generator(device=device)
+    layers = []
+    for l in range(NL):
+        gen.manual_seed(9000 + l)                                   # router: same on every rank
+        router = (torch.randn(h, e, generator=gen, device=device) * 0.02).cpu().numpy()
+        gen.manual_seed(100000 + 1000 * l + rank)                   # this rank's experts
+        if world > 1:
+            m = ExpertParallelMoe(cfg, device=local_rank, act_dtype=act, weight_dtype=wdt, max_tokens=T)
+            handle = m.moe
+        else:
+            m = cfg.init(device=local_rank, act_dtype=act, weight_dtype=wdt, max_tokens=T)
+            handle = m
+        m.set_router(router)
+        for which, shp in ((L.BANK_GATE, (el, i, h)), (L.BANK_UP, (el, i, h)), (L.BANK_DOWN, (el, h, i))):
+            wt = torch.randn(shp, generator=gen, device=device) * 0.02
+            handle.set_bank(which, moe.q4k_quantize_device(wt) if q4 else wt.to(tdt))
+            del wt
+        layers.append((m, handle))
+    gen.manual_seed(777 + rank)
+    xs = [torch.randn(T, h, generator=gen, device=device).to(tdt) for _ in range(NL)]
+    torch.cuda.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def step():
+        for (m, _), x in zip(layers, xs):
+            m.forward(x, k, False)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        barrier()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        barrier()
+        ms = a.elapsed_time(b) / steps
+        if dist is not None:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    l0 = sum(hd.launch_count() for _, hd in layers)
+    step()
+    launches_per_step = sum(hd.launch_count() for _, hd in layers) - l0
+    with ClockSampler(local_rank) as clocks:
+        ms = timed(step, args.steps, max(args.warmup, 3))
+        if ms * args.steps < 800:
+            timed(step, int(800 / max(ms, 1e-3)) + 1, 0)
+
+    hx = [x.cpu().pin_memory() for x in xs]
+    def e2e_step():
+        for (m, _), hxi in zip(layers, hx):
+            xd = hxi.to(device, non_blocking=True)
+            m.forward(xd, k, False).cpu()
+    e2e_ms = timed(e2e_step, max(3, min(args.steps, 10)), 2)
+
+    for _, hd in layers:
+        hd.set_profiling(True)
+    step()
+    torch.cuda.synchronize()
+    for _, hd in layers:
+        hd.take_profile()
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    prof = {}
+    for _, hd in layers:
+        for name, (n, avg_ms) in hd.take_profile().items():
+            cur = prof.setdefault(name, [0, 0.0])
+            cur[0] += n
+            cur[1] += avg_ms * n
+    kern = {name: {"launches": n, "avg_us": 1e3 * tot / n} for name, (n, tot) in prof.items() if n}
+
+    total_tokens = T * world
+    if rank == 0:
+        flops = total_tokens * k * 6 * h * i * NL
+        line = {
+            "metric": METRIC, "value": total_tokens * NL / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": shape["scaling"], "vs_baseline": None,
+            "dtype": "f16 activations x Q4_K weights, f32 accumulate" if q4 else "bf16 x bf16, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": shape["name"], "hidden": h, "intermediate": i, "experts": e, "top_k": k,
+                       "norm_topk_prob": False, "tokens_per_gpu": T, "tokens": total_tokens, "layers_per_step": NL,
+                       "parallelism": f"ep{world}: {el} experts per GPU, NCCL all-to-all dispatch and combine"
+                       if world > 1 else "single GPU",
+                       "l2": "inputs larger than L2: %.2f GB of expert weights per GPU rotate every step"
+                             % (NL * el * 3 * h * i * (144 / 256 if q4 else 2) / 1e9)},
+            "e2e": {"value": total_tokens * NL / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": NL * T * h * 2 * world,
+                    "d2h_bytes_per_step": NL * T * h * 2 * world, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches_per_step * args.steps), "gpu_launches_per_step": int(launches_per_step),
+            "clocks": clocks.summary(),
+            "roofline": None if q4 else {"bound": "tensor", "kernel": "whole step (all ranks)",
+                                         "achieved": flops / (ms * 1e-3) / 1e12, "peak": measured_peak_tflops()[0] * world,
+                                         "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / (measured_peak_tflops()[0] * world),
+                                         "traffic": None, "peak_kind": measured_peak_tflops()[2]},
+            "kernels_rank0": kern, "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    for m, _ in layers:
+        m.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
+        if args.layers is None:
+            args.layers = 16
         run_reference(args, rank, world)
         return
     if args.workload == "olmoe_bf16_prefill":
+        if args.layers is None:
+            args.layers = 4
         run_prefill(args, rank, world, local_rank)
+        return
+    if args.workload == "ep_qwen3":
+        total = args.tokens if args.tokens != 64 else 16384
+        run_ep(args, rank, world, local_rank, dict(
+            name=f"qwen3_30b_a3b_shaped_ep_T{total}", hidden=2048, inter=768, experts=128, top_k=8,
+            tokens_per_rank=total // world, layers=args.layers or 48, q4k=False, scaling="strong"))
+        return
+    if args.layers is None:
+        args.layers = 16
+    if world > 1:
+        # the default workload on N GPUs: same layer, experts sharded, every GPU brings its own T tokens
+        run_ep(args, rank, world, local_rank, dict(
+            name=f"olmoe_q4k_decode_T{args.tokens}_per_gpu", hidden=H, inter=I, experts=E, top_k=K,
+            tokens_per_rank=args.tokens, layers=args.layers, q4k=True, scaling="weak"))
         return
     run_ours(args, rank, world, local_rank)
 

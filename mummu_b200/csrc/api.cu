@@ -165,11 +165,19 @@ static int forward_device(MummuMoe* m, const void* x, void* y, int64_t tokens, i
                           cudaStream_t s) {
     const MummuMoeConfig& c = m->cfg;
     int rc;
-    if ((rc = launch_router(m, x, tokens, top_k, norm, m->ids, m->wts, m->counts, s))) return rc;
     if (decode_q4k_supported(c, tokens) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-        if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
+        // decode: router and grouping in one launch when the call is small enough
+        rc = launch_router(m, x, tokens, top_k, norm, m->ids, m->wts, m->counts, s, true);
+        if (rc == MUMMU_ERR_UNSUPPORTED) {
+            if ((rc = launch_router(m, x, tokens, top_k, norm, m->ids, m->wts, m->counts, s))) return rc;
+            rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s);
+        }
+        if (rc) return rc;
         if ((rc = launch_decode_q4k(m, x, tokens, top_k, s))) return rc;
-    } else if (prefill_tc_supported(c, tokens * top_k) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+        return launch_combine(m, m->ys, MUMMU_F32, m->ids, m->wts, m->pos, tokens, top_k, y, s);
+    }
+    if ((rc = launch_router(m, x, tokens, top_k, norm, m->ids, m->wts, m->counts, s))) return rc;
+    if (prefill_tc_supported(c, tokens * top_k) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                !getenv("MUMMU_CUDA_NO_TC")) {
         // tensor-core path: sorted copy of the routed rows, two grouped GEMMs, 16-bit expert outputs
         if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
@@ -396,7 +404,7 @@ int32_t mummu_moe_experts_grouped(MummuMoe* m, const void* xs, const int32_t* co
     if (prefill_tc_supported(m->cfg, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !getenv("MUMMU_CUDA_NO_TC"))
         return launch_experts_tc(m, xs, rows, counts, m->offsets, ys, m->cfg.act_dtype, s);
     if (m->cfg.weight_dtype == MUMMU_Q4_K && m->cfg.act_dtype == MUMMU_F16 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 &&
-        rows <= 64 * m->cfg.top_k && m->cfg.hidden <= 8192 && m->cfg.inter <= 8192) {
+        rows <= 8192 && m->cfg.hidden <= 8192 && m->cfg.inter <= 8192) {
         // decode regime: packed-weight kernels (f32 out), then narrowed to the activation dtype
         if ((rc = launch_decode_q4k_rows(m, xs, nullptr, counts, m->offsets, rows, (float*)m->ys, s))) return rc;
         return launch_narrow((const float*)m->ys, ys, m->cfg.act_dtype, (int64_t)rows * m->cfg.hidden, s);

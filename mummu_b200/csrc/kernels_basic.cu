@@ -2,9 +2,10 @@
 //
 // The router reproduces, operation for operation, the CPU oracle's arithmetic so that routing ids
 // and weights can be compared bit for bit:
-//   logit  = 8-lane dot product: lane l sums elements l, l+8, ... with the product and the sum
-//            rounded separately; lanes fold as ((a0+a4)+(a1+a5))+((a2+a6)+(a3+a7)); leftover
-//            elements are added one by one (reference: models/qwen4exp/experts.rs:463-478)
+//   logit  = 8-lane dot product: lane l accumulates elements l, l+8, ... with one fused
+//            multiply-add per step; lanes fold as ((a0+a4)+(a1+a5))+((a2+a6)+(a3+a7)); leftover
+//            elements are fused in one by one (lane order of the reference's
+//            models/qwen4exp/experts.rs:463-478, fused steps like the gemm crate behind burn's Linear)
 //   p      = exp_det(logit - max) / (left-to-right sum)           (nn/moe.rs:2138-2141)
 //   top-k  = descending p, equal p in ascending expert id         (experts.rs:532-535, 562-574)
 //   weight = p, or p / (sum of the picked p in slot order)        (nn/moe.rs:146-150, 2146-2152)
@@ -65,6 +66,15 @@ struct RouterArgs {
     unsigned long long* hits;  // [E] or null
     int32_t* status;
     int T, H, E, k, norm;
+    // decode-sized calls: the block that finishes last also groups the (token, slot) pairs by
+    // expert, so the layer needs no separate permute launch (see fused_permute)
+    int fuse;
+    int32_t* p_counts;
+    int32_t* p_offsets;
+    int32_t* p_row_token;
+    int32_t* p_pos;
+    int32_t* p_active;
+    int32_t* p_n_active;
 };
 
 // One warp: softmax over one token's logits, then top-k.  sm_v: E floats, sm_vals: k floats,
@@ -159,6 +169,78 @@ __device__ void warp_softmax_topk(const RouterArgs& a, int t, float* sm_v, float
     __syncwarp();
 }
 
+
+// One block (256 threads) builds, for at most 1024 (token, slot) pairs, everything permute_kernel
+// builds: counts, offsets, the heaviest-first active list, row_token and pos (stable: ascending
+// token inside an expert).  Called by the last block of router_kernel; scratch is that block's
+// dynamic shared memory, free by then.
+__device__ void fused_permute(const RouterArgs& a, unsigned char* smem_raw) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n = a.T * a.k, E = a.E;
+    int32_t* ids_s = reinterpret_cast<int32_t*>(smem_raw);      // [n]
+    int32_t* cnt_s = ids_s + n;                                  // [E]
+    int32_t* off_s = cnt_s + E;                                  // [E + 1]
+    for (int i = tid; i < E; i += R_THREADS) cnt_s[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += R_THREADS) {
+        const int e = __ldcg(a.ids + i);
+        ids_s[i] = e;
+        atomicAdd(cnt_s + e, 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int acc = 0;
+        for (int e0 = 0; e0 < E; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < E ? cnt_s[e] : 0;
+            int incl = c;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int up = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+                if (lane >= off) incl += up;
+            }
+            if (e < E) off_s[e] = acc + incl - c;
+            acc += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        }
+        if (lane == 0) off_s[E] = acc;
+    }
+    __syncthreads();
+    int nz_total = 0;
+    for (int e = tid; e < E; e += R_THREADS) {
+        const int c = cnt_s[e];
+        a.p_counts[e] = c;
+        a.p_offsets[e] = off_s[e];
+        if (c > 0) {
+            int rank = 0;
+            for (int i = 0; i < E; ++i) {
+                const int ci = cnt_s[i];
+                rank += (ci > c || (ci == c && i < e)) ? 1 : 0;
+            }
+            a.p_active[rank] = e;
+        }
+    }
+    if (tid == 0) {
+        for (int e = 0; e < E; ++e) nz_total += cnt_s[e] > 0;
+        a.p_offsets[E] = off_s[E];
+        *a.p_n_active = nz_total;
+    }
+    for (int e = warp; e < E; e += R_THREADS / 32) {
+        if (cnt_s[e] == 0) continue;
+        int running = off_s[e];
+        for (int base = 0; base < n; base += 32) {
+            const int i = base + lane;
+            const bool hit = i < n && ids_s[i] == e;
+            const unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
+            if (hit) {
+                const int p = running + __popc(ballot & ((1u << lane) - 1u));
+                a.p_row_token[p] = i / a.k;
+                a.p_pos[i] = p;
+            }
+            running += __popc(ballot);
+        }
+    }
+}
+
 // grid (expert slices, token tiles).  Each block stages its 8-expert slice of W and its token
 // tile of x in shared memory, computes the logits in the fixed lane order, and the block that
 // finishes a token tile last runs softmax + top-k for that tile.
@@ -225,7 +307,7 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
 #pragma unroll
         for (int u = 0; u < TPT; ++u) {
             float xv = xs[(size_t)(tg + 4 * u) * H + i * 8 + j];
-            acc[u] = __fadd_rn(acc[u], __fmul_rn(xv, wv));
+            acc[u] = __fmaf_rn(xv, wv, acc[u]);
         }
     }
 #pragma unroll
@@ -239,7 +321,7 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
             float s = __fadd_rn(__fadd_rn(__fadd_rn(q[0], q[4]), __fadd_rn(q[1], q[5])),
                                 __fadd_rn(__fadd_rn(q[2], q[6]), __fadd_rn(q[3], q[7])));
             for (int i = H8; i < H; ++i)
-                s = __fadd_rn(s, __fmul_rn(xs[(size_t)tt * H + i], a.w[(size_t)i * E + e]));
+                s = __fmaf_rn(xs[(size_t)tt * H + i], a.w[(size_t)i * E + e], s);
             if (a.bias) s = __fadd_rn(s, a.bias[e]);
             a.logits[(size_t)t * E + e] = s;
         }
@@ -265,15 +347,31 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
         int t = t0 + tt;
         if (t < a.T) warp_softmax_topk(a, t, sm_v, sm_vals, sm_ids);
     }
+    if (!a.fuse) return;
+    // the block that finishes the last token tile groups the pairs by expert
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int32_t* all_done = a.tile_done + gridDim.y;
+        int done = atomicAdd(all_done, 1);
+        is_last = (done == (int)gridDim.y - 1);
+        if (is_last) *all_done = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    fused_permute(a, smem_raw);
 }
 
 
-// Large-T router: one block owns ALL experts of a tile of 8 tokens (thread = (expert, lane) of the
-// 8-lane dot), so the router weight is read once per 8 tokens, the logits never leave shared memory
+// Large-T router: one block owns ALL experts of a tile of 16 tokens (thread = (expert, lane) of the
+// 8-lane dot), so the router weight is read once per 16 tokens, the logits never leave shared memory
 // and the selection runs in the same block.  Same arithmetic, same order as router_kernel.
-constexpr int RW_TT = 8;
-template <typename TX>
-__global__ void __launch_bounds__(1024) router_wide_kernel(RouterArgs a, int e_pad) {
+// SPLIT groups of e_pad*8 threads share the staged tokens; group g owns tokens g*RW_TT/SPLIT ... of the tile,
+// which doubles the resident warps (latency hiding) at the same shared-memory footprint.
+template <typename TX, int e_pad, int RW_TT, int SPLIT>
+__global__ void __launch_bounds__(e_pad * 8 * SPLIT) router_wide_kernel(RouterArgs a) {
+    constexpr int TPG = RW_TT / SPLIT;   // tokens per thread group
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = a.H, E = a.E;
     const int H8 = H & ~7;
@@ -291,44 +389,62 @@ __global__ void __launch_bounds__(1024) router_wide_kernel(RouterArgs a, int e_p
             xs[((size_t)tt * 8 + (k & 7)) * row + (k >> 3)] = t < a.T ? to_f32(x[(size_t)t * H + k]) : 0.0f;
     }
     __syncthreads();
-    const int e = tid % e_pad, j = tid / e_pad;                  // a warp = 32 experts of one lane j
-    float acc[RW_TT];
+    const int grp = tid / (e_pad * 8), lt = tid - grp * (e_pad * 8);
+    const int e = lt % e_pad, j = lt / e_pad;                    // a warp = 32 experts of one lane j
+    const int tt0 = grp * TPG;
+    float acc[TPG];
 #pragma unroll
-    for (int tt = 0; tt < RW_TT; ++tt) acc[tt] = 0.0f;
+    for (int tt = 0; tt < TPG; ++tt) acc[tt] = 0.0f;
     if (e < E) {
         const float* wcol = a.w + e;
         const int quads = H8 >> 5;                               // 4 lane-steps (32 k) per iteration
-        float wn[2][4];                                          // weights of the next two iterations, in flight
+        // the weight stream runs 3 iterations ahead of the arithmetic through a 4-slot register ring
+        // (slot index is a compile-time constant after the 4x unroll)
+        float ring[4][4];
 #pragma unroll
-        for (int d = 0; d < 2; ++d)
+        for (int d = 0; d < 3; ++d)
 #pragma unroll
-            for (int u = 0; u < 4; ++u) wn[d][u] = d < quads ? __ldg(wcol + (size_t)(8 * (4 * d + u) + j) * E) : 0.0f;
-#pragma unroll 2
-        for (int q = 0; q < quads; ++q) {
+            for (int u = 0; u < 4; ++u) ring[d][u] = d < quads ? __ldg(wcol + (size_t)(8 * (4 * d + u) + j) * E) : 0.0f;
+        int q = 0;
+        for (; q + 4 <= quads; q += 4) {
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+                const int qq = q + d;
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    ring[(d + 3) & 3][u] = qq + 3 < quads ? __ldg(wcol + (size_t)(8 * (4 * (qq + 3) + u) + j) * E) : 0.0f;
+#pragma unroll
+                for (int tt = 0; tt < TPG; ++tt) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xs + ((size_t)(tt0 + tt) * 8 + j) * row + 4 * qq);
+                    acc[tt] = __fmaf_rn(xv.x, ring[d][0], acc[tt]);
+                    acc[tt] = __fmaf_rn(xv.y, ring[d][1], acc[tt]);
+                    acc[tt] = __fmaf_rn(xv.z, ring[d][2], acc[tt]);
+                    acc[tt] = __fmaf_rn(xv.w, ring[d][3], acc[tt]);
+                }
+            }
+        }
+        for (; q < quads; ++q) {                                 // fewer than 4 iterations left
             float w[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                w[u] = wn[q & 1][u];
-                if (q + 2 < quads) wn[q & 1][u] = __ldg(wcol + (size_t)(8 * (4 * (q + 2) + u) + j) * E);
-            }
+            for (int u = 0; u < 4; ++u) w[u] = __ldg(wcol + (size_t)(8 * (4 * q + u) + j) * E);
 #pragma unroll
-            for (int tt = 0; tt < RW_TT; ++tt) {
-                const float4 xv = *reinterpret_cast<const float4*>(xs + ((size_t)tt * 8 + j) * row + 4 * q);
-                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xv.x, w[0]));
-                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xv.y, w[1]));
-                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xv.z, w[2]));
-                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xv.w, w[3]));
+            for (int tt = 0; tt < TPG; ++tt) {
+                const float4 xv = *reinterpret_cast<const float4*>(xs + ((size_t)(tt0 + tt) * 8 + j) * row + 4 * q);
+                acc[tt] = __fmaf_rn(xv.x, w[0], acc[tt]);
+                acc[tt] = __fmaf_rn(xv.y, w[1], acc[tt]);
+                acc[tt] = __fmaf_rn(xv.z, w[2], acc[tt]);
+                acc[tt] = __fmaf_rn(xv.w, w[3], acc[tt]);
             }
         }
         for (int i = quads * 4; i < (H8 >> 3); ++i) {            // lane-steps left when H8 % 32 != 0
             const float wv = __ldg(wcol + (size_t)(8 * i + j) * E);
 #pragma unroll
-            for (int tt = 0; tt < RW_TT; ++tt)
-                acc[tt] = __fadd_rn(acc[tt], __fmul_rn(xs[((size_t)tt * 8 + j) * row + i], wv));
+            for (int tt = 0; tt < TPG; ++tt)
+                acc[tt] = __fmaf_rn(xs[((size_t)(tt0 + tt) * 8 + j) * row + i], wv, acc[tt]);
         }
     }
 #pragma unroll
-    for (int tt = 0; tt < RW_TT; ++tt) parts[((size_t)tt * e_pad + e) * 8 + j] = acc[tt];
+    for (int tt = 0; tt < TPG; ++tt) parts[((size_t)(tt0 + tt) * e_pad + e) * 8 + j] = acc[tt];
     __syncthreads();
     for (int o = tid; o < RW_TT * E; o += nthreads) {
         const int tt = o / E, e2 = o - tt * E;
@@ -338,7 +454,7 @@ __global__ void __launch_bounds__(1024) router_wide_kernel(RouterArgs a, int e_p
             float sacc = __fadd_rn(__fadd_rn(__fadd_rn(q[0], q[4]), __fadd_rn(q[1], q[5])),
                                    __fadd_rn(__fadd_rn(q[2], q[6]), __fadd_rn(q[3], q[7])));
             for (int i = H8; i < H; ++i)
-                sacc = __fadd_rn(sacc, __fmul_rn(to_f32(x[(size_t)t * H + i]), a.w[(size_t)i * E + e2]));
+                sacc = __fmaf_rn(to_f32(x[(size_t)t * H + i]), a.w[(size_t)i * E + e2], sacc);
             if (a.bias) sacc = __fadd_rn(sacc, a.bias[e2]);
             a.logits[(size_t)t * E + e2] = sacc;                 // selection below reads them back (L1 bypass)
         }
@@ -354,7 +470,7 @@ __global__ void __launch_bounds__(1024) router_wide_kernel(RouterArgs a, int e_p
     }
 }
 
-static size_t router_wide_smem(int H, int E, int e_pad, int k, int nwarps) {
+static size_t router_wide_smem(int H, int E, int e_pad, int k, int nwarps, int RW_TT) {
     const size_t row = (size_t)((H & ~7) >> 3) + 4;
     return (RW_TT * 8 * row + (size_t)RW_TT * e_pad * 8 + (size_t)RW_TT * E + (size_t)nwarps * (E + 2 * k)) * 4;
 }
@@ -368,12 +484,32 @@ template <typename TX>
 static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
     const int e_pad = (a.E + 31) & ~31;
     if (a.T >= 256 && e_pad <= 128) {
+        // up to 64 experts: 512 threads with 128 registers each take 16 tokens per block; wider
+        // routers run 1024 threads (64 registers) and take 8
         const int threads = e_pad * 8;
-        const size_t smem = router_wide_smem(a.H, a.E, e_pad, a.k, threads / 32);
+        const int tt = e_pad <= 64 ? 16 : 8;
+        const size_t smem = router_wide_smem(a.H, a.E, e_pad, a.k, threads / 32, tt);
         if (smem <= 200 * 1024) {
-            MUMMU_CUDA_TRY(allow_big_smem(router_wide_kernel<TX>, m->cfg.device));
             LaunchScope scope(m, s, "router");
-            router_wide_kernel<TX><<<(a.T + RW_TT - 1) / RW_TT, threads, smem, s>>>(a, e_pad);
+            const unsigned blocks = (a.T + tt - 1) / tt;
+            switch (e_pad) {
+                case 32:
+                    MUMMU_CUDA_TRY(allow_big_smem(router_wide_kernel<TX, 32, 16, 1>, m->cfg.device));
+                    router_wide_kernel<TX, 32, 16, 1><<<blocks, threads, smem, s>>>(a);
+                    break;
+                case 64:
+                    MUMMU_CUDA_TRY(allow_big_smem(router_wide_kernel<TX, 64, 16, 1>, m->cfg.device));
+                    router_wide_kernel<TX, 64, 16, 1><<<blocks, threads, smem, s>>>(a);
+                    break;
+                case 96:
+                    MUMMU_CUDA_TRY(allow_big_smem(router_wide_kernel<TX, 96, 8, 1>, m->cfg.device));
+                    router_wide_kernel<TX, 96, 8, 1><<<blocks, threads, smem, s>>>(a);
+                    break;
+                default:
+                    MUMMU_CUDA_TRY(allow_big_smem(router_wide_kernel<TX, 128, 8, 1>, m->cfg.device));
+                    router_wide_kernel<TX, 128, 8, 1><<<blocks, threads, smem, s>>>(a);
+                    break;
+            }
             MUMMU_CUDA_TRY(cudaGetLastError());
             return MUMMU_OK;
         }
@@ -406,14 +542,26 @@ static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
 }
 
 int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int norm, int32_t* ids,
-                  float* wts, int32_t* counts, cudaStream_t s) {
+                  float* wts, int32_t* counts, cudaStream_t s, bool fuse_permute) {
     const MummuMoeConfig& c = m->cfg;
     if (c.experts > 32 * R_MAXV) {
         set_error("router: %d experts exceed the %d this build selects over", c.experts, 32 * R_MAXV);
         return MUMMU_ERR_UNSUPPORTED;
     }
-    if (counts) MUMMU_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int32_t) * c.experts, s));
+    // fused grouping pays off only for a handful of pairs (one block does it): at most 128, the narrow
+    // kernel, and room in its shared memory
+    const bool fuse = fuse_permute && counts == m->counts && tokens < 256 && tokens * top_k <= 128 &&
+                      (size_t)(tokens * top_k + 2 * c.experts + 2) * 4 <= router_smem(c.hidden, c.experts, top_k, 4);
+    if (fuse_permute && !fuse) return MUMMU_ERR_UNSUPPORTED;       // caller falls back to the separate launch
+    if (counts && !fuse) MUMMU_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int32_t) * c.experts, s));
     RouterArgs a;
+    a.fuse = fuse ? 1 : 0;
+    a.p_counts = m->counts;
+    a.p_offsets = m->offsets;
+    a.p_row_token = m->row_token;
+    a.p_pos = m->pos;
+    a.p_active = m->active;
+    a.p_n_active = m->n_active;
     a.x = x;
     a.w = m->router_w;
     a.bias = m->router_bias;
@@ -421,7 +569,7 @@ int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int nor
     a.tile_done = m->tile_done;
     a.ids = ids;
     a.wts = wts;
-    a.counts = counts;
+    a.counts = fuse ? nullptr : counts;
     a.hits = m->hits;
     a.status = m->status;
     a.T = (int)tokens;
@@ -510,11 +658,15 @@ __global__ void __launch_bounds__(P_THREADS) permute_kernel(const int32_t* ids, 
     const int e = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // exclusive prefix of counts up to e
+    // part: rows of experts before e (exclusive prefix).  nz: experts that come before e in the
+    // work order "most rows first, then lower id" - longest jobs are scheduled first so that the
+    // CTAs of the expert kernels finish together.
+    const int mine_c = counts[e];
     int part = 0, nz = 0;
-    for (int i = tid; i < e; i += P_THREADS) {
+    for (int i = tid; i < E; i += P_THREADS) {
         int c = counts[i];
-        part += c;
-        nz += c > 0;
+        if (i < e) part += c;
+        nz += (c > mine_c || (c == mine_c && i < e)) && c > 0;
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -538,9 +690,8 @@ __global__ void __launch_bounds__(P_THREADS) permute_kernel(const int32_t* ids, 
             offsets[e] = b;
             if (e == E - 1) offsets[E] = b + mine;
         }
-        // experts with rows, ascending id: this expert's rank among them
         if (active && mine > 0) active[z] = e;
-        if (n_active && e == E - 1) *n_active = z + (mine > 0);
+        if (n_active && mine > 0) atomicMax(n_active, z + 1);   // the last in the order sets the count
     }
     __syncthreads();
     int running = base_s;
@@ -588,6 +739,7 @@ __global__ void __launch_bounds__(P_THREADS) permute_kernel(const int32_t* ids, 
 int launch_permute(MummuMoe* m, const int32_t* ids, int64_t tokens, int top_k,
                    const int32_t* counts, int32_t* offsets, int32_t* row_token, int32_t* pos,
                    cudaStream_t s) {
+    MUMMU_CUDA_TRY(cudaMemsetAsync(m->n_active, 0, sizeof(int32_t), s));
     LaunchScope scope(m, s, "permute");
     permute_kernel<<<m->cfg.experts, P_THREADS, 0, s>>>(ids, tokens * top_k, top_k, m->cfg.experts,
                                                         counts, offsets, row_token, pos, m->active,
@@ -1185,6 +1337,8 @@ extern "C" int32_t mummu_moe_route_noalloc(const void* x, int32_t act_dtype, con
         a.wts = w_out;
         a.counts = nullptr;
         a.hits = nullptr;
+        a.fuse = 0;
+        a.p_counts = a.p_offsets = a.p_row_token = a.p_pos = a.p_active = a.p_n_active = nullptr;
         a.status = &sc->status;
         a.T = tokens;
         a.H = hidden;

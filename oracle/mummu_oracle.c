@@ -19,7 +19,8 @@
  *    (orc_moe_routed with ORC_SUM_SEQUENTIAL).  PARITY UNPINNED for what lives inside burn 0.22.0-pre.3 /
  *    gemm 0.19.0: the summation order of its matmul, the rounding of its `exp`, and the order
  *    `topk_with_indices` gives exactly equal probabilities.  This file fixes those three choices:
- *    dot products use the reference's own fixed 8-lane order (models/qwen4exp/experts.rs:463-478),
+ *    dot products use the reference's own fixed 8-lane order (models/qwen4exp/experts.rs:463-478;
+ *    the router's lanes step with a fused multiply-add, as the gemm crate behind burn's Linear does),
  *    the softmax exponential is orc_exp below (same IEEE operation sequence on CPU and GPU, within
  *    1 ulp of the true value), ties go to the lowest expert id (experts.rs:532-535, 564-573).
  *
@@ -153,6 +154,22 @@ float orc_dot8(const float* a, const float* b, int64_t n) {
     return s;
 }
 
+/* The router's inner product: the same 8 lanes and the same fold as orc_dot8, but each lane step
+ * is ONE fused multiply-add.  The reference computes router logits with burn's `Linear`
+ * (nn/moe.rs:139, 255), i.e. the `gemm` crate's matmul (0.19.0, not in the tree), whose x86
+ * microkernels are built on fused multiply-add; the summation order inside it cannot be read
+ * here (parity unpinned), so the lane order of the reference's own `dot`
+ * (models/qwen4exp/experts.rs:463-478) is kept and only the rounding per step follows gemm. */
+float orc_dot8_fma(const float* a, const float* b, int64_t n) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int64_t chunks = n / 8;
+    for (int64_t c = 0; c < chunks; ++c)
+        for (int l = 0; l < 8; ++l) acc[l] = fmaf(a[c * 8 + l], b[c * 8 + l], acc[l]);
+    float s = ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
+    for (int64_t i = chunks * 8; i < n; ++i) s = fmaf(a[i], b[i], s);
+    return s;
+}
+
 /* Plain left-to-right inner product — the reference tests' scalar loop
  * (`(0..HIDDEN).map(|i| x[i]*w[i]).sum()`, nn/moe.rs:2136, 2156-2167). */
 static float dot_seq(const float* a, const float* b, int64_t n, int64_t stride_b) {
@@ -212,8 +229,8 @@ float orc_exp(float x) {
 
 /* logits[t, e] = x[t, :] . W[:, e] (+ bias[e]) — `self.gate.forward(xt)` (nn/moe.rs:139, 255).
  * w is [hidden, experts] row-major (burn Linear [in, out], nn/moe.rs:1642-1646).
- * order: 0 = the reference's fixed 8-lane dot (experts.rs:463-478), 1 = left to right
- * (nn/moe.rs:2136). */
+ * order: 0 = 8 fused-multiply-add lanes (orc_dot8_fma; what the CUDA router is compared against),
+ * 1 = left to right with separate roundings (the reference tests' scalar loop, nn/moe.rs:2136). */
 #define ORC_SUM_LANES8 0
 #define ORC_SUM_SEQUENTIAL 1
 
@@ -226,7 +243,7 @@ void orc_router_logits(const float* x, const float* w, const float* bias, int64_
 #pragma omp parallel for schedule(static)
     for (int64_t t = 0; t < tokens; ++t) {
         for (int64_t e = 0; e < experts; ++e) {
-            float l = order == ORC_SUM_LANES8 ? orc_dot8(x + t * hidden, wt + e * hidden, hidden)
+            float l = order == ORC_SUM_LANES8 ? orc_dot8_fma(x + t * hidden, wt + e * hidden, hidden)
                                               : dot_seq(x + t * hidden, wt + e * hidden, hidden, 1);
             if (bias) l = l + bias[e];
             logits[t * experts + e] = l;

@@ -15,7 +15,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libmummu_oracle.so")
 
-SUM_LANES8 = 0      # the reference's fixed 8-lane dot (models/qwen4exp/experts.rs:463-478)
+SUM_LANES8 = 0      # 8 lanes in the order of models/qwen4exp/experts.rs:463-478 (router: fused steps)
 SUM_SEQUENTIAL = 1  # left to right, the reference tests' scalar loop (nn/moe.rs:2136)
 
 ERR_NONFINITE = 5

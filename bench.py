@@ -25,6 +25,8 @@ if ROOT not in sys.path:
 
 import numpy as np  # noqa: E402
 
+os.environ["NCCL_DEBUG"] = os.environ.get("MUMMU_NCCL_DEBUG", "WARN")   # stdout carries one JSON line only
+
 H, I, E, K = 2048, 1024, 64, 8
 EXPERT_BYTES_Q4K = 3 * H * I * 144 // 256          # 3,538,944 B: gate + up + down of one expert
 METRIC = "moe_layer_tokens_per_s"
@@ -499,15 +501,22 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
     cfg = moe.SparseMoeConfig(h, i, e, k)
     gen = torch.Generator(device=device)
     layers = []
+    ws = None
+    if world > 1 and not os.environ.get("MUMMU_EP_NCCL"):
+        from mummu_b200.ep import PeerWorkspace
+        ws = PeerWorkspace(None, local_rank, world * T * k, h)     # rows move by peer stores / loads
     for l in range(NL):
         gen.manual_seed(9000 + l)                                   # router: same on every rank
         router = (torch.randn(h, e, generator=gen, device=device) * 0.02).cpu().numpy()
         gen.manual_seed(100000 + 1000 * l + rank)                   # this rank's experts
         if world > 1:
-            m = ExpertParallelMoe(cfg, device=local_rank, act_dtype=act, weight_dtype=wdt, max_tokens=T)
+            m = ExpertParallelMoe(cfg, device=local_rank, act_dtype=act, weight_dtype=wdt, max_tokens=T,
+                                  workspace=ws, scratch_donor=layers[0][0] if layers else None)
             handle = m.moe
         else:
-            m = cfg.init(device=local_rank, act_dtype=act, weight_dtype=wdt, max_tokens=T)
+            m = cfg.init(device=local_rank, act_dtype=act, weight_dtype=wdt, max_tokens=T if not layers else 0)
+            if layers:
+                m.adopt_scratch(layers[0][0])
             handle = m
         m.set_router(router)
         for which, shp in ((L.BANK_GATE, (el, i, h)), (L.BANK_UP, (el, i, h)), (L.BANK_DOWN, (el, h, i))):
@@ -551,10 +560,26 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
     l0 = sum(hd.launch_count() for _, hd in layers)
     step()
     launches_per_step = sum(hd.launch_count() for _, hd in layers) - l0
+    # decode-sized steps are launch-bound: replay one CUDA graph per step when the step has no host
+    # synchronisation in it (single GPU, or the peer-memory exchange)
+    run, graphed = step, False
+    if q4 and (world == 1 or ws is not None) and not os.environ.get("MUMMU_NO_GRAPH"):
+        try:
+            torch.cuda.synchronize()
+            barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=torch.cuda.current_stream()):
+                step()
+            g.replay()
+            torch.cuda.synchronize()
+            run, graphed = g.replay, True
+        except Exception as exc:                                  # keep the eager step
+            sys.stderr.write(f"graph capture of the EP step failed, running eagerly: {exc}\n")
+            torch.cuda.synchronize()
     with ClockSampler(local_rank) as clocks:
-        ms = timed(step, args.steps, max(args.warmup, 3))
+        ms = timed(run, args.steps, max(args.warmup, 3))
         if ms * args.steps < 800:
-            timed(step, int(800 / max(ms, 1e-3)) + 1, 0)
+            timed(run, int(800 / max(ms, 1e-3)) + 1, 0)
 
     hx = [x.cpu().pin_memory() for x in xs]
     def e2e_step():
@@ -591,7 +616,10 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
             "data": "synthetic",
             "config": {"workload": shape["name"], "hidden": h, "intermediate": i, "experts": e, "top_k": k,
                        "norm_topk_prob": False, "tokens_per_gpu": T, "tokens": total_tokens, "layers_per_step": NL,
-                       "parallelism": f"ep{world}: {el} experts per GPU, NCCL all-to-all dispatch and combine"
+                       "launch": "one CUDA graph per step" if graphed else "eager",
+                       "parallelism": (f"ep{world}: {el} experts per GPU, "
+                                       + ("dispatch by peer stores and combine by peer loads over NVLink, no host sync"
+                                          if ws is not None else "NCCL all-to-all dispatch and combine"))
                        if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: %.2f GB of expert weights per GPU rotate every step"
                              % (NL * el * 3 * h * i * (144 / 256 if q4 else 2) / 1e9)},
@@ -606,9 +634,13 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
             "kernels_rank0": kern, "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
-    for m, _ in layers:
+    for m, _ in reversed(layers):
         m.close()
+    torch.cuda.synchronize()
     if dist is not None:
+        dist.barrier()
+        if ws is not None:
+            ws.close()
         dist.destroy_process_group()
 
 

@@ -91,6 +91,12 @@ int32_t mummu_moe_set_router(MummuMoe* moe, const void* w, int32_t dtype, int32_
 int32_t mummu_moe_set_bank(MummuMoe* moe, int32_t which, const void* data, size_t bytes,
                            int32_t on_device);
 
+/* Let `moe` use `donor`'s per-call scratch instead of its own (a stack of identical layers that
+ * run one after another needs one set, not one per layer).  Same shape, dtype and device; the
+ * donor must outlive `moe` and must not run at the same time; size the donor (max_tokens) first.
+ * No counterpart in the reference (burn allocates intermediates per op). */
+int32_t mummu_moe_adopt_scratch(MummuMoe* moe, MummuMoe* donor);
+
 /* -------- the layer ------------------------------------------------------------------------- */
 
 /* `SparseMoe::forward` / `SparseMoePerExpert::forward` (nn/moe.rs:116-177, 214-219) on the
@@ -140,6 +146,37 @@ int32_t mummu_moe_combine(MummuMoe* moe, const void* ys, const int32_t* ids, con
  * `RoutedExperts::expert_ffn` (models/qwen4exp/experts.rs:1015-1057): one expert (LOCAL id) on
  * `rows` f32 rows from host memory, f32 rows back to host memory. */
 int32_t mummu_expert_run(MummuMoe* moe, int32_t expert, const float* x, int32_t rows, float* y);
+
+/* -------- expert parallelism over peer memory (no counterpart in the reference: its devices
+ * exchange through host memory, backend.rs:128-143, nn/moe.rs:1219-1272) ----------------------- */
+
+/* A device buffer other processes on the node can map: cudaMalloc + cudaIpcGetMemHandle.  handle64
+ * receives 64 opaque bytes to hand to the peers (any transport); peers map it with mummu_ep_open
+ * and unmap with mummu_ep_close; the owner frees with mummu_ep_free. */
+int32_t mummu_ep_alloc(int32_t device, size_t bytes, void** ptr, uint8_t* handle64);
+int32_t mummu_ep_open(int32_t device, const uint8_t* handle64, void** ptr);
+int32_t mummu_ep_close(void* ptr);
+int32_t mummu_ep_free(void* ptr);
+
+/* From the all-gathered row counts all_counts[world, experts] (device): dst_base[experts] = first
+ * row, in the owning rank's buffers, of THIS rank's rows for each global expert;
+ * local_counts[experts_local] = rows per local expert over all sources.  Buffers are expert-major
+ * with sources in rank order inside an expert, so every expert's rows are in a fixed order. */
+int32_t mummu_ep_plan(MummuMoe* moe, const int32_t* all_counts, int32_t rank, int32_t world,
+                      int32_t* dst_base, int32_t* local_counts, void* stream);
+
+/* Dispatch: for every sorted row p of this rank (mummu_moe_permute order) copy x[row_token[p]]
+ * into the owner's receive buffer at dst_base[e] + (p - offsets[e]), with peer stores.
+ * peer_recv: HOST array of `world` device pointers ([cap_rows, hidden], 16-bit activations). */
+int32_t mummu_ep_dispatch(MummuMoe* moe, const void* x, const int32_t* row_token,
+                          const int32_t* offsets, const int32_t* dst_base, void* const* peer_recv,
+                          int32_t world, int32_t rows, void* stream);
+
+/* Combine: mummu_moe_combine, reading each expert output row from its owner's buffer peer_ys[rank]
+ * (same row numbering as the receive buffer) with peer loads. */
+int32_t mummu_ep_combine(MummuMoe* moe, void* const* peer_ys, const int32_t* ids, const float* w,
+                         const int32_t* pos, const int32_t* offsets, const int32_t* dst_base,
+                         int32_t tokens, int32_t top_k, int32_t world, void* out, void* stream);
 
 /* -------- parity taps and counters ----------------------------------------------------------- */
 

@@ -32,6 +32,7 @@ SYMBOLS = {
     "mummu_moe_destroy": (C.c_int32, [C.c_void_p]),
     "mummu_moe_set_router": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "mummu_moe_set_bank": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_size_t, C.c_int32]),
+    "mummu_moe_adopt_scratch": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "mummu_moe_forward": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                       C.c_int32, C.c_int32, C.c_void_p]),
     "mummu_moe_route": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
@@ -42,6 +43,17 @@ SYMBOLS = {
                                               C.c_void_p, C.c_void_p]),
     "mummu_moe_combine": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "mummu_ep_alloc": (C.c_int32, [C.c_int32, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
+    "mummu_ep_open": (C.c_int32, [C.c_int32, C.c_char_p, C.POINTER(C.c_void_p)]),
+    "mummu_ep_close": (C.c_int32, [C.c_void_p]),
+    "mummu_ep_free": (C.c_int32, [C.c_void_p]),
+    "mummu_ep_plan": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                  C.c_void_p]),
+    "mummu_ep_dispatch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                      C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p]),
+    "mummu_ep_combine": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                     C.c_void_p]),
     "mummu_expert_run": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "mummu_moe_dequant_bank": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "mummu_moe_take_hits": (C.c_int32, [C.c_void_p, C.c_void_p]),

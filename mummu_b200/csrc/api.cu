@@ -81,6 +81,14 @@ static int dev_alloc(T** p, size_t n) {
 }
 
 static void free_scratch(MummuMoe* m) {
+    if (m->scratch_borrowed) {
+        m->logits = nullptr; m->tile_done = nullptr; m->ids = nullptr; m->wts = nullptr;
+        m->row_token = nullptr; m->pos = nullptr; m->xs = nullptr; m->hact = nullptr; m->ys = nullptr;
+        m->io_x = nullptr; m->io_y = nullptr;
+        m->cap_tokens = 0;
+        m->scratch_borrowed = false;
+        return;
+    }
     cudaFree(m->logits); cudaFree(m->tile_done); cudaFree(m->ids); cudaFree(m->wts);
     cudaFree(m->row_token); cudaFree(m->pos); cudaFree(m->xs); cudaFree(m->hact); cudaFree(m->ys);
     cudaFree(m->io_x); cudaFree(m->io_y);
@@ -92,6 +100,11 @@ static void free_scratch(MummuMoe* m) {
 
 int ensure_scratch(MummuMoe* m, int64_t tokens) {
     if (tokens <= m->cap_tokens) return MUMMU_OK;
+    if (m->scratch_borrowed) {
+        set_error("MoE: %lld tokens exceed the %lld the adopted scratch was sized for", (long long)tokens,
+                  (long long)m->cap_tokens);
+        return MUMMU_ERR_CONTRACT;
+    }
     const MummuMoeConfig& c = m->cfg;
     MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
     MUMMU_CUDA_TRY(cudaDeviceSynchronize());
@@ -496,6 +509,24 @@ int32_t mummu_moe_take_hits(MummuMoe* m, uint64_t* per_expert) {
     MUMMU_CUDA_TRY(cudaMemcpyAsync(per_expert, m->hits, bytes, cudaMemcpyDeviceToHost, m->stream));
     MUMMU_CUDA_TRY(cudaMemsetAsync(m->hits, 0, bytes, m->stream));
     MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return MUMMU_OK;
+}
+
+int32_t mummu_moe_adopt_scratch(MummuMoe* m, MummuMoe* donor) {
+    MUMMU_REQUIRE(m && donor && m != donor, "mummu_moe_adopt_scratch: bad handles");
+    const MummuMoeConfig &a = m->cfg, &b = donor->cfg;
+    MUMMU_REQUIRE(a.device == b.device && a.hidden == b.hidden && a.inter == b.inter && a.experts == b.experts &&
+                      a.top_k == b.top_k && a.act_dtype == b.act_dtype && !donor->scratch_borrowed,
+                  "mummu_moe_adopt_scratch: the two layers must have the same shape, dtype and device");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(a.device);
+    MUMMU_CUDA_TRY(cudaDeviceSynchronize());
+    free_scratch(m);
+    m->logits = donor->logits; m->tile_done = donor->tile_done; m->ids = donor->ids; m->wts = donor->wts;
+    m->row_token = donor->row_token; m->pos = donor->pos; m->xs = donor->xs; m->hact = donor->hact;
+    m->ys = donor->ys; m->io_x = donor->io_x; m->io_y = donor->io_y;
+    m->cap_tokens = donor->cap_tokens;
+    m->scratch_borrowed = true;
     return MUMMU_OK;
 }
 

@@ -135,6 +135,7 @@ struct MummuMoe {
 
     // scratch, sized for cap_tokens tokens at cfg.top_k slots each
     int64_t cap_tokens = 0;
+    bool scratch_borrowed = false;  // scratch belongs to another handle (mummu_moe_adopt_scratch)
     float* logits = nullptr;        // [tokens, experts]
     int32_t* tile_done = nullptr;   // router tile counters (self-resetting)
     int32_t* ids = nullptr;         // [tokens, k]

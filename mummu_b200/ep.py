@@ -56,11 +56,63 @@ def plan_exchange(all_counts: np.ndarray, rank: int, world: int) -> ExchangePlan
     return ExchangePlan(send_splits, recv_splits, local_counts.astype(np.int32), to_expert_major.astype(np.int64))
 
 
+class PeerWorkspace:
+    """The two peer-visible buffers of a rank (rows received for its experts, and their outputs),
+    shared by every layer of a stack: allocated by the CUDA library, exported as IPC handles,
+    exchanged through the process group, mapped by every peer."""
+
+    def __init__(self, group, device: int, cap_rows: int, hidden: int):
+        import ctypes as C
+        import torch.distributed as dist
+        from . import _lib as L
+        self.L, self.device = L, device
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.cap_rows, self.bytes = cap_rows, cap_rows * hidden * 2
+        self.own, self.opened, handles = [], [], []
+        for _ in range(2):
+            ptr, h = C.c_void_p(), C.create_string_buffer(64)
+            rc = L.lib.mummu_ep_alloc(device, self.bytes, C.byref(ptr), h)
+            if rc:
+                raise RuntimeError(L.last_error())
+            self.own.append(ptr.value)
+            handles.append(h.raw)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, handles, group=group)
+        self.tables = []
+        for which in range(2):
+            table = (C.c_void_p * self.world)()
+            for r in range(self.world):
+                if r == self.rank:
+                    table[r] = self.own[which]
+                else:
+                    ptr = C.c_void_p()
+                    rc = L.lib.mummu_ep_open(device, gathered[r][which], C.byref(ptr))
+                    if rc:
+                        raise RuntimeError(L.last_error())
+                    self.opened.append(ptr.value)
+                    table[r] = ptr.value
+            self.tables.append(table)
+        self.recv_table, self.ys_table = self.tables
+        self.recv_ptr, self.ys_ptr = self.own
+
+    def close(self):
+        for p in self.opened:
+            self.L.lib.mummu_ep_close(p)
+        for p in self.own:
+            self.L.lib.mummu_ep_free(p)
+        self.opened, self.own = [], []
+
+
 class ExpertParallelMoe:
-    """One MoE layer sharded over `group`; each rank calls forward on its own tokens."""
+    """One MoE layer sharded over `group`; each rank calls forward on its own tokens.
+
+    With a `PeerWorkspace` (16-bit activations) rows move by peer stores and loads over NVLink and
+    nothing waits for the host; without one the exchange is two NCCL all-to-alls whose split sizes
+    are read back to the host."""
 
     def __init__(self, cfg, group=None, device: Optional[int] = None, act_dtype: int = 2,
-                 weight_dtype: Optional[int] = None, max_tokens: int = 0):
+                 weight_dtype: Optional[int] = None, max_tokens: int = 0, workspace=None,
+                 scratch_donor=None):
         import torch
         import torch.distributed as dist
         from . import moe
@@ -73,11 +125,17 @@ class ExpertParallelMoe:
         self.cfg = cfg
         dev = torch.cuda.current_device() if device is None else device
         self.device = torch.device("cuda", dev)
+        import torch as _t  # noqa: F401
         # scratch for the local experts must hold the rows that can arrive: every rank's tokens * k
+        self.workspace = workspace
         self.moe = moe.SparseMoeConfig(cfg.hidden_size, cfg.expert_intermediate_size, cfg.num_experts,
                                        cfg.num_experts_per_tok).init(
-            device=dev, act_dtype=act_dtype, weight_dtype=weight_dtype, max_tokens=max_tokens * self.world,
+            device=dev, act_dtype=act_dtype, weight_dtype=weight_dtype,
+            max_tokens=0 if scratch_donor is not None else max_tokens * self.world,
             expert_first=self.rank * self.el, experts_local=self.el)
+        if scratch_donor is not None:
+            self.moe.adopt_scratch(scratch_donor.moe)
+        self._flag = torch.zeros(1, device=self.device)
 
     def set_router(self, weight, layout: int = 0, bias=None):
         self.moe.set_router(weight, layout, bias)
@@ -86,7 +144,35 @@ class ExpertParallelMoe:
         """Banks of this rank's experts only: [experts / world, out, in]."""
         self.moe.set_banks(gate, up, down)
 
+    def _barrier(self):
+        self.dist.all_reduce(self._flag, group=self.group)       # device-side: nobody waits on the host
+
+    def forward_p2p(self, x, top_k: int, norm_topk_prob: bool):
+        import torch
+        dist, m, ws = self.dist, self.moe, self.workspace
+        T, H = x.shape
+        E, R = self.cfg.num_experts, self.world
+        assert T * top_k * R <= ws.cap_rows, "workspace too small for the rows that may arrive"
+        i32 = dict(dtype=torch.int32, device=x.device)
+        ids, w = m.route_flat(x, top_k, norm_topk_prob)
+        counts, offsets = torch.empty(E, **i32), torch.empty(E + 1, **i32)
+        row_token, pos = torch.empty(T * top_k, **i32), torch.empty(T * top_k, **i32)
+        m.permute(ids, counts, offsets, row_token, pos)
+        all_counts = torch.empty(R, E, **i32)
+        dist.all_gather_into_tensor(all_counts, counts, group=self.group)
+        dst_base, local_counts = torch.empty(E, **i32), torch.empty(self.el, **i32)
+        m.ep_plan(all_counts, self.rank, R, dst_base, local_counts)
+        m.ep_dispatch(x, row_token, offsets, dst_base, ws.recv_table, R)
+        self._barrier()                                           # every rank's rows have landed
+        m.experts_grouped_raw(ws.recv_ptr, local_counts, T * top_k * R, ws.ys_ptr)
+        self._barrier()                                           # every rank's outputs are written
+        y = torch.empty_like(x)
+        m.ep_combine(ws.ys_table, ids, w, pos, offsets, dst_base, R, y)
+        return y
+
     def forward(self, x, top_k: int, norm_topk_prob: bool):
+        if self.workspace is not None:
+            return self.forward_p2p(x, top_k, norm_topk_prob)
         import torch
         dist, m = self.dist, self.moe
         T, H = x.shape

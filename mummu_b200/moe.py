@@ -121,6 +121,10 @@ class SparseMoe:
         except Exception:
             pass
 
+    def adopt_scratch(self, donor: "SparseMoe") -> None:
+        """Use `donor`'s per-call scratch (layers of one stack run one after another)."""
+        _check(L.lib.mummu_moe_adopt_scratch(self._h, donor._h))
+
     # -- weights ----------------------------------------------------------------------------
     def set_router(self, weight, layout: int = L.ROUTER_IN_OUT, bias=None) -> None:
         """`gate: Linear` weight, [hidden, experts] (burn, nn/moe.rs:1642) or [experts, hidden]
@@ -279,6 +283,25 @@ class SparseMoe:
     def experts_grouped(self, xs, counts, ys) -> None:
         _check(L.lib.mummu_moe_experts_grouped(self._h, xs.data_ptr(), counts.data_ptr(),
                                                xs.shape[0], ys.data_ptr(), _torch_stream()))
+
+    def experts_grouped_raw(self, xs_ptr: int, counts, rows: int, ys_ptr: int) -> None:
+        _check(L.lib.mummu_moe_experts_grouped(self._h, xs_ptr, counts.data_ptr(), rows, ys_ptr,
+                                               _torch_stream()))
+
+    def ep_plan(self, all_counts, rank: int, world: int, dst_base, local_counts) -> None:
+        _check(L.lib.mummu_ep_plan(self._h, all_counts.data_ptr(), rank, world, dst_base.data_ptr(),
+                                   local_counts.data_ptr(), _torch_stream()))
+
+    def ep_dispatch(self, x, row_token, offsets, dst_base, peer_table, world: int) -> None:
+        _check(L.lib.mummu_ep_dispatch(self._h, x.data_ptr(), row_token.data_ptr(), offsets.data_ptr(),
+                                       dst_base.data_ptr(), peer_table, world, row_token.numel(),
+                                       _torch_stream()))
+
+    def ep_combine(self, peer_table, ids, w, pos, offsets, dst_base, world: int, out) -> None:
+        tokens, top_k = ids.shape
+        _check(L.lib.mummu_ep_combine(self._h, peer_table, ids.data_ptr(), w.data_ptr(), pos.data_ptr(),
+                                      offsets.data_ptr(), dst_base.data_ptr(), tokens, top_k, world,
+                                      out.data_ptr(), _torch_stream()))
 
     def combine(self, ys, ids, w, pos, out) -> None:
         tokens, top_k = ids.shape

@@ -33,7 +33,9 @@ def _worker(rank, world, port, q, act, wdt_name):
             enc = lambda a: torch.from_numpy(a).to(torch.bfloat16).cuda()
         el = E // world
         cfg = moe.SparseMoeConfig(H, I, E, K)
-        ep = ExpertParallelMoe(cfg, device=rank, act_dtype=act_code, weight_dtype=wcode, max_tokens=T)
+        from mummu_b200.ep import PeerWorkspace
+        ws = PeerWorkspace(None, rank, world * T * K, H) if act == "p2p" else None
+        ep = ExpertParallelMoe(cfg, device=rank, act_dtype=act_code, weight_dtype=wcode, max_tokens=T, workspace=ws)
         ep.set_router(router)
         sl = slice(rank * el, (rank + 1) * el)
         ep.set_local_banks(enc(gate[sl]), enc(up[sl]), enc(down[sl]))
@@ -50,12 +52,17 @@ def _worker(rank, world, port, q, act, wdt_name):
         q.put((rank, err, bool(torch.equal(y_ep, y_ep2))))
         ep.close()
         single.close()
+        torch.cuda.synchronize()
+        dist.barrier()
+        if ws is not None:
+            ws.close()
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("mode", ["nccl", "p2p"])
 @pytest.mark.parametrize("wdt_name", ["bf16", "q4k"])
-def test_expert_parallel_matches_single_gpu(cuda_lib, wdt_name):
+def test_expert_parallel_matches_single_gpu(cuda_lib, wdt_name, mode):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -65,7 +72,7 @@ def test_expert_parallel_matches_single_gpu(cuda_lib, wdt_name):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, "x", wdt_name)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, mode, wdt_name)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in procs]

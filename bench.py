@@ -560,10 +560,10 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
     l0 = sum(hd.launch_count() for _, hd in layers)
     step()
     launches_per_step = sum(hd.launch_count() for _, hd in layers) - l0
-    # decode-sized steps are launch-bound: replay one CUDA graph per step when the step has no host
-    # synchronisation in it (single GPU, or the peer-memory exchange)
+    # decode-sized steps are launch-bound: on one GPU replay one CUDA graph per step.  Multi-GPU steps
+    # stay eager: a captured graph that holds NCCL kernels kept the process group from shutting down
     run, graphed = step, False
-    if q4 and (world == 1 or ws is not None) and not os.environ.get("MUMMU_NO_GRAPH"):
+    if q4 and world == 1 and not os.environ.get("MUMMU_NO_GRAPH"):
         try:
             torch.cuda.synchronize()
             barrier()
@@ -634,6 +634,8 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
             "kernels_rank0": kern, "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
+    # the result is out: never let a stuck shutdown of peers / NCCL hold the GPUs
+    threading.Timer(30.0, lambda: os._exit(0)).start()
     for m, _ in reversed(layers):
         m.close()
     torch.cuda.synchronize()
@@ -642,6 +644,7 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
         if ws is not None:
             ws.close()
         dist.destroy_process_group()
+    os._exit(0)
 
 
 def main():

@@ -280,7 +280,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if "q4k_gate_up" in kern:
         ach = gu_bytes / (kern["q4k_gate_up"]["avg_us"] * 1e-6) / 1e9
         roof = {"bound": "hbm", "kernel": "q4k_gate_up", "achieved": ach, "peak": peak, "unit": "GB/s",
-                "frac": ach / peak, "peak_kind": peak_kind, "traffic": None,
+                "frac": ach / peak, "peak_kind": peak_kind,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this very shape
+                # (T=64, 64 experts hit), from the ncu capture summarised in profiles/decode_q4k_gate_up_T64.md
+                "traffic": 156.3e6 if (T == 64 and u_mean == 64.0) else None,
                 "algorithmic_bytes_per_launch": gu_bytes, "frac_of_nominal_8TBs": ach / 8000.0}
     layer_bytes = u_mean * EXPERT_BYTES_Q4K + H * E * 4 + 2 * T * H * 2
 
@@ -647,6 +650,69 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
     os._exit(0)
 
 
+# ----------------------------------------------------------------------------------------------
+# whole-model decode: OLMoE-1B-7B-shaped, random weights, Q4_K experts, f16 trunk
+# ----------------------------------------------------------------------------------------------
+def run_model(args, rank: int, world: int, local_rank: int):
+    import torch
+    from mummu_b200 import _lib as L
+    from mummu_b200.olmoe import OlmoeConfig, OlmoeDecoder
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    cfg = OlmoeConfig()
+    prompt, n_new = 512, 128
+    results = {}
+    for B in (1, 32):
+        chunk = max(1, 2048 // B)                       # prompt fed in chunks of <= 2048 tokens over the batch
+        dec = OlmoeDecoder(cfg, device=local_rank, expert_dtype=L.Q4_K, max_batch=B, max_ctx=prompt + n_new,
+                           max_tokens=B * chunk)
+        dec.random_init(seed=11)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(5 + B)
+        ids = torch.randint(0, cfg.vocab_size, (B, prompt), generator=gen, device=device)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        past, logits = 0, None
+        while past < prompt:
+            logits = dec.forward(ids[:, past:past + chunk], past)
+            past += min(chunk, prompt - past)
+        torch.cuda.synchronize()
+        t_prefill = time.perf_counter() - t0
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = sum(l["mlp"].launch_count() for l in dec.layers)
+        dec._decode_static(torch.zeros(B, 1, dtype=torch.int64, device=device),
+                           torch.tensor([prompt + n_new - 1], device=device))     # counts one step's launches
+        launches1 = sum(l["mlp"].launch_count() for l in dec.layers)
+        g, ids_buf, pos_buf, logits_buf = dec.make_decode_graph(B)              # one CUDA graph per decode step
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(n_new):
+            ids_buf.copy_(logits.argmax(-1)[:, None])
+            pos_buf.fill_(past)
+            g.replay()
+            logits = logits_buf
+            past += 1
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        results[B] = dict(decode_tok_per_s=B * n_new / (ms * 1e-3), ms_per_token_step=ms / n_new,
+                          prefill_s=t_prefill,
+                          moe_launches_per_step=launches1 - launches0)
+        dec.close()
+        del dec
+        torch.cuda.empty_cache()
+    line = {"metric": "olmoe_decode_tokens_per_s", "value": results[32]["decode_tok_per_s"], "unit": "tokens/s",
+            "n_gpus": 1, "steps": n_new, "warmup": 0, "ms_per_step": results[32]["ms_per_token_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 trunk, Q4_K experts", "data": "synthetic",
+            "config": {"workload": "olmoe_1b_7b_shaped_greedy_decode", "layers": cfg.num_hidden_layers,
+                       "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "experts": cfg.num_experts,
+                       "top_k": cfg.num_experts_per_tok, "vocab": cfg.vocab_size, "prompt": prompt, "new_tokens": n_new,
+                       "launch": "one CUDA graph per decode step (trunk in torch, MoE layers through the C ABI)"},
+            "batch_1": results[1], "batch_32": results[32]}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -661,6 +727,9 @@ def main():
         if args.layers is None:
             args.layers = 4
         run_prefill(args, rank, world, local_rank)
+        return
+    if args.workload == "olmoe_decode":
+        run_model(args, rank, world, local_rank)
         return
     if args.workload == "ep_qwen3":
         total = args.tokens if args.tokens != 64 else 16384

@@ -1,0 +1,93 @@
+"""The OLMoE decoder around the expert bank: the CPU restatement against itself (the reference's
+own cache test), and the GPU model against the restatement."""
+import numpy as np
+import pytest
+
+from mummu_b200 import q4k, synth
+from mummu_b200.olmoe import OlmoeConfig
+
+
+def tiny_state(cfg, q4: bool, seed=3):
+    rng = np.random.default_rng(seed)
+    H, I, E, V = cfg.hidden_size, cfg.intermediate_size, cfg.num_experts, cfg.vocab_size
+    n = lambda *s: (rng.standard_normal(s) * 0.05).astype(np.float32)
+    h16 = lambda a: a.astype(np.float16).astype(np.float32)          # what the f16 trunk will hold
+    st = dict(embed=h16(n(V, H) * 10), lm_head=h16(n(V, H)), norm=(1 + n(H)).astype(np.float32))
+    for l in range(cfg.num_hidden_layers):
+        for name in ("q", "k", "v", "o"):
+            st[f"l{l}.{name}"] = h16(n(H, H))
+        for name in ("in_norm", "post_norm", "q_norm", "k_norm"):
+            st[f"l{l}.{name}"] = (1 + n(H)).astype(np.float32)
+        st[f"l{l}.router"] = n(H, E)
+        g, u, d = n(E, I, H), n(E, I, H), n(E, H, I)
+        if q4:
+            g, u, d = (q4k.quantize(b) for b in (g, u, d))
+        else:
+            g, u, d = h16(g), h16(u), h16(d)
+        st[f"l{l}.gate"], st[f"l{l}.up"], st[f"l{l}.down"] = g, u, d
+    return st
+
+
+CFG = OlmoeConfig(vocab_size=97, hidden_size=256, intermediate_size=256, num_hidden_layers=2,
+                  num_attention_heads=4, num_key_value_heads=4, num_experts=4, num_experts_per_tok=2)
+
+
+def test_reference_restatement_cached_equals_full_forward():
+    """models/olmoe.rs:678-708: prefill + cached decode == one full forward, < 1e-4."""
+    from oracle.olmoe_ref import RefOlmoe
+    st = tiny_state(CFG, q4=False)
+    ids = [5, 17, 3, 88, 42, 7]
+    full = RefOlmoe(CFG, st, False).forward(ids, 0)
+    m = RefOlmoe(CFG, st, False)
+    m.forward(ids[:4], 0)
+    m.forward(ids[4:5], 4)
+    step = m.forward(ids[5:6], 5)
+    assert np.abs(full - step).max() < 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("q4", [True, False])
+def test_gpu_decoder_matches_restatement(cuda_lib, q4):
+    import torch
+    from mummu_b200 import _lib as L
+    from mummu_b200.olmoe import OlmoeDecoder
+    from oracle.olmoe_ref import RefOlmoe
+    st = tiny_state(CFG, q4)
+    dec = OlmoeDecoder(CFG, device=0, expert_dtype=L.Q4_K if q4 else L.F16, max_batch=2, max_ctx=32)
+    dec.load_state(st)
+    prompts = [[5, 17, 3, 88, 42], [9, 9, 61, 2, 30]]
+    ids = torch.tensor(prompts, device="cuda")
+    logits = dec.forward(ids, 0)
+    refs = [RefOlmoe(CFG, st, q4) for _ in prompts]
+    want = np.stack([r.forward(p, 0) for r, p in zip(refs, prompts)])
+    scale = np.abs(want).max()
+    assert np.abs(logits.cpu().numpy() - want).max() / scale < 2e-2
+    # three teacher-forced decode steps (the oracle's token is fed to both)
+    past = 5
+    for _ in range(3):
+        nxt = want.argmax(-1)
+        logits = dec.forward(torch.tensor(nxt, device="cuda")[:, None], past)
+        want = np.stack([r.forward([int(t)], past) for r, t in zip(refs, nxt)])
+        assert np.abs(logits.cpu().numpy() - want).max() / np.abs(want).max() < 2e-2
+        top2 = np.sort(want, -1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 0.05 * np.abs(want).max()
+        assert (logits.argmax(-1).cpu().numpy()[clear] == want.argmax(-1)[clear]).all()
+        past += 1
+    # the shape-static step (the one a CUDA graph captures) == the growing-cache step
+    ids_buf = torch.tensor(want.argmax(-1), device="cuda")[:, None]
+    pos_buf = torch.tensor([past], device="cuda")
+    static = dec._decode_static(ids_buf, pos_buf)
+    dec.k_cache[:, :, :, past].zero_()
+    dec.v_cache[:, :, :, past].zero_()
+    grown = dec.forward(ids_buf, past)
+    assert (static - grown).abs().max().item() / grown.abs().max().item() < 5e-3
+    g, gi, gp, gl = dec.make_decode_graph(2)
+    gi.copy_(ids_buf)
+    gp.fill_(past)
+    g.replay()
+    assert (gl - grown).abs().max().item() / grown.abs().max().item() < 5e-3
+    # greedy generation runs and is deterministic
+    a = dec.greedy_generate(ids, 4)
+    b = dec.greedy_generate(ids, 4)
+    assert torch.equal(a, b) and a.shape == (2, 4)
+    dec.close()

@@ -171,6 +171,12 @@ __device__ __forceinline__ void load_unit(UnitRegs& r, const uint8_t* row0, cons
     r.qb[1] = __ldcs(reinterpret_cast<const uint4*>(row1 + 32 + 32 * t));
 }
 
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -357,7 +363,7 @@ template <int NT, int NTC, bool GATEUP>
 __device__ __forceinline__ void stream_rows(const DecodeArgs& a, uint32_t frag_base, uint32_t sxh_base,
                                             const uint8_t* w0e, const uint8_t* w1e, int rt_first, int rt_end,
                                             int nsb, int g, int t, bool upper, uint32_t sel, int first_row,
-                                            int npass) {
+                                            int npass, uint32_t slot) {
     const size_t half_tile = (size_t)8 * a.row_bytes;
     for (int rt = rt_first; rt < rt_end; rt += DQ_WARPS) {
         // row g of matrix 0 / matrix 1 at super-block 0
@@ -370,19 +376,59 @@ __device__ __forceinline__ void stream_rows(const DecodeArgs& a, uint32_t frag_b
             for (int nt = 0; nt < NTC; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) y[mt][nt][i] = 0.0f;
-        UnitRegs ua, ub;
-        load_unit(ua, r0p, r0p + half_tile, t);
+        // The next unit's 96 bytes per lane travel global -> shared with cp.async (no registers
+        // held while in flight); each lane owns six private 16-byte slots, so no cross-lane hazard.
+        auto prefetch = [&](const uint8_t* row0) {
+            const uint8_t* row1 = row0 + half_tile;
+            cp_async16(slot + 0 * 512, row0);
+            cp_async16(slot + 1 * 512, row0 + 16 + 32 * t);
+            cp_async16(slot + 2 * 512, row0 + 32 + 32 * t);
+            cp_async16(slot + 3 * 512, row1);
+            cp_async16(slot + 4 * 512, row1 + 16 + 32 * t);
+            cp_async16(slot + 5 * 512, row1 + 32 + 32 * t);
+            cp_async_commit();
+        };
+        auto take = [&](UnitRegs& u) {
+            cp_async_wait_all();
+            u.hdr[0] = lds128(slot + 0 * 512);
+            u.qa[0] = lds128(slot + 1 * 512);
+            u.qb[0] = lds128(slot + 2 * 512);
+            u.hdr[1] = lds128(slot + 3 * 512);
+            u.qa[1] = lds128(slot + 4 * 512);
+            u.qb[1] = lds128(slot + 5 * 512);
+        };
         uint32_t frag_addr = frag_base + (uint32_t)((g * 4 + t) * 16);
         uint32_t sxh_addr = sxh_base + (uint32_t)((g * 8 + 2 * t) * 2);
-        for (int sb = 0; sb < nsb; ++sb) {
-            load_unit(ub, r1p, r1p + half_tile, t);
-            r1p += Q4K_BLOCK_BYTES;
-            r0p += Q4K_BLOCK_BYTES;
-            unit_terms<NT, NTC>(ua, upper, sel, frag_addr, sxh_addr, y[0]);
-            if (sb + 1 < nsb) load_unit(ua, r0p, r0p + half_tile, t);
-            unit_terms<NT, NTC>(ub, upper, sel, frag_addr, sxh_addr, y[1]);
-            frag_addr += (uint32_t)(NT * 64 * 4 * 16);
-            sxh_addr += (uint32_t)(NT * 8 * 8 * 2);
+        if (NTC >= 2) {
+            // two token tiles leave no registers for a second unit: prefetch through shared memory
+            UnitRegs un;
+            prefetch(r0p);
+            for (int sb = 0; sb < nsb; ++sb) {
+                take(un);
+                prefetch(r1p);                                    // matrix 1 of this super-block
+                unit_terms<NT, NTC>(un, upper, sel, frag_addr, sxh_addr, y[0]);
+                r0p += Q4K_BLOCK_BYTES;
+                take(un);
+                if (sb + 1 < nsb) prefetch(r0p);                  // matrix 0 of the next super-block
+                unit_terms<NT, NTC>(un, upper, sel, frag_addr, sxh_addr, y[1]);
+                r1p += Q4K_BLOCK_BYTES;
+                frag_addr += (uint32_t)(NT * 64 * 4 * 16);
+                sxh_addr += (uint32_t)(NT * 8 * 8 * 2);
+            }
+        } else {
+            // one token tile: the next unit waits in a second set of registers
+            UnitRegs ua, ub;
+            load_unit(ua, r0p, r0p + half_tile, t);
+            for (int sb = 0; sb < nsb; ++sb) {
+                load_unit(ub, r1p, r1p + half_tile, t);
+                r1p += Q4K_BLOCK_BYTES;
+                r0p += Q4K_BLOCK_BYTES;
+                unit_terms<NT, NTC>(ua, upper, sel, frag_addr, sxh_addr, y[0]);
+                if (sb + 1 < nsb) load_unit(ua, r0p, r0p + half_tile, t);
+                unit_terms<NT, NTC>(ub, upper, sel, frag_addr, sxh_addr, y[1]);
+                frag_addr += (uint32_t)(NT * 64 * 4 * 16);
+                sxh_addr += (uint32_t)(NT * 8 * 8 * 2);
+            }
         }
         // epilogue from registers: lane (g, t) holds rows g, g+8 x tokens 2t, 2t+1
 #pragma unroll
@@ -432,6 +478,8 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_stream_kernel(Decode
     const int g = lane >> 2, t = lane & 3;
     const bool upper = t >= 2;
     const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
+    // per-lane prefetch slots: [warp][6 chunks][32 lanes] x 16 B, after the token tile
+    const uint32_t slot = sxh_base + (uint32_t)(nsb * NT * 128) + (uint32_t)(warp * 6 * 512 + lane * 16);
     const int rt_begin = cb * a.rb;
     const int rt_end = min(a.n_rt, rt_begin + a.rb);
     const uint8_t* w0e = a.w0 + (size_t)e * a.expert_stride;
@@ -446,10 +494,10 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_stream_kernel(Decode
 
         if (NT == 1 || nt_count == 1)
             stream_rows<NT, 1, GATEUP>(a, frag_base, sxh_base, w0e, w1e, rt_begin + warp, rt_end, nsb, g, t, upper,
-                                       sel, base + pass0, npass);
+                                       sel, base + pass0, npass, slot);
         else
             stream_rows<NT, NT, GATEUP>(a, frag_base, sxh_base, w0e, w1e, rt_begin + warp, rt_end, nsb, g, t, upper,
-                                        sel, base + pass0, npass);
+                                        sel, base + pass0, npass, slot);
     }
 }
 
@@ -463,7 +511,7 @@ static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream
                       const char* name) {
     const int nsb = a.K >> 8;
     size_t smem = dq_smem_bytes<NT>(nsb);
-    if (stream) smem = (size_t)nsb * NT * 4096 + (size_t)nsb * NT * 128;
+    if (stream) smem = (size_t)nsb * NT * 4096 + (size_t)nsb * NT * 128 + (size_t)DQ_WARPS * 6 * 512;
     if (smem > 200 * 1024) {
         set_error("decode_q4k: %zu bytes of shared memory needed for K=%d", smem, a.K);
         return MUMMU_ERR_UNSUPPORTED;

@@ -153,6 +153,9 @@ struct MummuMoe {
     void* io_y = nullptr;
     unsigned long long* hits = nullptr;  // [experts]
     int32_t* status = nullptr;      // device status word
+    // cached tensor maps (CUtensorMap, 128 B each) of the Q4_K banks as [rows, row_bytes] byte views
+    alignas(64) unsigned char q4k_map[3][128];
+    const void* q4k_map_base[3] = {nullptr, nullptr, nullptr};
     int64_t launches = 0;
     mummu::Profiler prof;
 };

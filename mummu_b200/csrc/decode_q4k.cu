@@ -26,6 +26,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace mummu {
 
@@ -49,6 +50,9 @@ struct DecodeArgs {
     int ctas_per_expert;
     int ld_out;                 // output row stride (elements)
     void* out;                  // gate/up: __half hact; down: float ys
+    int rows_per_expert;        // weight rows per expert (TMA row coordinate)
+    int ring_depth;             // TMA stages per warp
+    int32_t* status;            // handle's device status word
 };
 
 // D = A*B + C with C given separately (zero registers for the first MMA of a chain)
@@ -86,8 +90,14 @@ __device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
 }
 
 // two nibbles of a word -> half2 (1024+q) resp. (1024+16q)
-__device__ __forceinline__ uint32_t nib_lo(uint32_t w) { return (w & 0x000F000Fu) | 0x64006400u; }
-__device__ __forceinline__ uint32_t nib_hi(uint32_t w) { return (w & 0x00F000F0u) | 0x64006400u; }
+// (one three-input logic op each: (w & mask) | 0x64006400)
+__device__ __forceinline__ uint32_t and_or(uint32_t w, uint32_t mask, uint32_t bits) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(d) : "r"(w), "r"(mask), "r"(bits));
+    return d;
+}
+__device__ __forceinline__ uint32_t nib_lo(uint32_t w) { return and_or(w, 0x000F000Fu, 0x64006400u); }
+__device__ __forceinline__ uint32_t nib_hi(uint32_t w) { return and_or(w, 0x00F000F0u, 0x64006400u); }
 
 // What one lane needs from the 16-byte super-block header (f16 d, f16 dmin, 12 packed scale
 // bytes; crates/mummu/src/gguf.rs:1685-1698) for its two sub-blocks 2t and 2t+1.
@@ -244,7 +254,7 @@ __host__ __device__ inline size_t dq_smem_bytes(int nsb) {
 
 template <int NT, bool GATEUP>
 __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_kernel(DecodeArgs a) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nsb = a.K >> 8;
     // [nsb][NT][8 words][8 tokens][4 lanes-of-quad] x 16 B: (lo sub-block 4 halves | hi sub-block 4 halves)
     uint4* s_frag = reinterpret_cast<uint4*>(smem_raw);
@@ -460,7 +470,7 @@ __device__ __forceinline__ void stream_rows(const DecodeArgs& a, uint32_t frag_b
 // unit u is decoded and multiplied.
 template <int NT, bool GATEUP>
 __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_stream_kernel(DecodeArgs a) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nsb = a.K >> 8;
     uint4* s_frag = reinterpret_cast<uint4*>(smem_raw);
     __half* s_sxh = reinterpret_cast<__half*>(s_frag + (size_t)nsb * NT * 256);
@@ -501,15 +511,253 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_stream_kernel(Decode
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Streaming variant with the weights staged by the copy engine.
+//
+// The banks are described to TMA as 2-D byte tensors [expert*rows, row_bytes]; one
+// (super-block, matrix) unit of a 16-row tile is then ONE box of 16 rows x 144 bytes = 2304 B,
+// fetched by one instruction from one lane into the warp's private ring (ring_depth stages, one
+// mbarrier each), instead of six per-lane copies with their address arithmetic.  The 144-byte
+// row pitch in shared memory makes the lanes' 16-byte reads conflict free.  Each warp is its own
+// producer: after copying a stage into registers it refills that stage, so up to ring_depth
+// units are in flight per warp while one is multiplied.  The first units are requested before
+// the token tile is staged (weights do not depend on the tokens).  Waits are bounded: when one
+// runs out the warp raises the status word, stops waiting and finishes with whatever it has.
+// ------------------------------------------------------------------------------------------------
+constexpr uint32_t DQ_UNIT_BYTES = 16 * Q4K_BLOCK_BYTES;   // 2304
+constexpr uint32_t DQ_WAIT_LIMIT = 1u << 21;
+
+struct UnitRing {
+    uint32_t data;       // shared address of this warp's first stage
+    uint32_t bars;       // shared address of this warp's first mbarrier
+    int depth;
+    // consumer
+    int c_stage;
+    uint32_t c_phase;
+    bool dead;           // a wait ran out
+    // producer cursor (uniform over the warp)
+    int p_rt, p_sb, p_m, p_pass;
+    bool p_valid;
+};
+
+template <bool GATEUP>
+__device__ __forceinline__ void ring_issue(UnitRing& r, int stage, const CUtensorMap* map0, const CUtensorMap* map1,
+                                           int row_base, int rt_first, int rt_end, int nsb, int npasses, int lane) {
+    if (lane == 0) {
+        const int row = GATEUP ? row_base + r.p_rt * 16 : row_base + r.p_rt * 32 + 16 * r.p_m;
+        const uint32_t bar = r.bars + (uint32_t)stage * 8u;
+        mbar_expect_tx(bar, DQ_UNIT_BYTES);
+        tma_load_2d(r.data + (uint32_t)stage * DQ_UNIT_BYTES, (GATEUP && r.p_m) ? map1 : map0,
+                    r.p_sb * Q4K_BLOCK_BYTES, row, bar);
+    }
+    r.p_m ^= 1;
+    if (r.p_m == 0 && ++r.p_sb == nsb) {
+        r.p_sb = 0;
+        r.p_rt += DQ_WARPS;
+        if (r.p_rt >= rt_end) {
+            r.p_rt = rt_first;
+            if (++r.p_pass >= npasses) r.p_valid = false;
+        }
+    }
+}
+
+__device__ __forceinline__ void ring_take(UnitRing& r, UnitRegs& u, int g, int t, int32_t* status) {
+    const uint32_t bar = r.bars + (uint32_t)r.c_stage * 8u;
+    if (!r.dead) {
+        uint32_t i = 0;
+        while (!mbar_test(bar, r.c_phase)) {
+            if (++i > 64) __nanosleep(32);
+            if (i >= DQ_WAIT_LIMIT) {
+                r.dead = true;
+                atomicOr(status, STATUS_TIMEOUT);
+                break;
+            }
+        }
+    }
+    const uint32_t row0 = r.data + (uint32_t)r.c_stage * DQ_UNIT_BYTES + (uint32_t)(g * Q4K_BLOCK_BYTES);
+    const uint32_t row1 = row0 + 8u * Q4K_BLOCK_BYTES;
+    u.hdr[0] = lds128(row0);
+    u.qa[0] = lds128(row0 + 16 + 32 * t);
+    u.qb[0] = lds128(row0 + 32 + 32 * t);
+    u.hdr[1] = lds128(row1);
+    u.qa[1] = lds128(row1 + 16 + 32 * t);
+    u.qb[1] = lds128(row1 + 32 + 32 * t);
+    __syncwarp();   // every lane holds its copy: the stage may be refilled
+}
+
+template <int NT, int NTC, bool GATEUP>
+__device__ __forceinline__ void ring_rows(const DecodeArgs& a, UnitRing& r, const CUtensorMap* map0,
+                                          const CUtensorMap* map1, uint32_t frag_base, uint32_t sxh_base, int row_base,
+                                          int rt_first, int rt_end, int nsb, int npasses, int g, int t, int lane,
+                                          bool upper, uint32_t sel, int first_row, int npass) {
+    for (int rt = rt_first; rt < rt_end; rt += DQ_WARPS) {
+        float y[2][NTC][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NTC; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) y[mt][nt][i] = 0.0f;
+        uint32_t frag_addr = frag_base + (uint32_t)((g * 4 + t) * 16);
+        uint32_t sxh_addr = sxh_base + (uint32_t)((g * 8 + 2 * t) * 2);
+        for (int sb = 0; sb < nsb; ++sb) {
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                UnitRegs un;
+                ring_take(r, un, g, t, a.status);
+                if (r.p_valid) ring_issue<GATEUP>(r, r.c_stage, map0, map1, row_base, rt_first, rt_end, nsb, npasses, lane);
+                if (++r.c_stage == r.depth) {
+                    r.c_stage = 0;
+                    r.c_phase ^= 1u;
+                }
+                unit_terms<NT, NTC>(un, upper, sel, frag_addr, sxh_addr, y[mt]);
+            }
+            frag_addr += (uint32_t)(NT * 64 * 4 * 16);
+            sxh_addr += (uint32_t)(NT * 8 * 8 * 2);
+        }
+        // epilogue from registers: lane (g, t) holds rows g, g+8 x tokens 2t, 2t+1
+#pragma unroll
+        for (int nt = 0; nt < NTC; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int slot = nt * 8 + 2 * t + (i & 1);
+                const int row = g + ((i >> 1) << 3);
+                if (slot < npass) {
+                    const size_t orow = (size_t)(first_row + slot);
+                    if (GATEUP) {
+                        const float s0 = y[0][nt][i], s1 = y[1][nt][i];
+                        const float v = (s0 / (1.0f + expf(-s0))) * s1;
+                        reinterpret_cast<__half*>(a.out)[orow * a.ld_out + rt * 16 + row] = __float2half_rn(v);
+                    } else {
+                        float* o32 = reinterpret_cast<float*>(a.out);
+                        o32[orow * a.ld_out + rt * 32 + row] = y[0][nt][i];
+                        o32[orow * a.ld_out + rt * 32 + 16 + row] = y[1][nt][i];
+                    }
+                }
+            }
+    }
+}
+
+template <int NT>
+__host__ __device__ inline size_t dq_ring_smem_bytes(int nsb, int depth) {
+    return (size_t)nsb * NT * 4096 + (size_t)nsb * NT * 128 + 128 + (size_t)DQ_WARPS * depth * (DQ_UNIT_BYTES + 8);
+}
+
+template <int NT, bool GATEUP>
+__global__ void __launch_bounds__(DQ_THREADS, 2)
+decode_q4k_tma_kernel(DecodeArgs a, const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int nsb = a.K >> 8;
+    uint4* s_frag = reinterpret_cast<uint4*>(smem_raw);
+    __half* s_sxh = reinterpret_cast<__half*>(s_frag + (size_t)nsb * NT * 256);
+    const uint32_t frag_base = smem_u32(s_frag);
+    const uint32_t sxh_base = smem_u32(s_sxh);
+
+    const int ai = blockIdx.x / a.ctas_per_expert;
+    const int cb = blockIdx.x - ai * a.ctas_per_expert;
+    if (ai >= *a.n_active) return;
+    const int e = a.active[ai];
+    const int cnt = a.counts[e];
+    const int base = a.offsets[e];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const bool upper = t >= 2;
+    const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
+    const int rt_begin = cb * a.rb;
+    const int rt_end = min(a.n_rt, rt_begin + a.rb);
+    const int rt_first = rt_begin + warp;
+    const int npasses = (cnt + 8 * NT - 1) / (8 * NT);
+    const int row_base = e * a.rows_per_expert;
+
+    UnitRing r;
+    r.depth = a.ring_depth;
+    const uint32_t ring_base = (sxh_base + (uint32_t)(nsb * NT * 128) + 127u) & ~127u;
+    r.data = ring_base + (uint32_t)(warp * r.depth) * DQ_UNIT_BYTES;
+    r.bars = ring_base + (uint32_t)(DQ_WARPS * r.depth) * DQ_UNIT_BYTES + (uint32_t)(warp * r.depth) * 8u;
+    r.c_stage = 0;
+    r.c_phase = 0;
+    r.dead = false;
+    r.p_rt = rt_first;
+    r.p_sb = 0;
+    r.p_m = 0;
+    r.p_pass = 0;
+    r.p_valid = rt_first < rt_end && npasses > 0;
+    if (lane == 0) {
+        for (int i = 0; i < r.depth; ++i) mbar_init(r.bars + (uint32_t)i * 8u, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    // request the first units before the tokens are staged
+    for (int i = 0; i < r.depth; ++i)
+        if (r.p_valid) ring_issue<GATEUP>(r, i, &map0, &map1, row_base, rt_first, rt_end, nsb, npasses, lane);
+
+    for (int pass0 = 0; pass0 < cnt; pass0 += 8 * NT) {
+        const int npass = min(8 * NT, cnt - pass0);
+        const int nt_count = (npass + 7) >> 3;
+        __syncthreads();
+        stage_token_tile<NT>(a, s_frag, s_sxh, base + pass0, npass, nt_count, tid);
+        __syncthreads();
+
+        if (NT == 1 || nt_count == 1)
+            ring_rows<NT, 1, GATEUP>(a, r, &map0, &map1, frag_base, sxh_base, row_base, rt_first, rt_end, nsb, npasses,
+                                     g, t, lane, upper, sel, base + pass0, npass);
+        else
+            ring_rows<NT, NT, GATEUP>(a, r, &map0, &map1, frag_base, sxh_base, row_base, rt_first, rt_end, nsb, npasses,
+                                      g, t, lane, upper, sel, base + pass0, npass);
+    }
+}
+
 bool decode_q4k_supported(const MummuMoeConfig& c, int64_t tokens) {
     return c.weight_dtype == MUMMU_Q4_K && c.act_dtype == MUMMU_F16 && tokens >= 1 && tokens <= 64 &&
            c.hidden % 256 == 0 && c.inter % 256 == 0 && c.hidden <= 8192 && c.inter <= 8192;
+}
+
+// Tensor map of one Q4_K bank as a [rows, row_bytes] byte view with a 16-row x 144-byte box,
+// encoded once per bank pointer and kept in the handle.
+static int bank_map(MummuMoe* m, int which, int row_bytes, int64_t rows, const CUtensorMap** out) {
+    CUtensorMap* map = reinterpret_cast<CUtensorMap*>(m->q4k_map[which]);
+    if (m->q4k_map_base[which] != m->bank[which]) {
+        int rc = encode_tiled_2d(map, m->bank[which], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)row_bytes,
+                                 (uint64_t)rows, Q4K_BLOCK_BYTES, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+        m->q4k_map_base[which] = m->bank[which];
+    }
+    *out = map;
+    return MUMMU_OK;
+}
+
+static bool use_tma_ring() {
+    static int v = -1;
+    if (v < 0) v = getenv("MUMMU_CUDA_DECODE_NO_TMA") ? 0 : 1;
+    return v == 1;
 }
 
 template <int NT, bool GATEUP>
 static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream, cudaStream_t s,
                       const char* name) {
     const int nsb = a.K >> 8;
+    // the copy-engine ring pays off on long rows (K >= 2048); short rows keep the per-lane prefetch
+    if (stream && use_tma_ring() && nsb >= 8) {
+        // deepest ring (2..4 stages per warp) that still lets two CTAs share an SM
+        int depth = 4;
+        while (depth > 2 && 2 * (dq_ring_smem_bytes<NT>(nsb, depth) + 1024) > 227 * 1024) --depth;
+        const size_t smem = dq_ring_smem_bytes<NT>(nsb, depth);
+        if (smem <= 200 * 1024) {
+            const CUtensorMap *map0 = nullptr, *map1 = nullptr;
+            const int64_t rows = (int64_t)m->cfg.experts_local * a.rows_per_expert;
+            int rc = bank_map(m, GATEUP ? MUMMU_BANK_GATE : MUMMU_BANK_DOWN, a.row_bytes, rows, &map0);
+            if (!rc && GATEUP) rc = bank_map(m, MUMMU_BANK_UP, a.row_bytes, rows, &map1);
+            if (rc) return rc;
+            if (!GATEUP) map1 = map0;
+            a.ring_depth = depth;
+            LaunchScope scope(m, s, name);
+            MUMMU_CUDA_TRY(allow_big_smem(decode_q4k_tma_kernel<NT, GATEUP>, m->cfg.device));
+            decode_q4k_tma_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a, *map0, *map1);
+            MUMMU_CUDA_TRY(cudaGetLastError());
+            return MUMMU_OK;
+        }
+    }
     size_t smem = dq_smem_bytes<NT>(nsb);
     if (stream) smem = (size_t)nsb * NT * 4096 + (size_t)nsb * NT * 128 + (size_t)DQ_WARPS * 6 * 512;
     if (smem > 200 * 1024) {
@@ -574,6 +822,8 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     plan(g, experts_est, g_stream);
     g.ld_out = c.inter;
     g.out = m->hact;
+    g.rows_per_expert = c.inter;
+    g.status = m->status;
     int rc = nt2 ? launch_one<2, true>(m, g, experts_est, g_stream, s, "q4k_gate_up")
                  : launch_one<1, true>(m, g, experts_est, g_stream, s, "q4k_gate_up");
     if (rc) return rc;
@@ -595,6 +845,8 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     plan(d, experts_est, d_stream);
     d.ld_out = c.hidden;
     d.out = ys;
+    d.rows_per_expert = c.hidden;
+    d.status = m->status;
     return nt2 ? launch_one<2, false>(m, d, experts_est, d_stream, s, "q4k_down")
                : launch_one<1, false>(m, d, experts_est, d_stream, s, "q4k_down");
 }

@@ -27,6 +27,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace mummu {
 
@@ -55,28 +56,6 @@ struct TcArgs {
 // ------------------------------------------------------------------------------------------------
 // PTX wrappers
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
 // Bounded wait.  Returns false when the limit ran out or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
@@ -88,14 +67,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
     *abort_flag = 1;
     return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c_inner, int c_outer,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
-            "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c_inner), "r"(c_outer)
-        : "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -416,26 +387,33 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [rows, K] 16-bit row-major view, box = 64 (K) x 128 (rows), 128-byte swizzle
-static int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t k) {
+int encode_tiled_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, uint32_t elem_bytes,
+                    uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
+                    CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from this driver");
         return MUMMU_ERR_DEVICE;
     }
-    cuuint64_t dims[2] = {k, rows};
-    cuuint64_t strides[1] = {k * 2};
-    cuuint32_t box[2] = {TC_BK, TC_BM};
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * elem_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, dtype == MUMMU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-        set_error("cuTensorMapEncodeTiled failed (%d) for a [%llu, %llu] view", (int)r, (unsigned long long)rows,
-                  (unsigned long long)k);
+        set_error("cuTensorMapEncodeTiled failed (%d) for a [%llu, %llu] view", (int)r, (unsigned long long)outer,
+                  (unsigned long long)inner);
         return MUMMU_ERR_DEVICE;
     }
     return MUMMU_OK;
+}
+
+// [rows, K] 16-bit row-major view, box = 64 (K) x 128 (rows), 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t k) {
+    return encode_tiled_2d(map, base,
+                           dtype == MUMMU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, k,
+                           rows, TC_BK, TC_BM, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 bool prefill_tc_supported(const MummuMoeConfig& c, int64_t rows_total) {

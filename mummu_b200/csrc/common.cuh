@@ -156,6 +156,8 @@ struct MummuMoe {
     // cached tensor maps (CUtensorMap, 128 B each) of the Q4_K banks as [rows, row_bytes] byte views
     alignas(64) unsigned char q4k_map[3][128];
     const void* q4k_map_base[3] = {nullptr, nullptr, nullptr};
+    alignas(64) unsigned char q4k_map128[3][128];   // same views with a 128-row box
+    const void* q4k_map128_base[3] = {nullptr, nullptr, nullptr};
     int64_t launches = 0;
     mummu::Profiler prof;
 };
@@ -214,6 +216,10 @@ int launch_experts_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32
 
 // ---- decode_q4k.cu ----
 bool decode_q4k_supported(const MummuMoeConfig& c, int64_t tokens);
+// ---- decode_umma.cu ----
+bool decode_umma_supported(const MummuMoeConfig& c);
+int launch_decode_umma(MummuMoe* m, bool gateup, const void* x, const int32_t* row_token, const int32_t* counts,
+                       const int32_t* offsets, int n_experts_max, void* out, cudaStream_t s);
 int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cudaStream_t s);
 int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token, const int32_t* counts,
                            const int32_t* offsets, int64_t rows_total, float* ys, cudaStream_t s);

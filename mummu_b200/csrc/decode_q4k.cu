@@ -820,6 +820,12 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     g.n_rt = c.inter / 16;
     bool g_stream;
     plan(g, experts_est, g_stream);
+    if (g_stream && decode_umma_supported(c)) {
+        // enough routed experts to fill the GPU with 128-row tiles: tensor-core variant
+        int rc = launch_decode_umma(m, true, x, row_token, counts, offsets, experts_est, m->hact, s);
+        if (rc) return rc;
+        return launch_decode_umma(m, false, m->hact, nullptr, counts, offsets, experts_est, ys, s);
+    }
     g.ld_out = c.inter;
     g.out = m->hact;
     g.rows_per_expert = c.inter;

@@ -35,6 +35,38 @@ __device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
     return ok;
 }
 
+// One suspending probe: the thread may sleep in hardware for up to about `ns` nanoseconds
+// waiting for the phase, instead of burning issue slots in a polling loop.
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok;
+}
+
+// Bounded wait.  Returns false when `limit` probes (each suspending for at most a microsecond or
+// so) ran out (the abort flag is raised) or another role of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint32_t limit) {
+    if (mbar_test(bar, parity)) return true;
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity, 1000u)) return true;
+        if ((i & 63u) == 63u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma operands)
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+}
+
 // one 2-D tile, global -> this CTA's shared memory, completion counted in bytes on `bar`
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c_inner, int c_outer,
                                             uint32_t bar) {

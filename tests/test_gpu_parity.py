@@ -234,6 +234,73 @@ def test_q4k_decode_all_tokens_one_expert(M, cuda_lib):
     m.close()
 
 
+@pytest.fixture(scope="module")
+def olmoe_q4k_layer(M, cuda_lib):
+    """One OLMoE-sized Q4_K layer (hidden 2048, intermediate 1024, 64 experts): large enough that
+    the decode path takes its streaming kernels (128-row tiles on the tensor cores)."""
+    import torch
+    L = cuda_lib
+    H, I, E, K = 2048, 1024, 64, 8
+    router, _, _, _, x = synth.moe_layer(H, 16, E, 64, cfg_seed=12)
+    banks = []
+    for i, shape in enumerate(((E * I, H), (E * I, H), (E * H, I))):
+        w = synth.normal(900 + i, shape, 0.02)
+        banks.append(M.q4k_quantize_device(torch.from_numpy(w).cuda()).cpu().numpy())
+    return H, I, E, K, router, banks, x.astype(np.float16)
+
+
+@pytest.mark.parametrize("T", [9, 40, 64])
+def test_q4k_decode_olmoe_shape(M, cuda_lib, olmoe_q4k_layer, T):
+    L = cuda_lib
+    H, I, E, K, router, (gq, uq, dq), xh = olmoe_q4k_layer
+    m = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, gq, uq, dq)
+    y = m.forward(xh[:T], K, False).astype(np.float32)
+    want, oid, ow = O.moe_forward(xh[:T].astype(np.float32), router, gq, uq, dq, K, False, q4k=True)
+    ids, w = m.route_flat(xh[:T], K, False)
+    assert np.array_equal(ids, oid) and np.array_equal(w.view(np.uint32), ow.view(np.uint32))
+    assert rel_err(y, want) < TOL_16
+    # a token's result does not depend on its batch-mates or on the kernel variant that ran
+    # (streaming for large batches, split-K for one token): bit for bit (nn/moe.rs:2318-2338)
+    if T == 64:
+        y40 = m.forward(xh[:40], K, False)
+        y64 = m.forward(xh, K, False)
+        assert np.array_equal(y40[:40], y64[:40])
+        assert np.array_equal(m.forward(xh[:1], K, False)[0], y64[0])
+    m.close()
+
+
+@pytest.mark.parametrize("T", [9, 64])
+def test_q4k_decode_tensor_core_variant(M, cuda_lib, olmoe_q4k_layer, T, monkeypatch):
+    """The opt-in tcgen05 variant of the decode bank (weights expanded into TMEM, accumulators in
+    TMEM) against the oracle and against the default kernels."""
+    L = cuda_lib
+    H, I, E, K, router, (gq, uq, dq), xh = olmoe_q4k_layer
+    m = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, gq, uq, dq)
+    base = m.forward(xh[:T], K, False).astype(np.float32)
+    monkeypatch.setenv("MUMMU_CUDA_DECODE_UMMA", "1")
+    y = m.forward(xh[:T], K, False).astype(np.float32)
+    monkeypatch.delenv("MUMMU_CUDA_DECODE_UMMA")
+    want, _, _ = O.moe_forward(xh[:T].astype(np.float32), router, gq, uq, dq, K, False, q4k=True)
+    assert rel_err(y, want) < TOL_16
+    assert rel_err(y, base) < 2e-3          # same exact products, different summation grouping
+    m.close()
+
+
+def test_q4k_decode_olmoe_shape_crowded_experts(M, cuda_lib, olmoe_q4k_layer):
+    """Every token on the same experts: 64 rows per expert = four passes of the 16-token tile."""
+    L = cuda_lib
+    H, I, E, K, router, (gq, uq, dq), xh = olmoe_q4k_layer
+    bias = np.zeros(E, np.float32)
+    bias[[3, 5, 11, 17, 23, 31, 42, 63]] = 60.0
+    m = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, gq, uq, dq, bias=bias)
+    T = 64
+    y = m.forward(xh[:T], K, True).astype(np.float32)
+    want, oid, _ = O.moe_forward(xh[:T].astype(np.float32), router, gq, uq, dq, K, True, bias=bias, q4k=True)
+    assert set(oid.reshape(-1).tolist()) == {3, 5, 11, 17, 23, 31, 42, 63}
+    assert rel_err(y, want) < TOL_16
+    m.close()
+
+
 def test_q4k_small_golden(M, cuda_lib):
     L = cuda_lib
     gold = np.load(os.path.join(HERE, "golden", "q4k_small.npz"))

@@ -507,7 +507,7 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
     ws = None
     if world > 1 and not os.environ.get("MUMMU_EP_NCCL"):
         from mummu_b200.ep import PeerWorkspace
-        ws = PeerWorkspace(None, local_rank, world * T * k, h)     # rows move by peer stores / loads
+        ws = PeerWorkspace(None, local_rank, world * T * k, h, e)  # rows move by peer stores / loads
     for l in range(NL):
         gen.manual_seed(9000 + l)                                   # router: same on every rank
         router = (torch.randn(h, e, generator=gen, device=device) * 0.02).cpu().numpy()
@@ -563,10 +563,13 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
     l0 = sum(hd.launch_count() for _, hd in layers)
     step()
     launches_per_step = sum(hd.launch_count() for _, hd in layers) - l0
-    # decode-sized steps are launch-bound: on one GPU replay one CUDA graph per step.  Multi-GPU steps
-    # stay eager: a captured graph that holds NCCL kernels kept the process group from shutting down
+    # decode-sized steps are launch-bound: replay one CUDA graph per step.  With the ranks signalling
+    # each other through peer memory the multi-GPU step holds no NCCL kernel and is captured too (a
+    # captured graph that held NCCL kernels kept the process group from shutting down, so the NCCL
+    # exchange stays eager)
     run, graphed = step, False
-    if q4 and world == 1 and not os.environ.get("MUMMU_NO_GRAPH"):
+    device_sync = world > 1 and ws is not None and all(getattr(m, "device_sync", False) for m, _ in layers)
+    if q4 and (world == 1 or device_sync) and not os.environ.get("MUMMU_NO_GRAPH"):
         try:
             torch.cuda.synchronize()
             barrier()

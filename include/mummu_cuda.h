@@ -165,6 +165,23 @@ int32_t mummu_ep_free(void* ptr);
 int32_t mummu_ep_plan(MummuMoe* moe, const int32_t* all_counts, int32_t rank, int32_t world,
                       int32_t* dst_base, int32_t* local_counts, void* stream);
 
+/* Device-side signalling between the ranks of an expert-parallel group (one rank per GPU), so that
+ * a step needs no library collective and can be replayed from a CUDA graph.  Every rank allocates
+ * mummu_ep_sync_bytes(world, experts) with mummu_ep_alloc (which zeroes it) and maps the peers'
+ * blocks; peer_sync[r] is rank r's block as seen from this device.
+ *   mummu_ep_exchange_plan: all-gather of the per-expert row counts by peer stores + what
+ *     mummu_ep_plan computes, in one launch (replaces the counts all-gather of nn/moe.rs's host
+ *     exchange, crates/mummu/src/backend.rs:128-143).
+ *   mummu_ep_barrier: every rank's earlier work on `stream` is visible to every rank after it.
+ * Waits are bounded (about a second); on expiry the status word is raised (MUMMU_ERR_TIMEOUT from
+ * the next mummu_moe_sync) and the kernel returns.  Every rank must issue the same sequence. */
+size_t mummu_ep_sync_bytes(int32_t world, int32_t experts);
+int32_t mummu_ep_exchange_plan(MummuMoe* moe, const int32_t* counts, void* const* peer_sync,
+                               int32_t rank, int32_t world, int32_t* dst_base,
+                               int32_t* local_counts, void* stream);
+int32_t mummu_ep_barrier(MummuMoe* moe, void* const* peer_sync, int32_t rank, int32_t world,
+                         void* stream);
+
 /* Dispatch: for every sorted row p of this rank (mummu_moe_permute order) copy x[row_token[p]]
  * into the owner's receive buffer at dst_base[e] + (p - offsets[e]), with peer stores.
  * peer_recv: HOST array of `world` device pointers ([cap_rows, hidden], 16-bit activations). */

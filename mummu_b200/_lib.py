@@ -49,6 +49,10 @@ SYMBOLS = {
     "mummu_ep_free": (C.c_int32, [C.c_void_p]),
     "mummu_ep_plan": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                   C.c_void_p]),
+    "mummu_ep_sync_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
+    "mummu_ep_exchange_plan": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
+                                           C.c_void_p, C.c_void_p, C.c_void_p]),
+    "mummu_ep_barrier": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p]),
     "mummu_ep_dispatch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p]),
     "mummu_ep_combine": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p,

@@ -737,8 +737,7 @@ template <int NT, bool GATEUP>
 static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream, cudaStream_t s,
                       const char* name) {
     const int nsb = a.K >> 8;
-    // the copy-engine ring pays off on long rows (K >= 2048); short rows keep the per-lane prefetch
-    if (stream && use_tma_ring() && nsb >= 8) {
+    if (stream && use_tma_ring()) {
         // deepest ring (2..4 stages per warp) that still lets two CTAs share an SM
         int depth = 4;
         while (depth > 2 && 2 * (dq_ring_smem_bytes<NT>(nsb, depth) + 1024) > 227 * 1024) --depth;
@@ -784,11 +783,17 @@ static void plan(DecodeArgs& a, int experts_est, bool& stream) {
     stream = (int64_t)experts_est * a.n_rt >= 148 * 16;
     if (stream) {
         a.rb = DQ_WARPS;                       // one row tile per warp
-        while (a.rb * 2 <= a.n_rt && (int64_t)experts_est * (a.n_rt / (a.rb * 2)) >= 148 * 3) a.rb *= 2;
+        // two row tiles per warp as long as the CTAs still cover the SMs one and a half times:
+        // the token tile is then staged half as often (measured: 2 % on the layer)
+        while (a.rb * 2 <= a.n_rt && (int64_t)experts_est * (a.n_rt / (a.rb * 2)) * 2 >= 148 * 3) a.rb *= 2;
     } else {
         const int ks = nsb < DQ_WARPS ? nsb : DQ_WARPS, rg = DQ_WARPS / ks;
         a.rb = rg;
         while (a.rb * 2 <= a.n_rt && (int64_t)experts_est * (a.n_rt / (a.rb * 2)) >= 148 * 3) a.rb *= 2;
+    }
+    if (const char* env = getenv(a.w1 ? "MUMMU_CUDA_DECODE_RB_GATEUP" : "MUMMU_CUDA_DECODE_RB_DOWN")) {
+        const int v = atoi(env);
+        if (v >= 1 && v <= a.n_rt) a.rb = v;
     }
     a.ctas_per_expert = (a.n_rt + a.rb - 1) / a.rb;
 }

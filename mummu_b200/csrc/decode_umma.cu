@@ -36,7 +36,6 @@ namespace mummu {
 constexpr int DU_PRODUCER_WARPS = 16;            // 2 matrices x 2 chunk halves x 4 row quarters
 constexpr int DU_WARP_TMA = 16;
 constexpr int DU_WARP_MMA = 17;
-constexpr int DU_WARP_EPI = 18;                  // 18..21
 constexpr int DU_THREADS = 22 * 32;
 constexpr uint32_t DU_RAW = 128 * Q4K_BLOCK_BYTES;   // 18432
 constexpr uint32_t DU_CHUNK = 16 * 128;          // token chunk [16 tokens x 64 f16] = 2 KiB

@@ -42,6 +42,90 @@ __global__ void ep_plan_kernel(const int32_t* all_counts, int world, int rank, i
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Device-side signalling between the ranks (one rank per GPU), so that a whole expert-parallel
+// step holds no library collective and no host round trip and can be replayed from a CUDA graph.
+// Every rank owns a peer-visible block of 32-bit words, zeroed by its owner before the peers map it:
+//   [0]                  epoch of the owner's last signal (touched by the owner only)
+//   [16 .. 16+R)         flag[s]: last epoch rank s has signalled to this rank
+//   [64 .. 64+R*E)       counts_in[s][e]: rank s's per-expert row counts for the current layer
+// A signal is a system-scope release store of the sender's epoch into flag[sender] of every rank;
+// a wait polls the own flags with system-scope acquire loads until all have reached the epoch.
+// Epochs only grow, so a rank that is already one signal ahead is harmless.  Polls are bounded
+// (a second or two): when they run out the kernel raises the status word and returns.
+// ---------------------------------------------------------------------------------------------
+constexpr int EP_SYNC_FLAGS = 16, EP_SYNC_COUNTS = 64;
+constexpr uint32_t EP_WAIT_LIMIT = 1u << 23;
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// one warp: lane s talks to rank s
+__device__ void ep_signal_and_wait(const PeerTable& sync, int rank, int world, int32_t* status) {
+    const int lane = threadIdx.x & 31;
+    int32_t* own = reinterpret_cast<int32_t*>(sync.ptr[rank]);
+    int32_t epoch = 0;
+    if (lane == 0) {
+        epoch = own[0] + 1;
+        own[0] = epoch;
+    }
+    epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);
+    __threadfence_system();
+    if (lane < world) {
+        st_release_sys(reinterpret_cast<int32_t*>(sync.ptr[lane]) + EP_SYNC_FLAGS + rank, epoch);
+        const int32_t* flag = own + EP_SYNC_FLAGS + lane;
+        uint32_t polls = 0;
+        while (ld_acquire_sys(flag) - epoch < 0) {
+            if (++polls > 64) __nanosleep(200);
+            if (polls > EP_WAIT_LIMIT) {
+                atomicOr(status, STATUS_TIMEOUT);
+                break;
+            }
+        }
+    }
+    __syncwarp();
+    __threadfence_system();
+}
+
+__global__ void __launch_bounds__(32) ep_barrier_kernel(PeerTable sync, int rank, int world, int32_t* status) {
+    ep_signal_and_wait(sync, rank, world, status);
+}
+
+// counts all-gather + plan in one launch: every rank stores its counts into counts_in[rank] of
+// every rank, signals, waits for the others' counts, then computes what ep_plan_kernel computes.
+__global__ void __launch_bounds__(256) ep_exchange_plan_kernel(const int32_t* counts, PeerTable sync, int world,
+                                                               int rank, int E, int EL, int32_t* dst_base,
+                                                               int32_t* local_counts, int32_t* status) {
+    for (int idx = threadIdx.x; idx < world * E; idx += blockDim.x) {
+        const int s = idx / E, e = idx - s * E;
+        reinterpret_cast<int32_t*>(sync.ptr[s])[EP_SYNC_COUNTS + rank * E + e] = counts[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < 32) ep_signal_and_wait(sync, rank, world, status);
+    __syncthreads();
+    const volatile int32_t* all_counts = reinterpret_cast<const volatile int32_t*>(sync.ptr[rank]) + EP_SYNC_COUNTS;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int d = e / EL, le = e - d * EL;
+        int base = 0;
+        for (int l2 = 0; l2 < le; ++l2)
+            for (int s = 0; s < world; ++s) base += all_counts[s * E + d * EL + l2];
+        for (int s = 0; s < rank; ++s) base += all_counts[s * E + e];
+        dst_base[e] = base;
+    }
+    for (int le = threadIdx.x; le < EL; le += blockDim.x) {
+        int c = 0;
+        for (int s = 0; s < world; ++s) c += all_counts[s * E + rank * EL + le];
+        local_counts[le] = c;
+    }
+}
+
 // one block per sorted row p: recv_x[owner][dst_base[e] + (p - offsets[e])] = x[row_token[p]]
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* x, const int32_t* row_token,
                                                           const int32_t* offsets, const int32_t* dst_base,
@@ -126,6 +210,8 @@ int32_t mummu_ep_alloc(int32_t device, size_t bytes, void** ptr, uint8_t* handle
     MUMMU_CUDA_TRY(cudaGetDevice(&prev));
     if (prev != device) MUMMU_CUDA_TRY(cudaSetDevice(device));
     cudaError_t err = cudaMalloc(ptr, bytes);
+    if (err == cudaSuccess) err = cudaMemset(*ptr, 0, bytes);
+    if (err == cudaSuccess) err = cudaDeviceSynchronize();
     cudaIpcMemHandle_t h;
     if (err == cudaSuccess) err = cudaIpcGetMemHandle(&h, *ptr);
     if (prev != device) cudaSetDevice(prev);
@@ -176,6 +262,48 @@ int32_t mummu_ep_plan(MummuMoe* m, const int32_t* all_counts, int32_t rank, int3
     LaunchScope scope(m, s, "ep_plan");
     ep_plan_kernel<<<1, 256, 0, s>>>(all_counts, world, rank, m->cfg.experts, m->cfg.experts_local, dst_base,
                                      local_counts);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+static int ep_check_ranks(MummuMoe* m, int32_t rank, int32_t world, const char* who) {
+    MUMMU_REQUIRE(world >= 1 && world <= EP_MAX_RANKS && rank >= 0 && rank < world &&
+                      m->cfg.experts % world == 0 && m->cfg.experts_local == m->cfg.experts / world,
+                  "%s: rank %d of %d with %d local experts of %d", who, rank, world, m->cfg.experts_local,
+                  m->cfg.experts);
+    return MUMMU_OK;
+}
+
+size_t mummu_ep_sync_bytes(int32_t world, int32_t experts) {
+    return (size_t)(EP_SYNC_COUNTS + (size_t)world * experts) * 4;
+}
+
+int32_t mummu_ep_exchange_plan(MummuMoe* m, const int32_t* counts, void* const* peer_sync, int32_t rank,
+                               int32_t world, int32_t* dst_base, int32_t* local_counts, void* stream) {
+    MUMMU_REQUIRE(m && counts && peer_sync && dst_base && local_counts, "mummu_ep_exchange_plan: null argument");
+    int rc = ep_check_ranks(m, rank, world, "mummu_ep_exchange_plan");
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(m->mu);
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    PeerTable t{};
+    for (int i = 0; i < world; ++i) t.ptr[i] = peer_sync[i];
+    LaunchScope scope(m, s, "ep_exchange_plan");
+    ep_exchange_plan_kernel<<<1, 256, 0, s>>>(counts, t, world, rank, m->cfg.experts, m->cfg.experts_local, dst_base,
+                                              local_counts, m->status);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+int32_t mummu_ep_barrier(MummuMoe* m, void* const* peer_sync, int32_t rank, int32_t world, void* stream) {
+    MUMMU_REQUIRE(m && peer_sync, "mummu_ep_barrier: null argument");
+    int rc = ep_check_ranks(m, rank, world, "mummu_ep_barrier");
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(m->mu);
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    PeerTable t{};
+    for (int i = 0; i < world; ++i) t.ptr[i] = peer_sync[i];
+    LaunchScope scope(m, s, "ep_barrier");
+    ep_barrier_kernel<<<1, 32, 0, s>>>(t, rank, world, m->status);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }

@@ -174,19 +174,35 @@ __device__ void warp_softmax_topk(const RouterArgs& a, int t, float* sm_v, float
 // One block (256 threads) builds, for at most 1024 (token, slot) pairs, everything permute_kernel
 // builds: counts, offsets, the heaviest-first active list, row_token and pos (stable: ascending
 // token inside an expert).  Called by the last block of router_kernel; scratch is that block's
-// dynamic shared memory, free by then.
+// dynamic shared memory, free by then.  Counting sort in three parallel steps: per 32-pair chunk
+// a histogram by expert (warp match), an exclusive prefix over the chunks per expert, then
+// pos = offset[expert] + pairs of that expert in earlier chunks + rank inside the chunk.
 __device__ void fused_permute(const RouterArgs& a, unsigned char* smem_raw) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = a.T * a.k, E = a.E;
-    int32_t* ids_s = reinterpret_cast<int32_t*>(smem_raw);      // [n]
-    int32_t* cnt_s = ids_s + n;                                  // [E]
+    const int chunks = (n + 31) >> 5;
+    int32_t* ids_s = reinterpret_cast<int32_t*>(smem_raw);      // [chunks * 32]
+    int32_t* cnt_s = ids_s + chunks * 32;                        // [E]
     int32_t* off_s = cnt_s + E;                                  // [E + 1]
-    for (int i = tid; i < E; i += R_THREADS) cnt_s[i] = 0;
+    int32_t* hist = off_s + E + 1;                               // [chunks][E] -> exclusive prefix over chunks
+    for (int i = tid; i < chunks * E; i += R_THREADS) hist[i] = 0;
     __syncthreads();
-    for (int i = tid; i < n; i += R_THREADS) {
-        const int e = __ldcg(a.ids + i);
+    for (int c = warp; c < chunks; c += R_THREADS / 32) {
+        const int i = c * 32 + lane;
+        const int e = i < n ? __ldcg(a.ids + i) : -1;
         ids_s[i] = e;
-        atomicAdd(cnt_s + e, 1);
+        const unsigned same = __match_any_sync(0xFFFFFFFFu, e);
+        if (e >= 0 && (same & ((1u << lane) - 1u)) == 0) hist[c * E + e] = __popc(same);   // group leader
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += R_THREADS) {
+        int run = 0;
+        for (int c = 0; c < chunks; ++c) {
+            const int h = hist[c * E + e];
+            hist[c * E + e] = run;
+            run += h;
+        }
+        cnt_s[e] = run;
     }
     __syncthreads();
     if (warp == 0) {
@@ -206,7 +222,6 @@ __device__ void fused_permute(const RouterArgs& a, unsigned char* smem_raw) {
         if (lane == 0) off_s[E] = acc;
     }
     __syncthreads();
-    int nz_total = 0;
     for (int e = tid; e < E; e += R_THREADS) {
         const int c = cnt_s[e];
         a.p_counts[e] = c;
@@ -221,23 +236,19 @@ __device__ void fused_permute(const RouterArgs& a, unsigned char* smem_raw) {
         }
     }
     if (tid == 0) {
+        int nz_total = 0;
         for (int e = 0; e < E; ++e) nz_total += cnt_s[e] > 0;
         a.p_offsets[E] = off_s[E];
         *a.p_n_active = nz_total;
     }
-    for (int e = warp; e < E; e += R_THREADS / 32) {
-        if (cnt_s[e] == 0) continue;
-        int running = off_s[e];
-        for (int base = 0; base < n; base += 32) {
-            const int i = base + lane;
-            const bool hit = i < n && ids_s[i] == e;
-            const unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
-            if (hit) {
-                const int p = running + __popc(ballot & ((1u << lane) - 1u));
-                a.p_row_token[p] = i / a.k;
-                a.p_pos[i] = p;
-            }
-            running += __popc(ballot);
+    for (int c = warp; c < chunks; c += R_THREADS / 32) {
+        const int i = c * 32 + lane;
+        const int e = ids_s[i];
+        const unsigned same = __match_any_sync(0xFFFFFFFFu, e);
+        if (e >= 0) {
+            const int p = off_s[e] + hist[c * E + e] + __popc(same & ((1u << lane) - 1u));
+            a.p_row_token[p] = i / a.k;
+            a.p_pos[i] = p;
         }
     }
 }
@@ -245,22 +256,47 @@ __device__ void fused_permute(const RouterArgs& a, unsigned char* smem_raw) {
 // grid (expert slices, token tiles).  Each block stages its 8-expert slice of W and its token
 // tile of x in shared memory, computes the logits in the fixed lane order, and the block that
 // finishes a token tile last runs softmax + top-k for that tile.
-template <typename TX, int TPT>
+// TR (hidden % 32 == 0, experts % 8 == 0, 16-byte aligned 16-bit activations): W and x sit in
+// shared memory transposed, one padded row per (lane j, expert) resp. (token, lane j), so that a
+// thread's chain reads four consecutive steps with one 128-bit load; same sums in the same order.
+template <typename TX, int TPT, bool TR>
 __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int TT = 4 * TPT;
     const int H = a.H, E = a.E;
     const int H8 = H & ~7;
-    float* Ws = reinterpret_cast<float*>(smem_raw);           // [H8][8]
-    float* xs = Ws + (size_t)H8 * R_ES;                        // [TT][H]
-    float* parts = xs + (size_t)TT * H;                        // [TT][8][8]
+    const int S = (H >> 3) + 4;                                // padded row of the transposed layout
+    float* Ws = reinterpret_cast<float*>(smem_raw);           // [H8][8]        | TR: [8 j][8 e][S]
+    float* xs = Ws + (TR ? (size_t)64 * S : (size_t)H8 * R_ES);   // [TT][H]    | TR: [TT][8 j][S]
+    float* parts = xs + (TR ? (size_t)TT * 8 * S : (size_t)TT * H);   // [TT][8][8]
     float* tk = parts + TT * 64;                               // top-k scratch, 8 warps
     const int tid = threadIdx.x;
     const int e0 = blockIdx.x * R_ES;
     const int t0 = blockIdx.y * TT;
     const TX* x = reinterpret_cast<const TX*>(a.x);
 
-    if ((E & 3) == 0 && e0 + R_ES <= E) {
+    if constexpr (TR) {
+        const int steps = H >> 3;                              // i = 0 .. steps-1, row h = 8 i + j
+        // W: a warp takes 32 consecutive i of one j; each lane reads its row's 8 experts (32 B)
+        for (int idx = tid; idx < H; idx += R_THREADS) {
+            const int j = idx / steps, i = idx - j * steps;
+            const float4* src = reinterpret_cast<const float4*>(a.w + (size_t)(i * 8 + j) * E + e0);
+            const float4 w0 = __ldg(src), w1 = __ldg(src + 1);
+            float* dst = Ws + (size_t)(j * 8) * S + i;
+            dst[0 * S] = w0.x; dst[1 * S] = w0.y; dst[2 * S] = w0.z; dst[3 * S] = w0.w;
+            dst[4 * S] = w1.x; dst[5 * S] = w1.y; dst[6 * S] = w1.z; dst[7 * S] = w1.w;
+        }
+        for (int idx = tid; idx < TT * steps; idx += R_THREADS) {
+            const int tt = idx / steps, i = idx - tt * steps;
+            const int t = t0 + tt;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (t < a.T) v = *reinterpret_cast<const uint4*>(x + (size_t)t * H + (size_t)i * 8);
+            const TX* hv = reinterpret_cast<const TX*>(&v);
+            float* dst = xs + (size_t)(tt * 8) * S + i;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) dst[u * S] = to_f32(hv[u]);
+        }
+    } else if ((E & 3) == 0 && e0 + R_ES <= E) {
         // 8 experts of one row = two aligned float4
         const float4* w4 = reinterpret_cast<const float4*>(a.w);
         float4* Ws4 = reinterpret_cast<float4*>(Ws);
@@ -275,7 +311,8 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
             Ws[idx] = e < E ? a.w[(size_t)i * E + e] : 0.0f;
         }
     }
-    if (sizeof(TX) == 2 && (H & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    if constexpr (TR) {
+    } else if (sizeof(TX) == 2 && (H & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
         const int groups = H >> 3;
 #pragma unroll 4
         for (int idx = tid; idx < TT * groups; idx += R_THREADS) {
@@ -302,13 +339,29 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
 #pragma unroll
     for (int u = 0; u < TPT; ++u) acc[u] = 0.0f;
     const int iters = H8 >> 3;
+    if constexpr (TR) {
+        const float4* wrow = reinterpret_cast<const float4*>(Ws + (size_t)(j * 8 + el) * S);
 #pragma unroll 4
-    for (int i = 0; i < iters; ++i) {
-        float wv = Ws[(i * 8 + j) * R_ES + el];
+        for (int i4 = 0; i4 < (iters >> 2); ++i4) {
+            const float4 wv = wrow[i4];
 #pragma unroll
-        for (int u = 0; u < TPT; ++u) {
-            float xv = xs[(size_t)(tg + 4 * u) * H + i * 8 + j];
-            acc[u] = __fmaf_rn(xv, wv, acc[u]);
+            for (int u = 0; u < TPT; ++u) {
+                const float4 xv = reinterpret_cast<const float4*>(xs + (size_t)((tg + 4 * u) * 8 + j) * S)[i4];
+                acc[u] = __fmaf_rn(xv.x, wv.x, acc[u]);
+                acc[u] = __fmaf_rn(xv.y, wv.y, acc[u]);
+                acc[u] = __fmaf_rn(xv.z, wv.z, acc[u]);
+                acc[u] = __fmaf_rn(xv.w, wv.w, acc[u]);
+            }
+        }
+    } else {
+#pragma unroll 4
+        for (int i = 0; i < iters; ++i) {
+            float wv = Ws[(i * 8 + j) * R_ES + el];
+#pragma unroll
+            for (int u = 0; u < TPT; ++u) {
+                float xv = xs[(size_t)(tg + 4 * u) * H + i * 8 + j];
+                acc[u] = __fmaf_rn(xv, wv, acc[u]);
+            }
         }
     }
 #pragma unroll
@@ -629,6 +682,19 @@ static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
     }
     int tpt = a.T >= 2048 ? 4 : (a.T >= 256 ? 2 : 1);
     while (tpt > 1 && router_smem(a.H, a.E, a.k, 4 * tpt) > 200 * 1024) tpt >>= 1;
+    if (tpt == 1 && sizeof(TX) == 2 && a.H % 32 == 0 && a.E % R_ES == 0 &&
+        (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && !getenv("MUMMU_CUDA_ROUTER_PLAIN")) {
+        const int S = a.H / 8 + 4;
+        const size_t smem_t = ((size_t)64 * S + (size_t)4 * 8 * S + 4 * 64 + (size_t)8 * (a.E + 2 * a.k)) * 4;
+        if (smem_t <= 200 * 1024) {
+            dim3 grid_t(a.E / R_ES, (a.T + 3) / 4);
+            LaunchScope scope(m, s, "router");
+            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 1, true>, m->cfg.device));
+            router_kernel<TX, 1, true><<<grid_t, R_THREADS, smem_t, s>>>(a);
+            MUMMU_CUDA_TRY(cudaGetLastError());
+            return MUMMU_OK;
+        }
+    }
     size_t smem = router_smem(a.H, a.E, a.k, 4 * tpt);
     if (smem > 220 * 1024) {
         set_error("router: hidden %d too wide for the shared-memory staged router", a.H);
@@ -638,16 +704,16 @@ static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
     LaunchScope scope(m, s, "router");
     switch (tpt) {
         case 4:
-            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 4>, m->cfg.device));
-            router_kernel<TX, 4><<<grid, R_THREADS, smem, s>>>(a);
+            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 4, false>, m->cfg.device));
+            router_kernel<TX, 4, false><<<grid, R_THREADS, smem, s>>>(a);
             break;
         case 2:
-            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 2>, m->cfg.device));
-            router_kernel<TX, 2><<<grid, R_THREADS, smem, s>>>(a);
+            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 2, false>, m->cfg.device));
+            router_kernel<TX, 2, false><<<grid, R_THREADS, smem, s>>>(a);
             break;
         default:
-            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 1>, m->cfg.device));
-            router_kernel<TX, 1><<<grid, R_THREADS, smem, s>>>(a);
+            MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 1, false>, m->cfg.device));
+            router_kernel<TX, 1, false><<<grid, R_THREADS, smem, s>>>(a);
             break;
     }
     MUMMU_CUDA_TRY(cudaGetLastError());
@@ -661,10 +727,11 @@ int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int nor
         set_error("router: %d experts exceed the %d this build selects over", c.experts, 32 * R_MAXV);
         return MUMMU_ERR_UNSUPPORTED;
     }
-    // fused grouping pays off only for a handful of pairs (one block does it): at most 128, the narrow
-    // kernel, and room in its shared memory
-    const bool fuse = fuse_permute && counts == m->counts && tokens < 256 && tokens * top_k <= 128 &&
-                      (size_t)(tokens * top_k + 2 * c.experts + 2) * 4 <= router_smem(c.hidden, c.experts, top_k, 4);
+    // fused grouping: one block sorts up to 1024 pairs in the narrow kernel's shared memory
+    const int64_t pairs = tokens * top_k, pair_chunks = (pairs + 31) / 32;
+    const bool fuse = fuse_permute && counts == m->counts && tokens < 256 && pairs <= 1024 &&
+                      (size_t)(pair_chunks * 32 + 2 * c.experts + 2 + pair_chunks * c.experts) * 4 <=
+                          router_smem(c.hidden, c.experts, top_k, 4);
     if (fuse_permute && !fuse) return MUMMU_ERR_UNSUPPORTED;       // caller falls back to the separate launch
     if (counts && !fuse) MUMMU_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int32_t) * c.experts, s));
     RouterArgs a;
@@ -933,13 +1000,13 @@ __global__ void __launch_bounds__(256) combine_vec8_kernel(const TY* ys, const i
     __syncthreads();
     for (int h = (blockIdx.y * blockDim.x + threadIdx.x) * 8; h < H; h += gridDim.y * blockDim.x * 8) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int r0 = 0; r0 < top_k; r0 += 4) {
-            float v[4][8];
+        for (int r0 = 0; r0 < top_k; r0 += 8) {
+            float v[8][8];   // eight experts' rows in flight at once
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 8; ++u)
                 if (r0 + u < top_k) load8(ys + (size_t)s_pos[r0 + u] * H + h, v[u]);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 8; ++u)
                 if (r0 + u < top_k) {
                     const float wv = s_w[r0 + u];
 #pragma unroll
@@ -957,19 +1024,21 @@ static int launch_combine_y(MummuMoe* m, const void* ys, const int32_t* ids, con
     size_t smem = (size_t)top_k * 8;
     const int H = m->cfg.hidden;
     const bool vec = (H & 7) == 0 && (reinterpret_cast<uintptr_t>(ys) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-    const dim3 grid((unsigned)tokens, vec ? (tokens < 512 ? (unsigned)((H / 8 + 255) / 256) : 1u)
+    // few tokens: 64-thread blocks so that a decode batch still spreads over the SMs
+    const unsigned vthreads = tokens < 128 ? 64u : 256u;
+    const dim3 grid((unsigned)tokens, vec ? (tokens < 512 ? (unsigned)((H / 8 + vthreads - 1) / vthreads) : 1u)
                                           : (tokens < 512 ? (unsigned)((H + 255) / 256) : 1u));
     LaunchScope scope(m, s, "combine");
     if (vec) {
         switch (m->cfg.act_dtype) {
             case MUMMU_F32:
-                combine_vec8_kernel<TY, float><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
+                combine_vec8_kernel<TY, float><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
                 break;
             case MUMMU_F16:
-                combine_vec8_kernel<TY, __half><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__half*)out);
+                combine_vec8_kernel<TY, __half><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__half*)out);
                 break;
             case MUMMU_BF16:
-                combine_vec8_kernel<TY, __nv_bfloat16><<<grid, 256, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__nv_bfloat16*)out);
+                combine_vec8_kernel<TY, __nv_bfloat16><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__nv_bfloat16*)out);
                 break;
         }
         MUMMU_CUDA_TRY(cudaGetLastError());
@@ -1395,9 +1464,9 @@ static int route_noalloc_launch(RouterArgs& a, int device, cudaStream_t s) {
         set_error("mummu_moe_route_noalloc: hidden %d too wide for the shared-memory staged router", a.H);
         return MUMMU_ERR_UNSUPPORTED;
     }
-    MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 1>, device));
+    MUMMU_CUDA_TRY(allow_big_smem(router_kernel<TX, 1, false>, device));
     dim3 grid((a.E + R_ES - 1) / R_ES, (a.T + 3) / 4);
-    router_kernel<TX, 1><<<grid, R_THREADS, smem, s>>>(a);
+    router_kernel<TX, 1, false><<<grid, R_THREADS, smem, s>>>(a);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }

@@ -16,6 +16,8 @@ ranks with the gloo backend; only steps 1, 2, 5 and 6 touch the CUDA library.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Optional
 
@@ -57,11 +59,12 @@ def plan_exchange(all_counts: np.ndarray, rank: int, world: int) -> ExchangePlan
 
 
 class PeerWorkspace:
-    """The two peer-visible buffers of a rank (rows received for its experts, and their outputs),
-    shared by every layer of a stack: allocated by the CUDA library, exported as IPC handles,
-    exchanged through the process group, mapped by every peer."""
+    """The peer-visible buffers of a rank (rows received for its experts, their outputs, and the
+    block of flags and counts the ranks signal each other through), shared by every layer of a
+    stack: allocated by the CUDA library, exported as IPC handles, exchanged through the process
+    group, mapped by every peer."""
 
-    def __init__(self, group, device: int, cap_rows: int, hidden: int):
+    def __init__(self, group, device: int, cap_rows: int, hidden: int, experts: int = 256):
         import ctypes as C
         import torch.distributed as dist
         from . import _lib as L
@@ -69,9 +72,10 @@ class PeerWorkspace:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.cap_rows, self.bytes = cap_rows, cap_rows * hidden * 2
         self.own, self.opened, handles = [], [], []
-        for _ in range(2):
+        sync_bytes = int(L.lib.mummu_ep_sync_bytes(self.world, experts))
+        for nbytes in (self.bytes, self.bytes, sync_bytes):
             ptr, h = C.c_void_p(), C.create_string_buffer(64)
-            rc = L.lib.mummu_ep_alloc(device, self.bytes, C.byref(ptr), h)
+            rc = L.lib.mummu_ep_alloc(device, nbytes, C.byref(ptr), h)
             if rc:
                 raise RuntimeError(L.last_error())
             self.own.append(ptr.value)
@@ -79,7 +83,7 @@ class PeerWorkspace:
         gathered = [None] * self.world
         dist.all_gather_object(gathered, handles, group=group)
         self.tables = []
-        for which in range(2):
+        for which in range(3):
             table = (C.c_void_p * self.world)()
             for r in range(self.world):
                 if r == self.rank:
@@ -92,8 +96,11 @@ class PeerWorkspace:
                     self.opened.append(ptr.value)
                     table[r] = ptr.value
             self.tables.append(table)
-        self.recv_table, self.ys_table = self.tables
-        self.recv_ptr, self.ys_ptr = self.own
+        self.recv_table, self.ys_table, self.sync_table = self.tables
+        self.recv_ptr, self.ys_ptr, self.sync_ptr = self.own
+        self.experts = experts
+        if group is not None or dist.is_initialized():
+            dist.barrier(group=group)          # every peer has mapped every (zeroed) block
 
     def close(self):
         for p in self.opened:
@@ -128,6 +135,9 @@ class ExpertParallelMoe:
         import torch as _t  # noqa: F401
         # scratch for the local experts must hold the rows that can arrive: every rank's tokens * k
         self.workspace = workspace
+        # flags and counts in peer memory instead of NCCL calls (MUMMU_EP_NCCL_SYNC=1 keeps NCCL)
+        self.device_sync = (workspace is not None and cfg.num_experts <= getattr(workspace, "experts", 0)
+                            and not os.environ.get("MUMMU_EP_NCCL_SYNC"))
         self.moe = moe.SparseMoeConfig(cfg.hidden_size, cfg.expert_intermediate_size, cfg.num_experts,
                                        cfg.num_experts_per_tok).init(
             device=dev, act_dtype=act_dtype, weight_dtype=weight_dtype,
@@ -145,7 +155,10 @@ class ExpertParallelMoe:
         self.moe.set_banks(gate, up, down)
 
     def _barrier(self):
-        self.dist.all_reduce(self._flag, group=self.group)       # device-side: nobody waits on the host
+        if self.device_sync:
+            self.moe.ep_barrier(self.workspace.sync_table, self.rank, self.world)
+        else:
+            self.dist.all_reduce(self._flag, group=self.group)   # device-side: nobody waits on the host
 
     def forward_p2p(self, x, top_k: int, norm_topk_prob: bool):
         import torch
@@ -158,10 +171,14 @@ class ExpertParallelMoe:
         counts, offsets = torch.empty(E, **i32), torch.empty(E + 1, **i32)
         row_token, pos = torch.empty(T * top_k, **i32), torch.empty(T * top_k, **i32)
         m.permute(ids, counts, offsets, row_token, pos)
-        all_counts = torch.empty(R, E, **i32)
-        dist.all_gather_into_tensor(all_counts, counts, group=self.group)
         dst_base, local_counts = torch.empty(E, **i32), torch.empty(self.el, **i32)
-        m.ep_plan(all_counts, self.rank, R, dst_base, local_counts)
+        if self.device_sync:
+            # counts all-gather, plan and both barriers on the device: the step holds no collective
+            m.ep_exchange_plan(counts, ws.sync_table, self.rank, R, dst_base, local_counts)
+        else:
+            all_counts = torch.empty(R, E, **i32)
+            dist.all_gather_into_tensor(all_counts, counts, group=self.group)
+            m.ep_plan(all_counts, self.rank, R, dst_base, local_counts)
         m.ep_dispatch(x, row_token, offsets, dst_base, ws.recv_table, R)
         self._barrier()                                           # every rank's rows have landed
         m.experts_grouped_raw(ws.recv_ptr, local_counts, T * top_k * R, ws.ys_ptr)

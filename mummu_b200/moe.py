@@ -292,6 +292,14 @@ class SparseMoe:
         _check(L.lib.mummu_ep_plan(self._h, all_counts.data_ptr(), rank, world, dst_base.data_ptr(),
                                    local_counts.data_ptr(), _torch_stream()))
 
+    def ep_exchange_plan(self, counts, sync_table, rank: int, world: int, dst_base, local_counts) -> None:
+        """Counts all-gather by peer stores + plan, one launch, no collective library."""
+        _check(L.lib.mummu_ep_exchange_plan(self._h, counts.data_ptr(), sync_table, rank, world,
+                                            dst_base.data_ptr(), local_counts.data_ptr(), _torch_stream()))
+
+    def ep_barrier(self, sync_table, rank: int, world: int) -> None:
+        _check(L.lib.mummu_ep_barrier(self._h, sync_table, rank, world, _torch_stream()))
+
     def ep_dispatch(self, x, row_token, offsets, dst_base, peer_table, world: int) -> None:
         _check(L.lib.mummu_ep_dispatch(self._h, x.data_ptr(), row_token.data_ptr(), offsets.data_ptr(),
                                        dst_base.data_ptr(), peer_table, world, row_token.numel(),

@@ -34,7 +34,7 @@ def _worker(rank, world, port, q, act, wdt_name):
         el = E // world
         cfg = moe.SparseMoeConfig(H, I, E, K)
         from mummu_b200.ep import PeerWorkspace
-        ws = PeerWorkspace(None, rank, world * T * K, H) if act == "p2p" else None
+        ws = PeerWorkspace(None, rank, world * T * K, H, E) if act == "p2p" else None
         ep = ExpertParallelMoe(cfg, device=rank, act_dtype=act_code, weight_dtype=wcode, max_tokens=T, workspace=ws)
         ep.set_router(router)
         sl = slice(rank * el, (rank + 1) * el)
@@ -42,6 +42,7 @@ def _worker(rank, world, port, q, act, wdt_name):
         xd = torch.from_numpy(x).cuda().to(tdt)
         y_ep = ep.forward(xd, K, False)
         y_ep2 = ep.forward(xd, K, False)
+        ep.moe.sync()                      # raises if a bounded device-side wait ran out
         # the same layer, all experts on this GPU
         single = cfg.init(device=rank, act_dtype=act_code, weight_dtype=wcode, max_tokens=T)
         single.set_router(router)

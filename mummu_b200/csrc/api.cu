@@ -278,7 +278,7 @@ int32_t mummu_moe_destroy(MummuMoe* m) {
         DeviceGuard guard(m->cfg.device);
         if (m->stream) cudaStreamSynchronize(m->stream);
         free_scratch(m);
-        cudaFree(m->router_w); cudaFree(m->router_bias);
+        cudaFree(m->router_w); cudaFree(m->router_wt); cudaFree(m->router_bias);
         for (int b = 0; b < 3; ++b) cudaFree(m->bank[b]);
         cudaFree(m->counts); cudaFree(m->offsets); cudaFree(m->hits); cudaFree(m->status);
         cudaFree(m->active); cudaFree(m->n_active);
@@ -309,6 +309,20 @@ int32_t mummu_moe_set_router(MummuMoe* m, const void* w, int32_t dtype, int32_t 
             host[(size_t)i * E + e] = v;
         }
     MUMMU_CUDA_TRY(cudaMemcpy(m->router_w, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice));
+    if (H % 32 == 0 && E % 8 == 0) {
+        // image of the decode router's shared-memory slice, so that a block fetches its 8 experts
+        // with one bulk copy instead of 2048 scattered 32-byte reads
+        const int S = H / 8 + 4;
+        std::vector<float> img((size_t)E * 8 * S, 0.0f);
+        for (int e = 0; e < E; ++e)
+            for (int i = 0; i < H; ++i)
+                img[((size_t)(e / 8) * 64 + (size_t)(i % 8) * 8 + (e % 8)) * S + i / 8] = host[(size_t)i * E + e];
+        if (!m->router_wt) {
+            int rc = dev_alloc(&m->router_wt, img.size());
+            if (rc) return rc;
+        }
+        MUMMU_CUDA_TRY(cudaMemcpy(m->router_wt, img.data(), img.size() * sizeof(float), cudaMemcpyHostToDevice));
+    }
     if (bias) {
         if (!m->router_bias) {
             int rc = dev_alloc(&m->router_bias, (size_t)E);

@@ -127,6 +127,9 @@ struct MummuMoe {
     cudaStream_t stream = nullptr;
 
     float* router_w = nullptr;      // f32 [hidden, experts]
+    // the same weights as the decode router's shared-memory image: [experts/8][8 lanes j][8 experts]
+    // [hidden/8 + 4] (value of row 8i+j at index i), present when hidden % 32 == 0, experts % 8 == 0
+    float* router_wt = nullptr;
     float* router_bias = nullptr;   // f32 [experts] or null
     void* bank[3] = {nullptr, nullptr, nullptr};
     size_t bank_bytes[3] = {0, 0, 0};

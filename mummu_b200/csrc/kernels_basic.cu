@@ -14,6 +14,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace mummu {
 
@@ -58,6 +59,7 @@ constexpr int R_MAXV = 8;        // probabilities per lane in the top-k stage: e
 struct RouterArgs {
     const void* x;
     const float* w;      // [H, E]
+    const float* wt;     // shared-memory image of the 8-expert slices, or null
     const float* bias;   // [E] or null
     float* logits;       // [T, E] scratch
     int32_t* tile_done;  // [tiles] zero on entry, zero on exit
@@ -80,15 +82,16 @@ struct RouterArgs {
 
 // One warp: softmax over one token's logits, then top-k.  sm_v: E floats, sm_vals: k floats,
 // sm_ids: k ints (all private to the warp).
+template <int NV = R_MAXV>   // probabilities per lane: experts <= 32 * NV
 __device__ void warp_softmax_topk(const RouterArgs& a, int t, float* sm_v, float* sm_vals,
                                   int32_t* sm_ids) {
     const int lane = threadIdx.x & 31;
     const unsigned full = 0xFFFFFFFFu;
     const float* lrow = a.logits + (size_t)t * a.E;
-    float l[R_MAXV], p[R_MAXV];
+    float l[NV], p[NV];
     bool bad = false;
 #pragma unroll
-    for (int i = 0; i < R_MAXV; ++i) {
+    for (int i = 0; i < NV; ++i) {
         int e = lane + 32 * i;
         l[i] = e < a.E ? __ldcg(lrow + e) : -FLT_MAX;
         if (e < a.E && !isfinite(l[i])) bad = true;
@@ -108,11 +111,11 @@ __device__ void warp_softmax_topk(const RouterArgs& a, int t, float* sm_v, float
     }
     float mx = -FLT_MAX;
 #pragma unroll
-    for (int i = 0; i < R_MAXV; ++i) mx = fmaxf(mx, l[i]);
+    for (int i = 0; i < NV; ++i) mx = fmaxf(mx, l[i]);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, off));
 #pragma unroll
-    for (int i = 0; i < R_MAXV; ++i) {
+    for (int i = 0; i < NV; ++i) {
         int e = lane + 32 * i;
         if (e < a.E) {
             p[i] = exp_det(__fsub_rn(l[i], mx));
@@ -124,7 +127,7 @@ __device__ void warp_softmax_topk(const RouterArgs& a, int t, float* sm_v, float
 #pragma unroll 8
     for (int e = 0; e < a.E; ++e) total = __fadd_rn(total, sm_v[e]);
 #pragma unroll
-    for (int i = 0; i < R_MAXV; ++i) {
+    for (int i = 0; i < NV; ++i) {
         int e = lane + 32 * i;
         p[i] = e < a.E ? __fdiv_rn(p[i], total) : -1.0f;
     }
@@ -133,7 +136,7 @@ __device__ void warp_softmax_topk(const RouterArgs& a, int t, float* sm_v, float
         float bp = -2.0f;
         int be = INT_MAX;
 #pragma unroll
-        for (int i = 0; i < R_MAXV; ++i) {
+        for (int i = 0; i < NV; ++i) {
             if (p[i] > bp) {
                 bp = p[i];
                 be = lane + 32 * i;
@@ -149,7 +152,7 @@ __device__ void warp_softmax_topk(const RouterArgs& a, int t, float* sm_v, float
             }
         }
 #pragma unroll
-        for (int i = 0; i < R_MAXV; ++i)
+        for (int i = 0; i < NV; ++i)
             if (be == lane + 32 * i) p[i] = -1.0f;
         denom = __fadd_rn(denom, bp);
         if (lane == 0) {
@@ -222,24 +225,35 @@ __device__ void fused_permute(const RouterArgs& a, unsigned char* smem_raw) {
         if (lane == 0) off_s[E] = acc;
     }
     __syncthreads();
-    for (int e = tid; e < E; e += R_THREADS) {
+    // heaviest-first order: rank of expert e = experts that come before it; four threads per expert
+    // each compare against a quarter of the others
+    for (int q0 = 0; q0 < 4 * E; q0 += R_THREADS) {       // every thread makes every trip (shuffles)
+        const int q = q0 + tid;
+        const bool valid = q < 4 * E;
+        const int e = valid ? q >> 2 : 0, part = q & 3;
         const int c = cnt_s[e];
-        a.p_counts[e] = c;
-        a.p_offsets[e] = off_s[e];
-        if (c > 0) {
-            int rank = 0;
-            for (int i = 0; i < E; ++i) {
-                const int ci = cnt_s[i];
-                rank += (ci > c || (ci == c && i < e)) ? 1 : 0;
-            }
-            a.p_active[rank] = e;
+        int rank = 0;
+        for (int i = part; i < E; i += 4) {
+            const int ci = cnt_s[i];
+            rank += (ci > c || (ci == c && i < e)) ? 1 : 0;
+        }
+        rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 1);
+        rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 2);
+        if (valid && part == 0) {
+            a.p_counts[e] = c;
+            a.p_offsets[e] = off_s[e];
+            if (c > 0) a.p_active[rank] = e;
         }
     }
-    if (tid == 0) {
-        int nz_total = 0;
-        for (int e = 0; e < E; ++e) nz_total += cnt_s[e] > 0;
-        a.p_offsets[E] = off_s[E];
-        *a.p_n_active = nz_total;
+    if (warp == 1) {
+        int nz = 0;
+        for (int e = lane; e < E; e += 32) nz += cnt_s[e] > 0;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) nz += __shfl_xor_sync(0xFFFFFFFFu, nz, off);
+        if (lane == 0) {
+            a.p_offsets[E] = off_s[E];
+            *a.p_n_active = nz;
+        }
     }
     for (int c = warp; c < chunks; c += R_THREADS / 32) {
         const int i = c * 32 + lane;
@@ -262,6 +276,7 @@ __device__ void fused_permute(const RouterArgs& a, unsigned char* smem_raw) {
 template <typename TX, int TPT, bool TR>
 __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long w_bar;         // TR: completion of the W bulk copy
     constexpr int TT = 4 * TPT;
     const int H = a.H, E = a.E;
     const int H8 = H & ~7;
@@ -277,24 +292,54 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
 
     if constexpr (TR) {
         const int steps = H >> 3;                              // i = 0 .. steps-1, row h = 8 i + j
-        // W: a warp takes 32 consecutive i of one j; each lane reads its row's 8 experts (32 B)
-        for (int idx = tid; idx < H; idx += R_THREADS) {
-            const int j = idx / steps, i = idx - j * steps;
-            const float4* src = reinterpret_cast<const float4*>(a.w + (size_t)(i * 8 + j) * E + e0);
-            const float4 w0 = __ldg(src), w1 = __ldg(src + 1);
-            float* dst = Ws + (size_t)(j * 8) * S + i;
-            dst[0 * S] = w0.x; dst[1 * S] = w0.y; dst[2 * S] = w0.z; dst[3 * S] = w0.w;
-            dst[4 * S] = w1.x; dst[5 * S] = w1.y; dst[6 * S] = w1.z; dst[7 * S] = w1.w;
+        // x first (kept in registers while W streams in), then W eight rows per thread at a time
+        // with all loads issued before the first store: the block's critical path is L2 latency
+        constexpr int XU = TT;                                // 16-byte groups per thread up to H = 2048
+        uint4 xv[XU];
+        const int xgroups = TT * steps;
+#pragma unroll
+        for (int u = 0; u < XU; ++u) {
+            const int idx = tid + u * R_THREADS;
+            xv[u] = make_uint4(0, 0, 0, 0);
+            if (idx < xgroups && idx < XU * R_THREADS) {
+                const int tt = idx / steps, i = idx - tt * steps;
+                if (t0 + tt < a.T) xv[u] = *reinterpret_cast<const uint4*>(x + (size_t)(t0 + tt) * H + (size_t)i * 8);
+            }
         }
-        for (int idx = tid; idx < TT * steps; idx += R_THREADS) {
+        // W: the slice's image lies contiguous in global memory; one bulk copy by the copy engine
+        // (issued first, above the x loads would be even better, but x needs no barrier)
+        const uint32_t bar = smem_u32(&w_bar);
+        const uint32_t w_bytes = (uint32_t)(64 * S * 4);
+        if (tid == 0) {
+            mbar_init(bar, 1);
+            mbar_init_fence();
+            mbar_expect_tx(bar, w_bytes);
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                    smem_u32(Ws)),
+                "l"(a.wt + (size_t)blockIdx.x * 64 * S), "r"(w_bytes), "r"(bar)
+                : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < XU; ++u) {
+            const int idx = tid + u * R_THREADS;
+            if (idx < xgroups && idx < XU * R_THREADS) {
+                const int tt = idx / steps, i = idx - tt * steps;
+                const TX* hv = reinterpret_cast<const TX*>(&xv[u]);
+                float* dst = xs + (size_t)(tt * 8) * S + i;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) dst[q * S] = to_f32(hv[q]);
+            }
+        }
+        // wider rows than the registers above cover (hidden > 2048): the rest, plainly
+        for (int idx = tid + XU * R_THREADS; idx < xgroups; idx += R_THREADS) {
             const int tt = idx / steps, i = idx - tt * steps;
-            const int t = t0 + tt;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (t < a.T) v = *reinterpret_cast<const uint4*>(x + (size_t)t * H + (size_t)i * 8);
+            if (t0 + tt < a.T) v = *reinterpret_cast<const uint4*>(x + (size_t)(t0 + tt) * H + (size_t)i * 8);
             const TX* hv = reinterpret_cast<const TX*>(&v);
             float* dst = xs + (size_t)(tt * 8) * S + i;
 #pragma unroll
-            for (int u = 0; u < 8; ++u) dst[u * S] = to_f32(hv[u]);
+            for (int q = 0; q < 8; ++q) dst[q * S] = to_f32(hv[q]);
         }
     } else if ((E & 3) == 0 && e0 + R_ES <= E) {
         // 8 experts of one row = two aligned float4
@@ -330,6 +375,16 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
             int tt = idx / H, h = idx - tt * H;
             int t = t0 + tt;
             xs[idx] = t < a.T ? to_f32(x[(size_t)t * H + h]) : 0.0f;
+        }
+    }
+    if constexpr (TR) {
+        __syncthreads();                       // the barrier initialised by thread 0 is visible
+        uint32_t polls = 0;
+        while (!mbar_try_wait(smem_u32(&w_bar), 0, 1000u)) {
+            if (++polls > (1u << 20)) {        // a bulk copy from valid memory always lands; bounded anyway
+                if (tid == 0) atomicOr(a.status, STATUS_TIMEOUT);
+                break;
+            }
         }
     }
     __syncthreads();
@@ -399,7 +454,10 @@ __global__ void __launch_bounds__(R_THREADS) router_kernel(RouterArgs a) {
     int32_t* sm_ids = reinterpret_cast<int32_t*>(sm_vals + a.k);
     for (int tt = warp; tt < TT; tt += R_THREADS / 32) {
         int t = t0 + tt;
-        if (t < a.T) warp_softmax_topk(a, t, sm_v, sm_vals, sm_ids);
+        if (t < a.T) {
+            if (E <= 64) warp_softmax_topk<2>(a, t, sm_v, sm_vals, sm_ids);
+            else warp_softmax_topk<R_MAXV>(a, t, sm_v, sm_vals, sm_ids);
+        }
     }
     if (!a.fuse) return;
     // the block that finishes the last token tile groups the pairs by expert
@@ -683,7 +741,7 @@ static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
     int tpt = a.T >= 2048 ? 4 : (a.T >= 256 ? 2 : 1);
     while (tpt > 1 && router_smem(a.H, a.E, a.k, 4 * tpt) > 200 * 1024) tpt >>= 1;
     if (tpt == 1 && sizeof(TX) == 2 && a.H % 32 == 0 && a.E % R_ES == 0 &&
-        (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && !getenv("MUMMU_CUDA_ROUTER_PLAIN")) {
+        a.wt != nullptr && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && !getenv("MUMMU_CUDA_ROUTER_PLAIN")) {
         const int S = a.H / 8 + 4;
         const size_t smem_t = ((size_t)64 * S + (size_t)4 * 8 * S + 4 * 64 + (size_t)8 * (a.E + 2 * a.k)) * 4;
         if (smem_t <= 200 * 1024) {
@@ -744,6 +802,7 @@ int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int nor
     a.p_n_active = m->n_active;
     a.x = x;
     a.w = m->router_w;
+    a.wt = m->router_wt;
     a.bias = m->router_bias;
     a.logits = m->logits;
     a.tile_done = m->tile_done;
@@ -1512,6 +1571,7 @@ extern "C" int32_t mummu_moe_route_noalloc(const void* x, int32_t act_dtype, con
         RouterArgs a;
         a.x = x;
         a.w = router_w;
+        a.wt = nullptr;
         a.bias = bias;
         a.logits = sc->logits;
         a.tile_done = sc->tile_done;

@@ -52,6 +52,7 @@ struct DecodeArgs {
     void* out;                  // gate/up: __half hact; down: float ys
     int rows_per_expert;        // weight rows per expert (TMA row coordinate)
     int ring_depth;             // TMA stages per warp
+    int pdl;                    // this launch is one of a programmatically dependent pair
     int32_t* status;            // handle's device status word
 };
 
@@ -691,6 +692,16 @@ decode_q4k_tma_kernel(DecodeArgs a, const __grid_constant__ CUtensorMap map0, co
     // request the first units before the tokens are staged
     for (int i = 0; i < r.depth; ++i)
         if (r.p_valid) ring_issue<GATEUP>(r, i, &map0, &map1, row_base, rt_first, rt_end, nsb, npasses, lane);
+    if (!a.pdl) {
+    } else if (GATEUP) {
+        // programmatic dependent launch: the down kernel's CTAs may take the SMs this grid leaves
+        // idle in its tail and request their first weights there
+        asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    } else {
+        // launched early (see above): the weights requested so far do not depend on the previous
+        // grid, the activations staged next do.  Returns at once after an ordinary launch.
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    }
 
     for (int pass0 = 0; pass0 < cnt; pass0 += 8 * NT) {
         const int npass = min(8 * NT, cnt - pass0);
@@ -735,7 +746,7 @@ static bool use_tma_ring() {
 
 template <int NT, bool GATEUP>
 static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream, cudaStream_t s,
-                      const char* name) {
+                      const char* name, bool pdl = false, bool* used_tma = nullptr) {
     const int nsb = a.K >> 8;
     if (stream && use_tma_ring()) {
         // deepest ring (2..4 stages per warp) that still lets two CTAs share an SM
@@ -752,8 +763,24 @@ static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream
             a.ring_depth = depth;
             LaunchScope scope(m, s, name);
             MUMMU_CUDA_TRY(allow_big_smem(decode_q4k_tma_kernel<NT, GATEUP>, m->cfg.device));
-            decode_q4k_tma_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a, *map0, *map1);
+            if (!GATEUP && pdl) {
+                // may start while the gate/up grid drains (it waits on the device before it reads hact)
+                cudaLaunchConfig_t cfg{};
+                cfg.gridDim = dim3((unsigned)(n_experts_max * a.ctas_per_expert));
+                cfg.blockDim = dim3(DQ_THREADS);
+                cfg.dynamicSmemBytes = smem;
+                cfg.stream = s;
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[0].val.programmaticStreamSerializationAllowed = 1;
+                cfg.attrs = attr;
+                cfg.numAttrs = 1;
+                MUMMU_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_q4k_tma_kernel<NT, GATEUP>, a, *map0, *map1));
+            } else {
+                decode_q4k_tma_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a, *map0, *map1);
+            }
             MUMMU_CUDA_TRY(cudaGetLastError());
+            if (used_tma) *used_tma = true;
             return MUMMU_OK;
         }
     }
@@ -835,9 +862,18 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     g.out = m->hact;
     g.rows_per_expert = c.inter;
     g.status = m->status;
-    int rc = nt2 ? launch_one<2, true>(m, g, experts_est, g_stream, s, "q4k_gate_up")
-                 : launch_one<1, true>(m, g, experts_est, g_stream, s, "q4k_gate_up");
+    // Programmatic dependent launch of the down kernel behind gate/up: opt-in
+    // (MUMMU_CUDA_DECODE_PDL=1); profiling brackets every launch with events, which would
+    // serialise the pair anyway.
+    const char* pdl_env = getenv("MUMMU_CUDA_DECODE_PDL");
+    const bool want_pdl = pdl_env && atoi(pdl_env) != 0 && !m->prof.enabled;
+    g.pdl = want_pdl ? 1 : 0;
+    bool g_tma = false;
+    int rc = nt2 ? launch_one<2, true>(m, g, experts_est, g_stream, s, "q4k_gate_up", false, &g_tma)
+                 : launch_one<1, true>(m, g, experts_est, g_stream, s, "q4k_gate_up", false, &g_tma);
     if (rc) return rc;
+    // profiling brackets every launch with events, which would serialise the pair anyway
+    const bool pdl = g_tma && want_pdl;
 
     DecodeArgs d{};
     d.x = (const __half*)m->hact;
@@ -854,12 +890,13 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     d.n_rt = c.hidden / 32;
     bool d_stream;
     plan(d, experts_est, d_stream);
+    d.pdl = pdl ? 1 : 0;
     d.ld_out = c.hidden;
     d.out = ys;
     d.rows_per_expert = c.hidden;
     d.status = m->status;
-    return nt2 ? launch_one<2, false>(m, d, experts_est, d_stream, s, "q4k_down")
-               : launch_one<1, false>(m, d, experts_est, d_stream, s, "q4k_down");
+    return nt2 ? launch_one<2, false>(m, d, experts_est, d_stream, s, "q4k_down", pdl)
+               : launch_one<1, false>(m, d, experts_est, d_stream, s, "q4k_down", pdl);
 }
 
 int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cudaStream_t s) {

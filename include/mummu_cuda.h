@@ -117,6 +117,14 @@ int32_t mummu_moe_route(MummuMoe* moe, const void* x, int32_t tokens, int32_t to
                         int32_t norm_topk_prob, int32_t* ids_out, float* w_out,
                         int32_t on_device, void* stream);
 
+/* mummu_moe_route followed by mummu_moe_permute, device pointers only; for decode-sized calls (at
+ * most 1024 (token, slot) pairs) it is one launch: the router's last block groups the pairs.
+ * Same outputs as the two calls (SparseMoePerExpert::route, nn/moe.rs:247-290, then the grouping
+ * of Routing.per_expert, nn/moe.rs:275-289). */
+int32_t mummu_moe_route_grouped(MummuMoe* moe, const void* x, int32_t tokens, int32_t top_k,
+                                int32_t norm_topk_prob, int32_t* ids, float* w, int32_t* counts,
+                                int32_t* offsets, int32_t* row_token, int32_t* pos, void* stream);
+
 /* Group the routed (token, slot) pairs by expert — the `Routing.per_expert` lists of
  * nn/moe.rs:275-289 as flat device arrays.  ids: device [tokens*top_k] global expert ids.
  * Outputs (device): counts[experts] rows per expert; offsets[experts+1] exclusive prefix sum;

@@ -37,6 +37,8 @@ SYMBOLS = {
                                       C.c_int32, C.c_int32, C.c_void_p]),
     "mummu_moe_route": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                     C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "mummu_moe_route_grouped": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "mummu_moe_permute": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "mummu_moe_experts_grouped": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,

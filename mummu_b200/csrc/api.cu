@@ -400,6 +400,28 @@ int32_t mummu_moe_route(MummuMoe* m, const void* x, int32_t tokens, int32_t top_
     return read_status(m, s);
 }
 
+int32_t mummu_moe_route_grouped(MummuMoe* m, const void* x, int32_t tokens, int32_t top_k, int32_t norm,
+                                int32_t* ids, float* w, int32_t* counts, int32_t* offsets, int32_t* row_token,
+                                int32_t* pos, void* stream) {
+    MUMMU_REQUIRE(m, "mummu_moe_route_grouped: null handle");
+    MUMMU_REQUIRE(tokens >= 0, "MoE route: negative token count %d", tokens);
+    int rc;
+    if ((rc = check_top_k(m, top_k))) return rc;
+    if ((rc = check_ready(m, true, false))) return rc;
+    if (tokens == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(x && ids && w && counts && offsets && row_token && pos, "mummu_moe_route_grouped: null pointer");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    if ((rc = ensure_scratch(m, tokens))) return rc;
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    // decode-sized calls: one launch (the router's last block groups the pairs); else two
+    const GroupedOut out{counts, offsets, row_token, pos};
+    rc = launch_router(m, x, tokens, top_k, norm, ids, w, counts, s, true, &out);
+    if (rc != MUMMU_ERR_UNSUPPORTED) return rc;
+    if ((rc = launch_router(m, x, tokens, top_k, norm, ids, w, counts, s))) return rc;
+    return launch_permute(m, ids, tokens, top_k, counts, offsets, row_token, pos, s);
+}
+
 int32_t mummu_moe_permute(MummuMoe* m, const int32_t* ids, int32_t tokens, int32_t top_k,
                           int32_t* counts, int32_t* offsets, int32_t* row_token, int32_t* pos,
                           void* stream) {

@@ -190,8 +190,13 @@ struct LaunchScope {
 };
 
 // ---- kernels_basic.cu ----
+// where the fused grouping of a decode-sized router call writes (null = the handle's own scratch)
+struct GroupedOut {
+    int32_t *counts, *offsets, *row_token, *pos;
+};
 int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int norm, int32_t* ids,
-                  float* wts, int32_t* counts, cudaStream_t s, bool fuse_permute = false);
+                  float* wts, int32_t* counts, cudaStream_t s, bool fuse_permute = false,
+                  const GroupedOut* grouped = nullptr);
 int launch_count(MummuMoe* m, const int32_t* ids, int64_t n, int32_t* counts, cudaStream_t s);
 int launch_permute(MummuMoe* m, const int32_t* ids, int64_t tokens, int top_k,
                    const int32_t* counts, int32_t* offsets, int32_t* row_token, int32_t* pos,

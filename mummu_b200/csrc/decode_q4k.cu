@@ -802,12 +802,17 @@ static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream
     return MUMMU_OK;
 }
 
-// Work split for one projection.  Streaming (one warp per row tile over all of K) needs enough
-// row tiles to fill the GPU: experts * n_rt warp tasks against 148 SMs x 16 resident warps.
-// Otherwise the split-K variant spreads each row tile over up to 8 warps.
+// Work split for one projection.  Streaming (one warp per row tile over all of K) needs row
+// tiles for a fair share of the 148 SMs x 16 resident warps (measured at the OLMoE shape: 36.9 us
+// against 35.3 us for split-K with 8 experts, 39 against 51 with 15, 48 against 72 with 27);
+// below that the split-K variant spreads each row tile over up to 8 warps.
 static void plan(DecodeArgs& a, int experts_est, bool& stream) {
     const int nsb = a.K >> 8;
-    stream = (int64_t)experts_est * a.n_rt >= 148 * 16;
+    static const int stream_min = [] {
+        const char* env = getenv("MUMMU_CUDA_DECODE_STREAM_MIN");
+        return env ? atoi(env) : 148 * 5;   // measured: streaming wins from about 15 experts' row tiles on
+    }();
+    stream = (int64_t)experts_est * a.n_rt >= stream_min;
     if (stream) {
         a.rb = DQ_WARPS;                       // one row tile per warp
         // two row tiles per warp as long as the CTAs still cover the SMs one and a half times:

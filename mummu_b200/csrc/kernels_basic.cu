@@ -779,7 +779,7 @@ static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
 }
 
 int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int norm, int32_t* ids,
-                  float* wts, int32_t* counts, cudaStream_t s, bool fuse_permute) {
+                  float* wts, int32_t* counts, cudaStream_t s, bool fuse_permute, const GroupedOut* grouped) {
     const MummuMoeConfig& c = m->cfg;
     if (c.experts > 32 * R_MAXV) {
         set_error("router: %d experts exceed the %d this build selects over", c.experts, 32 * R_MAXV);
@@ -787,17 +787,17 @@ int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int nor
     }
     // fused grouping: one block sorts up to 1024 pairs in the narrow kernel's shared memory
     const int64_t pairs = tokens * top_k, pair_chunks = (pairs + 31) / 32;
-    const bool fuse = fuse_permute && counts == m->counts && tokens < 256 && pairs <= 1024 &&
+    const bool fuse = fuse_permute && (counts == m->counts || grouped) && tokens < 256 && pairs <= 1024 &&
                       (size_t)(pair_chunks * 32 + 2 * c.experts + 2 + pair_chunks * c.experts) * 4 <=
                           router_smem(c.hidden, c.experts, top_k, 4);
     if (fuse_permute && !fuse) return MUMMU_ERR_UNSUPPORTED;       // caller falls back to the separate launch
     if (counts && !fuse) MUMMU_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int32_t) * c.experts, s));
     RouterArgs a;
     a.fuse = fuse ? 1 : 0;
-    a.p_counts = m->counts;
-    a.p_offsets = m->offsets;
-    a.p_row_token = m->row_token;
-    a.p_pos = m->pos;
+    a.p_counts = grouped ? grouped->counts : m->counts;
+    a.p_offsets = grouped ? grouped->offsets : m->offsets;
+    a.p_row_token = grouped ? grouped->row_token : m->row_token;
+    a.p_pos = grouped ? grouped->pos : m->pos;
     a.p_active = m->active;
     a.p_n_active = m->n_active;
     a.x = x;

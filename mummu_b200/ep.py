@@ -167,10 +167,7 @@ class ExpertParallelMoe:
         E, R = self.cfg.num_experts, self.world
         assert T * top_k * R <= ws.cap_rows, "workspace too small for the rows that may arrive"
         i32 = dict(dtype=torch.int32, device=x.device)
-        ids, w = m.route_flat(x, top_k, norm_topk_prob)
-        counts, offsets = torch.empty(E, **i32), torch.empty(E + 1, **i32)
-        row_token, pos = torch.empty(T * top_k, **i32), torch.empty(T * top_k, **i32)
-        m.permute(ids, counts, offsets, row_token, pos)
+        ids, w, counts, offsets, row_token, pos = m.route_grouped(x, top_k, norm_topk_prob)
         dst_base, local_counts = torch.empty(E, **i32), torch.empty(self.el, **i32)
         if self.device_sync:
             # counts all-gather, plan and both barriers on the device: the step holds no collective

@@ -274,6 +274,22 @@ class SparseMoe:
         return int(L.lib.mummu_moe_launch_count(self._h))
 
     # -- staged calls (device tensors), used by the expert-parallel layer -----------------------
+    def route_grouped(self, xt, top_k: int, norm_topk_prob: bool):
+        """`route_flat` + `permute` on device tensors; one launch for decode-sized calls.
+        Returns (ids, w, counts, offsets, row_token, pos)."""
+        import torch
+        xc = xt.contiguous()
+        tokens, E = xc.shape[0], self.cfg.num_experts
+        i32 = dict(dtype=torch.int32, device=xc.device)
+        ids = torch.empty((tokens, top_k), **i32)
+        w = torch.empty((tokens, top_k), dtype=torch.float32, device=xc.device)
+        counts, offsets = torch.empty(E, **i32), torch.empty(E + 1, **i32)
+        row_token, pos = torch.empty(tokens * top_k, **i32), torch.empty(tokens * top_k, **i32)
+        _check(L.lib.mummu_moe_route_grouped(self._h, xc.data_ptr(), tokens, top_k, int(bool(norm_topk_prob)),
+                                             ids.data_ptr(), w.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
+                                             row_token.data_ptr(), pos.data_ptr(), _torch_stream()))
+        return ids, w, counts, offsets, row_token, pos
+
     def permute(self, ids, counts=None, offsets=None, row_token=None, pos=None) -> None:
         tokens, top_k = ids.shape
         p = lambda t: None if t is None else t.data_ptr()

@@ -360,6 +360,28 @@ def test_half_precision_layer(M, cuda_lib, act):
     m.close()
 
 
+@pytest.mark.parametrize("T", [1, 24, 128, 300])
+def test_route_grouped_equals_route_then_permute(M, cuda_lib, T):
+    """The fused router + grouping launch (and its two-launch fallback for large T) give exactly
+    the (ids, weights, counts, offsets, row_token, pos) of route followed by permute."""
+    import torch
+    L = cuda_lib
+    H, I, E, K = 512, 64, 16, 4
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=17)
+    m = make_layer(M, L, H, I, E, K, L.F16, L.F16, router, *(b.astype(np.float16) for b in (gate, up, down)))
+    xd = torch.from_numpy(x.astype(np.float16)).cuda()
+    ids, w = m.route_flat(xd, K, False)
+    i32 = dict(dtype=torch.int32, device="cuda")
+    counts, offsets = torch.empty(E, **i32), torch.empty(E + 1, **i32)
+    row_token, pos = torch.empty(T * K, **i32), torch.empty(T * K, **i32)
+    m.permute(ids, counts, offsets, row_token, pos)
+    got = m.route_grouped(xd, K, False)
+    torch.cuda.synchronize()
+    for a, b in zip(got, (ids, w, counts, offsets, row_token, pos)):
+        assert torch.equal(a, b)
+    m.close()
+
+
 def test_staged_calls_match_whole_layer(M, cuda_lib):
     """permute -> experts_grouped -> combine on device tensors == forward."""
     import torch

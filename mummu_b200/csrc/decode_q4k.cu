@@ -53,6 +53,7 @@ struct DecodeArgs {
     int rows_per_expert;        // weight rows per expert (TMA row coordinate)
     int ring_depth;             // TMA stages per warp
     int pdl;                    // this launch is one of a programmatically dependent pair
+    int pass_split;             // CTAs sharing the passes of an expert (grid y)
     int32_t* status;            // handle's device status word
 };
 
@@ -668,7 +669,12 @@ decode_q4k_tma_kernel(DecodeArgs a, const __grid_constant__ CUtensorMap map0, co
     const int rt_begin = cb * a.rb;
     const int rt_end = min(a.n_rt, rt_begin + a.rb);
     const int rt_first = rt_begin + warp;
-    const int npasses = (cnt + 8 * NT - 1) / (8 * NT);
+    // An expert with more rows than one token tile holds needs several passes over its weights;
+    // gridDim.y CTAs share them (pass p goes to CTA p % gridDim.y), each streaming the weights again
+    // (from L2 after the first), instead of one CTA looping while SMs stand idle.
+    const int pass_first = (int)blockIdx.y * 8 * NT, pass_step = (int)gridDim.y * 8 * NT;
+    if (pass_first >= cnt) return;
+    const int npasses = (cnt - pass_first + pass_step - 1) / pass_step;
     const int row_base = e * a.rows_per_expert;
 
     UnitRing r;
@@ -703,7 +709,7 @@ decode_q4k_tma_kernel(DecodeArgs a, const __grid_constant__ CUtensorMap map0, co
         asm volatile("griddepcontrol.wait;\n" ::: "memory");
     }
 
-    for (int pass0 = 0; pass0 < cnt; pass0 += 8 * NT) {
+    for (int pass0 = pass_first; pass0 < cnt; pass0 += pass_step) {
         const int npass = min(8 * NT, cnt - pass0);
         const int nt_count = (npass + 7) >> 3;
         __syncthreads();
@@ -766,7 +772,7 @@ static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream
             if (!GATEUP && pdl) {
                 // may start while the gate/up grid drains (it waits on the device before it reads hact)
                 cudaLaunchConfig_t cfg{};
-                cfg.gridDim = dim3((unsigned)(n_experts_max * a.ctas_per_expert));
+                cfg.gridDim = dim3((unsigned)(n_experts_max * a.ctas_per_expert), (unsigned)a.pass_split);
                 cfg.blockDim = dim3(DQ_THREADS);
                 cfg.dynamicSmemBytes = smem;
                 cfg.stream = s;
@@ -777,7 +783,7 @@ static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream
                 cfg.numAttrs = 1;
                 MUMMU_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_q4k_tma_kernel<NT, GATEUP>, a, *map0, *map1));
             } else {
-                decode_q4k_tma_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a, *map0, *map1);
+                decode_q4k_tma_kernel<NT, GATEUP><<<dim3((unsigned)(n_experts_max * a.ctas_per_expert), (unsigned)a.pass_split), DQ_THREADS, smem, s>>>(a, *map0, *map1);
             }
             MUMMU_CUDA_TRY(cudaGetLastError());
             if (used_tma) *used_tma = true;
@@ -806,18 +812,21 @@ static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream
 // tiles for a fair share of the 148 SMs x 16 resident warps (measured at the OLMoE shape: 36.9 us
 // against 35.3 us for split-K with 8 experts, 39 against 51 with 15, 48 against 72 with 27);
 // below that the split-K variant spreads each row tile over up to 8 warps.
-static void plan(DecodeArgs& a, int experts_est, bool& stream) {
+static void plan(DecodeArgs& a, int experts_est, int64_t rows_total, int nt, bool& stream) {
     const int nsb = a.K >> 8;
+    // expected passes per expert from the row bound the caller gave (1 in plain decode calls)
+    int64_t per_expert = (rows_total + experts_est - 1) / experts_est;
+    a.pass_split = (int)std::min<int64_t>(4, std::max<int64_t>(1, (per_expert + 8 * nt - 1) / (8 * nt)));
     static const int stream_min = [] {
         const char* env = getenv("MUMMU_CUDA_DECODE_STREAM_MIN");
         return env ? atoi(env) : 148 * 5;   // measured: streaming wins from about 15 experts' row tiles on
     }();
-    stream = (int64_t)experts_est * a.n_rt >= stream_min;
+    stream = (int64_t)experts_est * a.n_rt * a.pass_split >= stream_min;
     if (stream) {
         a.rb = DQ_WARPS;                       // one row tile per warp
         // two row tiles per warp as long as the CTAs still cover the SMs one and a half times:
         // the token tile is then staged half as often (measured: 2 % on the layer)
-        while (a.rb * 2 <= a.n_rt && (int64_t)experts_est * (a.n_rt / (a.rb * 2)) * 2 >= 148 * 3) a.rb *= 2;
+        while (a.rb * 2 <= a.n_rt && (int64_t)experts_est * (a.n_rt / (a.rb * 2)) * a.pass_split * 2 >= 148 * 3) a.rb *= 2;
     } else {
         const int ks = nsb < DQ_WARPS ? nsb : DQ_WARPS, rg = DQ_WARPS / ks;
         a.rb = rg;
@@ -856,7 +865,7 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     g.K = c.hidden;
     g.n_rt = c.inter / 16;
     bool g_stream;
-    plan(g, experts_est, g_stream);
+    plan(g, experts_est, rows_total, nt2 ? 2 : 1, g_stream);
     if (g_stream && decode_umma_supported(c)) {
         // enough routed experts to fill the GPU with 128-row tiles: tensor-core variant
         int rc = launch_decode_umma(m, true, x, row_token, counts, offsets, experts_est, m->hact, s);
@@ -893,7 +902,7 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     d.K = c.inter;
     d.n_rt = c.hidden / 32;
     bool d_stream;
-    plan(d, experts_est, d_stream);
+    plan(d, experts_est, rows_total, nt2 ? 2 : 1, d_stream);
     d.pdl = pdl ? 1 : 0;
     d.ld_out = c.hidden;
     d.out = ys;

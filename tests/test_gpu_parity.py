@@ -301,6 +301,40 @@ def test_q4k_decode_olmoe_shape_crowded_experts(M, cuda_lib, olmoe_q4k_layer):
     m.close()
 
 
+def test_q4k_grouped_rows_many_passes(M, cuda_lib, olmoe_q4k_layer):
+    """`experts_grouped` on already sorted rows with ragged segments (0 .. 64 rows per expert, the
+    shape an expert-parallel rank sees): several passes of the token tile, shared between CTAs."""
+    import torch
+    L = cuda_lib
+    H, I, E, K, router, (gq, uq, dq), _ = olmoe_q4k_layer
+    counts = np.full(E, 8, np.int32)
+    counts[[0, 5, 9, 20, 33, 47, 63]] = [17, 0, 33, 64, 1, 40, 16]
+    rows = int(counts.sum())
+    xs = synth.normal(31, (rows, H), 1.0).astype(np.float16)
+    m = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, gq, uq, dq)
+    ys = torch.zeros(rows, H, dtype=torch.float16, device="cuda")
+    # the row bound an expert-parallel caller passes (capacity, not the exact count) sets the split
+    cap = torch.zeros(4 * rows, H, dtype=torch.float16, device="cuda")
+    cap[:rows] = torch.from_numpy(xs).cuda()
+    ycap = torch.zeros(4 * rows, H, dtype=torch.float16, device="cuda")
+    m.experts_grouped(torch.from_numpy(xs).cuda(), torch.from_numpy(counts).cuda(), ys)
+    m.experts_grouped(cap, torch.from_numpy(counts).cuda(), ycap)
+    torch.cuda.synchronize()
+    m.sync()
+    assert torch.equal(ys, ycap[:rows])            # same bits whatever the pass split
+    off = np.concatenate([[0], np.cumsum(counts)])
+    got = ys.cpu().numpy().astype(np.float32)
+    rb_gate, rb_down = H // 256 * 144, I // 256 * 144
+    for e in (0, 9, 20, 33, 47):
+        g = O.dequant_q4_k(gq.reshape(E, I, rb_gate)[e]).reshape(I, H)
+        u = O.dequant_q4_k(uq.reshape(E, I, rb_gate)[e]).reshape(I, H)
+        d = O.dequant_q4_k(dq.reshape(E, H, rb_down)[e]).reshape(H, I)
+        want = O.expert_ffn(g, u, d, xs[off[e]:off[e + 1]].astype(np.float32))
+        assert rel_err(got[off[e]:off[e + 1]], want) < TOL_16
+    assert not got[off[5]:off[6]].size
+    m.close()
+
+
 def test_q4k_small_golden(M, cuda_lib):
     L = cuda_lib
     gold = np.load(os.path.join(HERE, "golden", "q4k_small.npz"))

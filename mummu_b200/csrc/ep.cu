@@ -110,7 +110,14 @@ __global__ void __launch_bounds__(256) ep_exchange_plan_kernel(const int32_t* co
     __syncthreads();
     if (threadIdx.x < 32) ep_signal_and_wait(sync, rank, world, status);
     __syncthreads();
-    const volatile int32_t* all_counts = reinterpret_cast<const volatile int32_t*>(sync.ptr[rank]) + EP_SYNC_COUNTS;
+    // the gathered counts once into shared memory (coalesced), then the plan from there: read one
+    // by one from global memory the dependent loads below cost tens of microseconds
+    extern __shared__ int32_t all_counts[];                    // [world][E]
+    {
+        const volatile int32_t* src = reinterpret_cast<const volatile int32_t*>(sync.ptr[rank]) + EP_SYNC_COUNTS;
+        for (int i = threadIdx.x; i < world * E; i += blockDim.x) all_counts[i] = src[i];
+    }
+    __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         const int d = e / EL, le = e - d * EL;
         int base = 0;
@@ -288,7 +295,7 @@ int32_t mummu_ep_exchange_plan(MummuMoe* m, const int32_t* counts, void* const* 
     PeerTable t{};
     for (int i = 0; i < world; ++i) t.ptr[i] = peer_sync[i];
     LaunchScope scope(m, s, "ep_exchange_plan");
-    ep_exchange_plan_kernel<<<1, 256, 0, s>>>(counts, t, world, rank, m->cfg.experts, m->cfg.experts_local, dst_base,
+    ep_exchange_plan_kernel<<<1, 256, (size_t)world * m->cfg.experts * sizeof(int32_t), s>>>(counts, t, world, rank, m->cfg.experts, m->cfg.experts_local, dst_base,
                                               local_counts, m->status);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;

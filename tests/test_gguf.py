@@ -1,0 +1,148 @@
+"""GGUF container: the reader's limits and refusals (crates/mummu/src/gguf.rs:1124-1376), the
+OLMoE keys and tensor names (models/olmoe.rs:116-179, 319-349), and verbatim Q4_K expert banks."""
+import os
+import struct
+
+import numpy as np
+import pytest
+
+from mummu_b200 import gguf, q4k, synth
+
+META = {"general.architecture": "olmoe", "olmoe.embedding_length": 256, "olmoe.expert_feed_forward_length": 256,
+        "olmoe.expert_count": 4, "olmoe.expert_used_count": 2, "olmoe.block_count": 2,
+        "tokenizer.ggml.tokens": ["a", "b", "c"], "olmoe.rope.freq_base": 10000.0}
+
+
+def synthetic_file(path, alignment=32, layers=2, extra_meta=None):
+    H, I, E = 256, 256, 4
+    tensors, truth = [], {}
+    for l in range(layers):
+        router, gate, up, down, _ = synth.moe_layer(H, I, E, 1, cfg_seed=50 + l)
+        banks = {"gate": q4k.quantize(gate), "up": q4k.quantize(up), "down": q4k.quantize(down)}
+        truth[l] = (router, banks)
+        tensors.append((f"blk.{l}.ffn_gate_inp.weight", [H, E], "F32", np.ascontiguousarray(router.T)))
+        tensors.append((f"blk.{l}.ffn_gate_exps.weight", [H, I, E], "Q4_K", banks["gate"]))
+        tensors.append((f"blk.{l}.ffn_up_exps.weight", [H, I, E], "Q4_K", banks["up"]))
+        tensors.append((f"blk.{l}.ffn_down_exps.weight", [I, H, E], "Q4_K", banks["down"]))
+    meta = dict(META)
+    meta.update(extra_meta or {})
+    gguf.write_gguf(path, meta, tensors, alignment=alignment)
+    return truth
+
+
+@pytest.mark.parametrize("alignment", [32, 64, 4096])
+def test_round_trip_verbatim_banks(tmp_path, alignment):
+    p = str(tmp_path / "m.gguf")
+    truth = synthetic_file(p, alignment)
+    f = gguf.GgufFile.open(p)
+    assert f.version == 3 and f.alignment == alignment and f.data_offset % alignment == 0
+    assert f.architecture() == "olmoe" and f.get("tokenizer.ggml.tokens") == ["a", "b", "c"]
+    assert abs(f.get("olmoe.rope.freq_base") - 10000.0) < 1e-3
+    shp = gguf.olmoe_moe_shape(f)
+    assert (shp.hidden_size, shp.expert_intermediate_size, shp.num_experts, shp.num_experts_per_tok,
+            shp.norm_topk_prob, shp.num_hidden_layers) == (256, 256, 4, 2, False, 2)
+    for l, (router, banks) in truth.items():
+        t = f.tensor(f"blk.{l}.ffn_gate_exps.weight")
+        assert t.dtype == "Q4_K" and t.shape == (4, 256, 256) and t.byte_len == 4 * 256 * 144 and t.offset % alignment == 0
+        for which in ("gate", "up", "down"):
+            got = f.tensor_bytes(f"blk.{l}.ffn_{which}_exps.weight")
+            assert np.array_equal(got, banks[which].reshape(-1))          # byte for byte
+        assert np.array_equal(f.tensor_array(f"blk.{l}.ffn_gate_inp.weight"), router.T)
+    f.close()
+
+
+def test_feed_forward_length_spelling_and_norm_key(tmp_path):
+    p = str(tmp_path / "m.gguf")
+    meta = dict(META)
+    del meta["olmoe.expert_feed_forward_length"]
+    meta.update({"olmoe.feed_forward_length": 256, "olmoe.expert_weights_norm": True})
+    gguf.write_gguf(p, meta, [("x", [32], "F32", np.zeros(32, np.float32))])
+    shp = gguf.olmoe_moe_shape(gguf.GgufFile.open(p))
+    assert shp.expert_intermediate_size == 256 and shp.norm_topk_prob is True
+    meta["general.architecture"] = "llama"
+    gguf.write_gguf(p, meta, [("x", [32], "F32", np.zeros(32, np.float32))])
+    with pytest.raises(ValueError, match="is not olmoe"):
+        gguf.olmoe_moe_shape(gguf.GgufFile.open(p))
+
+
+def _header(version=3, tensors=0, kvs=0, magic=b"GGUF"):
+    return magic + struct.pack("<IQQ", version, tensors, kvs)
+
+
+def _str(s):
+    b = s.encode()
+    return struct.pack("<Q", len(b)) + b
+
+
+def _tensor(name, dims, type_id, offset):
+    return _str(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", type_id, offset)
+
+
+def _write(tmp_path, blob):
+    p = str(tmp_path / "bad.gguf")
+    with open(p, "wb") as fh:
+        fh.write(blob + b"\0" * 4096)
+    return p
+
+
+@pytest.mark.parametrize("blob,exc,text", [
+    (_header(magic=b"GGML"), gguf.BadMagic, "bad magic"),
+    (_header(version=1), gguf.UnsupportedVersion, "unsupported version 1"),
+    (_header(version=4), gguf.UnsupportedVersion, "unsupported version 4"),
+    (_header(tensors=65_537), gguf.OverBound, "tensor count 65537"),
+    (_header(kvs=4097), gguf.OverBound, "metadata kv count 4097"),
+    (_header(kvs=1) + struct.pack("<Q", (1 << 20) + 1), gguf.OverBound, "metadata key"),
+    (_header(kvs=1) + _str("k") + struct.pack("<IB", 7, 2), gguf.BadValue, "bool byte 2"),
+    (_header(kvs=1) + _str("k") + struct.pack("<I", 13), gguf.BadValue, "unknown value type 13"),
+    (_header(kvs=1) + _str("k") + struct.pack("<IIQ", 9, 9, 1) + struct.pack("<IQ", 9, 1) + struct.pack("<IQ", 4, 0),
+     gguf.BadValue, "nested deeper than 2"),
+    (_header(kvs=1) + _str("k") + struct.pack("<IIQ", 9, 4, (1 << 22) + 1), gguf.OverBound, "metadata array"),
+    (_header(kvs=1) + _str("general.alignment") + struct.pack("<II", 4, 24), gguf.BadValue, "24 is not a power of two"),
+    (_header(kvs=1) + _str("general.alignment") + struct.pack("<II", 4, 0), gguf.BadValue, "0 is not a power of two"),
+    (_header(tensors=1) + _tensor("t", [], 0, 0), gguf.BadTensor, "0 dims"),
+    (_header(tensors=1) + _tensor("t", [2, 2, 2, 2, 2], 0, 0), gguf.BadTensor, "5 dims"),
+    (_header(tensors=1) + _tensor("t", [32], 99, 0), gguf.BadTensor, "unknown ggml type id 99"),
+    (_header(tensors=1) + _tensor("t", [32], 0, 16), gguf.BadTensor, "offset 16 not 32-aligned"),
+    (_header(tensors=1) + _tensor("t", [255], 12, 0), gguf.BadTensor, "255 elements is not whole Q4_K blocks"),
+    (_header(tensors=1) + _tensor("t", [0], 0, 0), gguf.BadTensor, "0 elements"),
+    (_header(tensors=2) + _tensor("t", [32], 0, 0) + _tensor("t", [32], 0, 128), gguf.BadTensor, "duplicate tensor name 't'"),
+    (_header(tensors=2) + _tensor("a", [64], 0, 0) + _tensor("b", [32], 0, 128), gguf.BadTensor, "overlaps 'a'"),
+])
+def test_refusals(tmp_path, blob, exc, text):
+    with pytest.raises(exc, match=text):
+        gguf.GgufFile.open(_write(tmp_path, blob))
+
+
+def test_truncated_and_arrays(tmp_path):
+    p = str(tmp_path / "t.gguf")
+    with open(p, "wb") as fh:
+        fh.write(_header(kvs=1) + _str("k"))
+    with pytest.raises(gguf.GgufError, match="unexpected end of file"):
+        gguf.GgufFile.open(p)
+    # two levels of arrays are allowed; every scalar type round-trips
+    blob = (_header(kvs=3, version=2) + _str("nest") + struct.pack("<IIQ", 9, 9, 1) + struct.pack("<IQ", 5, 2) + struct.pack("<ii", -1, 7)
+            + _str("f64") + struct.pack("<Id", 12, 2.5) + _str("u8") + struct.pack("<IB", 0, 200))
+    f = gguf.GgufFile.open(_write(tmp_path, blob))
+    assert f.version == 2 and f.get("nest") == [[-1, 7]] and f.get("f64") == 2.5 and f.get("u8") == 200
+
+
+@pytest.mark.gpu
+def test_layer_from_gguf_equals_direct_upload(tmp_path):
+    """`ffn_*_exps` Q4_K bytes go from the file to the device verbatim: the layer built from the
+    file gives the bits of the layer built from the same arrays in memory."""
+    from mummu_b200 import _lib as L, moe
+    p = str(tmp_path / "m.gguf")
+    truth = synthetic_file(p)
+    f = gguf.GgufFile.open(p)
+    x = synth.normal(5, (9, 256), 1.0).astype(np.float16)
+    for l, (router, banks) in truth.items():
+        from_file, shp = gguf.load_moe_layer(f, l)
+        direct = moe.SparseMoeConfig(256, 256, 4, 2).init(act_dtype=L.F16, weight_dtype=L.Q4_K)
+        direct.set_router(router)
+        direct.set_banks(banks["gate"], banks["up"], banks["down"])
+        a = from_file.forward(x, shp.num_experts_per_tok, shp.norm_topk_prob)
+        b = direct.forward(x, 2, False)
+        assert np.array_equal(a, b)
+        assert np.array_equal(from_file.dequant_bank(L.BANK_DOWN, 3), direct.dequant_bank(L.BANK_DOWN, 3))
+        from_file.close()
+        direct.close()

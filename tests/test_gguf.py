@@ -146,3 +146,38 @@ def test_layer_from_gguf_equals_direct_upload(tmp_path):
         assert np.array_equal(from_file.dequant_bank(L.BANK_DOWN, 3), direct.dequant_bank(L.BANK_DOWN, 3))
         from_file.close()
         direct.close()
+
+
+def test_loader_refuses_what_the_bank_cannot_take(tmp_path):
+    """Shape and type checks of `load_moe_layer` happen before anything touches a device."""
+    H, I, E = 256, 256, 4
+    p = str(tmp_path / "m.gguf")
+    z = lambda n: np.zeros(n, np.uint8)
+    q = E * I * H // 256 * 144
+    base = [("blk.0.ffn_gate_inp.weight", [H, E], "F32", np.zeros((E, H), np.float32)),
+            ("blk.0.ffn_gate_exps.weight", [H, I, E], "Q4_K", z(q)),
+            ("blk.0.ffn_up_exps.weight", [H, I, E], "Q4_K", z(q)),
+            ("blk.0.ffn_down_exps.weight", [I, H, E], "Q4_K", z(q))]
+    # a bank stored as Q6_K: a real type, but not one this path computes from
+    t = list(base)
+    t[3] = ("blk.0.ffn_down_exps.weight", [I, H, E], "Q6_K", z(E * I * H // 256 * 210))
+    gguf.write_gguf(p, META, t)
+    with pytest.raises(NotImplementedError, match="Q6_K"):
+        gguf.load_moe_layer(gguf.GgufFile.open(p), 0)
+    # mixed bank types
+    t = list(base)
+    t[2] = ("blk.0.ffn_up_exps.weight", [H, I, E], "F16", np.zeros(E * I * H, np.float16))
+    gguf.write_gguf(p, META, t)
+    with pytest.raises(NotImplementedError, match="mixes bank types"):
+        gguf.load_moe_layer(gguf.GgufFile.open(p), 0)
+    # wrong dims and a missing tensor
+    t = list(base)
+    t[1] = ("blk.0.ffn_gate_exps.weight", [I, H, E], "Q4_K", z(q))
+    meta = dict(META)
+    meta["olmoe.expert_feed_forward_length"] = 512
+    gguf.write_gguf(p, meta, t)
+    with pytest.raises(ValueError, match="do not match"):
+        gguf.load_moe_layer(gguf.GgufFile.open(p), 0)
+    gguf.write_gguf(p, META, base[:3])
+    with pytest.raises(KeyError, match="ffn_down_exps"):
+        gguf.load_moe_layer(gguf.GgufFile.open(p), 0)

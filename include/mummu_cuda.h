@@ -41,7 +41,12 @@ typedef enum {
     MUMMU_F32  = 0,
     MUMMU_F16  = 1,
     MUMMU_BF16 = 2,
-    MUMMU_Q4_K = 3      /* GGUF Q4_K super-blocks; weights only */
+    MUMMU_Q4_K = 3,     /* GGUF Q4_K super-blocks; weights only */
+    /* sibling GGUF formats (gguf.rs:1535-1543, 1731-1797), weights only, computed by the generic
+     * bank (every weight decoded element by element; no fast decode kernel) */
+    MUMMU_Q8_0 = 4,     /* 34-byte blocks of 32 */
+    MUMMU_Q5_K = 5,     /* 176-byte super-blocks of 256 */
+    MUMMU_Q6_K = 6      /* 210-byte super-blocks of 256 */
 } mummu_dtype;
 
 #define MUMMU_BANK_GATE 0

@@ -13,6 +13,7 @@ SO_PATH = os.path.join(_HERE, "libmummu_cuda.so")
 
 OK, ERR_CONTRACT, ERR_DEVICE, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_NUMERIC = 0, 1, 2, 3, 4, 5
 F32, F16, BF16, Q4_K = 0, 1, 2, 3
+Q8_0, Q5_K, Q6_K = 4, 5, 6       # sibling GGUF block formats: generic bank only
 BANK_GATE, BANK_UP, BANK_DOWN = 0, 1, 2
 ROUTER_IN_OUT, ROUTER_OUT_IN = 0, 1
 

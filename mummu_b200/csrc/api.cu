@@ -39,7 +39,13 @@ cudaError_t allow_big_smem_impl(const void* kernel, int device) {
 
 size_t bank_row_bytes(const MummuMoeConfig& c, int which) {
     size_t in_dim = which == MUMMU_BANK_DOWN ? c.inter : c.hidden;
-    if (c.weight_dtype == MUMMU_Q4_K) return in_dim / Q4K_BLOCK_ELEMS * Q4K_BLOCK_BYTES;
+    switch (c.weight_dtype) {
+        case MUMMU_Q4_K: return in_dim / Q4K_BLOCK_ELEMS * Q4K_BLOCK_BYTES;
+        case MUMMU_Q8_0: return in_dim / Q80_BLOCK_ELEMS * Q80_BLOCK_BYTES;
+        case MUMMU_Q5_K: return in_dim / 256 * Q5K_BLOCK_BYTES;
+        case MUMMU_Q6_K: return in_dim / 256 * Q6K_BLOCK_BYTES;
+        default: break;
+    }
     return in_dim * dtype_size(c.weight_dtype);
 }
 
@@ -228,16 +234,20 @@ int32_t mummu_moe_create(const MummuMoeConfig* cfg, MummuMoe** out) {
                   "MoE: hidden_size and expert_intermediate_size must be >= 1");
     MUMMU_REQUIRE(cfg->act_dtype == MUMMU_F32 || cfg->act_dtype == MUMMU_F16 || cfg->act_dtype == MUMMU_BF16,
                   "MoE: activation dtype %d is not F32, F16 or BF16", cfg->act_dtype);
-    MUMMU_REQUIRE(cfg->weight_dtype >= MUMMU_F32 && cfg->weight_dtype <= MUMMU_Q4_K,
-                  "MoE: weight dtype %d is not F32, F16, BF16 or Q4_K", cfg->weight_dtype);
+    MUMMU_REQUIRE(cfg->weight_dtype >= MUMMU_F32 && cfg->weight_dtype <= MUMMU_Q6_K,
+                  "MoE: weight dtype %d is not F32, F16, BF16, Q4_K, Q8_0, Q5_K or Q6_K", cfg->weight_dtype);
     MUMMU_REQUIRE(cfg->experts_local >= 1 && cfg->expert_first >= 0 &&
                       cfg->expert_first + cfg->experts_local <= cfg->experts,
                   "MoE: local experts [%d, %d) are not inside 0..%d", cfg->expert_first,
                   cfg->expert_first + cfg->experts_local, cfg->experts);
-    if (cfg->weight_dtype == MUMMU_Q4_K)
+    if (cfg->weight_dtype == MUMMU_Q4_K || cfg->weight_dtype == MUMMU_Q5_K || cfg->weight_dtype == MUMMU_Q6_K)
         MUMMU_REQUIRE(cfg->hidden % Q4K_BLOCK_ELEMS == 0 && cfg->inter % Q4K_BLOCK_ELEMS == 0,
-                      "MoE: Q4_K rows hold whole 256-value super-blocks (hidden %d, intermediate %d)",
+                      "MoE: K-quant rows hold whole 256-value super-blocks (hidden %d, intermediate %d)",
                       cfg->hidden, cfg->inter);
+    if (cfg->weight_dtype == MUMMU_Q8_0)
+        MUMMU_REQUIRE(cfg->hidden % Q80_BLOCK_ELEMS == 0 && cfg->inter % Q80_BLOCK_ELEMS == 0,
+                      "MoE: Q8_0 rows hold whole 32-value blocks (hidden %d, intermediate %d)", cfg->hidden,
+                      cfg->inter);
     int ndev = 0;
     MUMMU_CUDA_TRY(cudaGetDeviceCount(&ndev));
     MUMMU_REQUIRE(cfg->device >= 0 && cfg->device < ndev, "MoE: CUDA device %d of %d", cfg->device, ndev);
@@ -524,6 +534,9 @@ int32_t mummu_moe_dequant_bank(MummuMoe* m, int32_t which, int32_t expert, float
     int rc;
     if ((rc = dev_alloc(&tmp, n))) return rc;
     if (c.weight_dtype == MUMMU_Q4_K) rc = launch_q4k_dequant(src, tmp, (int64_t)(n / Q4K_BLOCK_ELEMS), m->stream);
+    else if (c.weight_dtype > MUMMU_Q4_K)
+        rc = launch_block_dequant(src, c.weight_dtype, tmp, (int64_t)out_dim, (int64_t)in_dim, bank_row_bytes(c, which),
+                                  m->stream);
     else rc = launch_widen(src, c.weight_dtype, tmp, (int64_t)n, m->stream);
     cudaError_t err = cudaSuccess;
     if (!rc) err = cudaMemcpyAsync(out, tmp, n * sizeof(float), cudaMemcpyDeviceToHost, m->stream);

@@ -103,6 +103,51 @@ __device__ __forceinline__ float q4k_decode_elem(const uint8_t* row, int k) {
     return __fsub_rn(product, __fmul_rn(dmin, m));
 }
 
+// Sibling GGUF block formats, correctness path only (the SIMT bank decodes them element by
+// element; the fast decode kernels take Q4_K).  Same operation order as the reference:
+//   Q8_0 (crates/mummu/src/gguf.rs:1535-1543): 34 B = f16 d + 32 i8;            x = d*q
+//   Q5_K (gguf.rs:1731-1765): 176 B = f16 d, f16 dmin, 12 B scales, 32 B fifth bits, 128 B nibbles;
+//                              x = (d*sc)*(q + 16*bit) - dmin*m
+//   Q6_K (gguf.rs:1769-1797): 210 B = 128 B low nibbles, 64 B high pairs, 16 i8 scales, f16 d;
+//                              x = (d*s)*(q - 32)
+struct q80_t { uint8_t b; };
+struct q5k_t { uint8_t b; };
+struct q6k_t { uint8_t b; };
+constexpr int Q80_BLOCK_ELEMS = 32, Q80_BLOCK_BYTES = 34;
+constexpr int Q5K_BLOCK_BYTES = 176, Q6K_BLOCK_BYTES = 210;   // 256 elements each
+
+__device__ __forceinline__ float f16_at(const uint8_t* p) {
+    return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8))));
+}
+
+__device__ __forceinline__ float q80_decode_elem(const uint8_t* row, int k) {
+    const uint8_t* blk = row + (size_t)(k >> 5) * Q80_BLOCK_BYTES;
+    return __fmul_rn(f16_at(blk), (float)(int8_t)blk[2 + (k & 31)]);
+}
+
+__device__ __forceinline__ float q5k_decode_elem(const uint8_t* row, int k) {
+    const uint8_t* blk = row + (size_t)(k >> 8) * Q5K_BLOCK_BYTES;
+    const int within = k & 255, j = within >> 5, chunk = j >> 1, b = within & 31;
+    float sc, m;
+    q4k_scale_min(blk + 4, j, sc, m);
+    const uint8_t byte = blk[48 + chunk * 32 + b];
+    const int top = (blk[16 + b] >> j) & 1;                   // bit-plane j of the shared 32 bytes
+    const float q = (float)(((j & 1) ? (byte >> 4) : (byte & 0x0F)) + 16 * top);
+    const float product = __fmul_rn(__fmul_rn(f16_at(blk), sc), q);
+    return __fsub_rn(product, __fmul_rn(f16_at(blk + 2), m));
+}
+
+__device__ __forceinline__ float q6k_decode_elem(const uint8_t* row, int k) {
+    const uint8_t* blk = row + (size_t)(k >> 8) * Q6K_BLOCK_BYTES;
+    const int within = k & 255, half = within >> 7, r = within & 127, quarter = r >> 5, l = r & 31;
+    const uint8_t lo = blk[half * 64 + l + ((quarter & 1) ? 32 : 0)];
+    const uint8_t hi = blk[128 + half * 32 + l];
+    const int low4 = (quarter & 2) ? (lo >> 4) : (lo & 0x0F);
+    const int q = (low4 | (((hi >> (2 * quarter)) & 3) << 4)) - 32;
+    const float s = (float)(int8_t)blk[192 + half * 8 + (l >> 4) + 2 * quarter];
+    return __fmul_rn(__fmul_rn(f16_at(blk + 208), s), (float)q);
+}
+
 // ---------------------------------------------------------------------------------------------
 // the handle
 // ---------------------------------------------------------------------------------------------
@@ -214,6 +259,8 @@ int launch_experts_simt(MummuMoe* m, const void* x, int x_dtype, const int32_t* 
 int launch_q4k_dequant(const void* src, float* dst, int64_t n_blocks, cudaStream_t s);
 int launch_q4k_quantize(const float* src, void* dst, int64_t n_blocks, cudaStream_t s);
 int launch_widen(const void* src, int dtype, float* dst, int64_t n, cudaStream_t s);
+int launch_block_dequant(const void* src, int dtype, float* dst, int64_t rows, int64_t cols, size_t row_bytes,
+                         cudaStream_t s);
 
 // ---- prefill_tc.cu ----
 bool prefill_tc_supported(const MummuMoeConfig& c, int64_t rows_total);

@@ -1140,6 +1140,37 @@ template <typename TW> __device__ __forceinline__ float load_w(const uint8_t* ro
 template <> __device__ __forceinline__ float load_w<q4k_t>(const uint8_t* row, int k) {
     return q4k_decode_elem(row, k);
 }
+template <> __device__ __forceinline__ float load_w<q80_t>(const uint8_t* row, int k) { return q80_decode_elem(row, k); }
+template <> __device__ __forceinline__ float load_w<q5k_t>(const uint8_t* row, int k) { return q5k_decode_elem(row, k); }
+template <> __device__ __forceinline__ float load_w<q6k_t>(const uint8_t* row, int k) { return q6k_decode_elem(row, k); }
+
+// rows of a block-quantised matrix -> f32 [rows, cols] (mummu_moe_dequant_bank for the sibling formats)
+template <typename TW>
+__global__ void block_dequant_kernel(const uint8_t* src, float* dst, int64_t rows, int64_t cols, size_t row_bytes) {
+    const int64_t n = rows * cols;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols;
+        dst[i] = load_w<TW>(src + (size_t)r * row_bytes, (int)(i - r * cols));
+    }
+}
+
+int launch_block_dequant(const void* src, int dtype, float* dst, int64_t rows, int64_t cols, size_t row_bytes,
+                         cudaStream_t s) {
+    const int64_t n = rows * cols;
+    const unsigned blocks = (unsigned)std::min<int64_t>((n + 255) / 256, 148 * 16);
+    const uint8_t* p = (const uint8_t*)src;
+    switch (dtype) {
+        case MUMMU_Q4_K: block_dequant_kernel<q4k_t><<<blocks, 256, 0, s>>>(p, dst, rows, cols, row_bytes); break;
+        case MUMMU_Q8_0: block_dequant_kernel<q80_t><<<blocks, 256, 0, s>>>(p, dst, rows, cols, row_bytes); break;
+        case MUMMU_Q5_K: block_dequant_kernel<q5k_t><<<blocks, 256, 0, s>>>(p, dst, rows, cols, row_bytes); break;
+        case MUMMU_Q6_K: block_dequant_kernel<q6k_t><<<blocks, 256, 0, s>>>(p, dst, rows, cols, row_bytes); break;
+        default:
+            set_error("block dequant: dtype %d is not a block format", dtype);
+            return MUMMU_ERR_CONTRACT;
+    }
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
@@ -1308,6 +1339,9 @@ static int simt_by_weight(MummuMoe* m, const void* x, const int32_t* row_index,
         case MUMMU_F16: return simt_two_stage<TA, __half>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
         case MUMMU_BF16: return simt_two_stage<TA, __nv_bfloat16>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
         case MUMMU_Q4_K: return simt_two_stage<TA, q4k_t>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
+        case MUMMU_Q8_0: return simt_two_stage<TA, q80_t>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
+        case MUMMU_Q5_K: return simt_two_stage<TA, q5k_t>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
+        case MUMMU_Q6_K: return simt_two_stage<TA, q6k_t>(m, x, row_index, counts, offsets, max_rows, ys, ys_dtype, expert_only, rows_single, s);
     }
     set_error("experts: bad weight dtype %d", m->cfg.weight_dtype);
     return MUMMU_ERR_CONTRACT;

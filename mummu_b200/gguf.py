@@ -369,7 +369,7 @@ def olmoe_moe_shape(f: GgufFile) -> OlmoeMoeShape:
                          need("olmoe.block_count"))
 
 
-_BANK_CODES = {"Q4_K": "Q4_K", "F32": "F32", "F16": "F16", "BF16": "BF16"}
+_BANK_CODES = {"Q4_K": "Q4_K", "Q8_0": "Q8_0", "Q5_K": "Q5_K", "Q6_K": "Q6_K", "F32": "F32", "F16": "F16", "BF16": "BF16"}
 
 
 def load_moe_layer(f: GgufFile, layer: int, device: int = 0, act_dtype: Optional[int] = None, max_tokens: int = 0):
@@ -390,14 +390,15 @@ def load_moe_layer(f: GgufFile, layer: int, device: int = 0, act_dtype: Optional
         if t.dims != dims:
             raise ValueError(f"'{pre + name}' dims {t.dims} do not match {dims}")
         if t.dtype not in _BANK_CODES:
-            raise NotImplementedError(f"'{pre + name}' is {t.dtype}: this path takes Q4_K, F32, F16 and BF16 banks")
+            raise NotImplementedError(f"'{pre + name}' is {t.dtype}: this path takes Q4_K, Q8_0, Q5_K, Q6_K, F32, F16 and BF16 banks")
         kinds.add(t.dtype)
     if len(kinds) != 1:
         raise NotImplementedError(f"layer {layer} mixes bank types {sorted(kinds)}")
     kind = kinds.pop()
-    wcode = {"Q4_K": L.Q4_K, "F32": L.F32, "F16": L.F16, "BF16": L.BF16}[kind]
+    wcode = {"Q4_K": L.Q4_K, "Q8_0": L.Q8_0, "Q5_K": L.Q5_K, "Q6_K": L.Q6_K, "F32": L.F32, "F16": L.F16,
+             "BF16": L.BF16}[kind]
     if act_dtype is None:
-        act_dtype = {"Q4_K": L.F16, "F32": L.F32, "F16": L.F16, "BF16": L.BF16}[kind]
+        act_dtype = {"F32": L.F32, "BF16": L.BF16}.get(kind, L.F16)
     rt = f.tensor(pre + "ffn_gate_inp.weight")
     if rt is None or rt.dims != [H, E] or rt.dtype not in ("F32", "F16"):
         raise ValueError(f"'{pre}ffn_gate_inp.weight' must be an F32 or F16 [hidden={H}, experts={E}] tensor")
@@ -408,7 +409,7 @@ def load_moe_layer(f: GgufFile, layer: int, device: int = 0, act_dtype: Optional
     banks = []
     for name in want:
         raw = f.tensor_bytes(pre + name)
-        if kind == "Q4_K":
+        if kind in ("Q4_K", "Q8_0", "Q5_K", "Q6_K"):
             banks.append(raw)
         elif kind == "F32":
             banks.append(raw.view(np.float32).reshape(f.tensor(pre + name).shape))

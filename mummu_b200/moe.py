@@ -139,7 +139,8 @@ class SparseMoe:
 
     def set_bank(self, which: int, data) -> None:
         """One of `MoeExperts::{gate, up, down}` (nn/moe.rs:22-30), [experts, out, in]; numpy
-        (f32/f16, uint16 bit patterns for bf16, uint8 Q4_K bytes) or a torch CUDA tensor."""
+        (f32/f16, uint16 bit patterns for bf16, uint8 bytes of a block format) or a torch CUDA
+        tensor."""
         if _is_torch(data):
             t = data.contiguous()
             _check(L.lib.mummu_moe_set_bank(self._h, which, t.data_ptr(),
@@ -356,7 +357,8 @@ class CudaExpert:
 
     def resident_bytes(self) -> int:
         c = self.moe.cfg
-        per = {L.F32: 4.0, L.F16: 2.0, L.BF16: 2.0, L.Q4_K: 144.0 / 256.0}[self.moe.weight_dtype]
+        per = {L.F32: 4.0, L.F16: 2.0, L.BF16: 2.0, L.Q4_K: 144.0 / 256.0, L.Q8_0: 34.0 / 32.0,
+               L.Q5_K: 176.0 / 256.0, L.Q6_K: 210.0 / 256.0}[self.moe.weight_dtype]
         return int(3 * c.hidden_size * c.expert_intermediate_size * per)
 
 

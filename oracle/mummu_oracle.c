@@ -130,6 +130,88 @@ void orc_dequant_q4_k_blocks(const uint8_t* bytes, int64_t n_blocks, float* out)
     for (int64_t b = 0; b < n_blocks; ++b) orc_dequant_q4_k(bytes + b * 144, out + b * 256);
 }
 
+/* Q8_0 — gguf.rs:1535-1543: 34 bytes = f16 d + 32 i8; x = d * q. */
+void orc_dequant_q8_0(const uint8_t* block, float* out) {
+    float d = orc_f16_to_f32((uint16_t)(block[0] | (block[1] << 8)));
+    for (int i = 0; i < 32; ++i) out[i] = d * (float)(int8_t)block[2 + i];
+}
+
+/* Q5_K — gguf.rs:1731-1765: 176 bytes = f16 d, f16 dmin, 12 B packed 6-bit (scale, min) pairs,
+ * 32 B of fifth bits, 128 B of nibbles.  Chunk c (64 values) reads 32 nibble bytes (low nibbles
+ * first) and bit planes 2c (low nibbles) and 2c+1 (high nibbles) of the shared 32 bytes;
+ * x = d*sc*(q + 16*bit) - dmin*m with the products rounded as in Q4_K. */
+void orc_dequant_q5_k(const uint8_t* block, float* out) {
+    float d = orc_f16_to_f32((uint16_t)(block[0] | (block[1] << 8)));
+    float dmin = orc_f16_to_f32((uint16_t)(block[2] | (block[3] << 8)));
+    const uint8_t* scales = block + 4;
+    const uint8_t* qh = block + 16;
+    const uint8_t* qs = block + 48;
+    uint8_t u1 = 1, u2 = 2;
+    for (int chunk = 0; chunk < 4; ++chunk) {
+        float sc1, m1, sc2, m2;
+        scale_min_k4(scales, chunk * 2, &sc1, &m1);
+        scale_min_k4(scales, chunk * 2 + 1, &sc2, &m2);
+        const uint8_t* q = qs + chunk * 32;
+        float min1 = dmin * m1;
+        float min2 = dmin * m2;
+        for (int b = 0; b < 32; ++b) {
+            int top = (qh[b] & u1) ? 16 : 0;
+            float ds = d * sc1;
+            float product = ds * (float)((q[b] & 0x0F) + top);
+            out[chunk * 64 + b] = product - min1;
+        }
+        for (int b = 0; b < 32; ++b) {
+            int top = (qh[b] & u2) ? 16 : 0;
+            float ds = d * sc2;
+            float product = ds * (float)((q[b] >> 4) + top);
+            out[chunk * 64 + 32 + b] = product - min2;
+        }
+        u1 = (uint8_t)(u1 << 2);
+        u2 = (uint8_t)(u2 << 2);
+    }
+}
+
+/* Q6_K — gguf.rs:1769-1797: 210 bytes = 128 B low nibbles, 64 B high bit pairs, 16 i8 sub-scales,
+ * f16 d; two halves of 128 values; x = d * s * (q - 32), `d*s` first. */
+void orc_dequant_q6_k(const uint8_t* block, float* out) {
+    const uint8_t* lows = block;
+    const uint8_t* highs = block + 128;
+    const uint8_t* scales = block + 192;
+    float d = orc_f16_to_f32((uint16_t)(block[208] | (block[209] << 8)));
+    for (int h = 0; h < 2; ++h) {
+        const uint8_t* ql = lows + h * 64;
+        const uint8_t* qh = highs + h * 32;
+        const uint8_t* sc = scales + h * 8;
+        float* y = out + h * 128;
+        for (int l = 0; l < 32; ++l) {
+            int is = l / 16;
+            int q1 = (int)((ql[l] & 0x0F) | ((qh[l] & 3) << 4)) - 32;
+            int q2 = (int)((ql[l + 32] & 0x0F) | (((qh[l] >> 2) & 3) << 4)) - 32;
+            int q3 = (int)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+            int q4 = (int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+            float s0 = d * (float)(int8_t)sc[is], s2 = d * (float)(int8_t)sc[is + 2];
+            float s4 = d * (float)(int8_t)sc[is + 4], s6 = d * (float)(int8_t)sc[is + 6];
+            y[l] = s0 * (float)q1;
+            y[l + 32] = s2 * (float)q2;
+            y[l + 64] = s4 * (float)q3;
+            y[l + 96] = s6 * (float)q4;
+        }
+    }
+}
+
+/* kind: 4 = Q8_0, 5 = Q5_K, 6 = Q6_K, 3 = Q4_K (the codes of the C ABI's weight dtypes) */
+int orc_dequant_blocks(int kind, const uint8_t* bytes, int64_t n_blocks, float* out) {
+    if (kind != 3 && kind != 4 && kind != 5 && kind != 6) return 1;
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < n_blocks; ++b) {
+        if (kind == 3) orc_dequant_q4_k(bytes + b * 144, out + b * 256);
+        else if (kind == 4) orc_dequant_q8_0(bytes + b * 34, out + b * 32);
+        else if (kind == 5) orc_dequant_q5_k(bytes + b * 176, out + b * 256);
+        else orc_dequant_q6_k(bytes + b * 210, out + b * 256);
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* scalar pieces                                                                               */
 /* ------------------------------------------------------------------------------------------ */

@@ -49,6 +49,8 @@ def lib() -> C.CDLL:
         L.orc_dot8.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
         L.orc_dequant_q4_k_blocks.restype = None
         L.orc_dequant_q4_k_blocks.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+        L.orc_dequant_blocks.restype = C.c_int
+        L.orc_dequant_blocks.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p]
         L.orc_router_logits.restype = None
         L.orc_router_logits.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                         C.c_int64, C.c_int, C.c_void_p]
@@ -114,6 +116,22 @@ def dequant_q4_k(raw) -> np.ndarray:
     nb = raw.size // 144
     out = np.empty(nb * 256, dtype=np.float32)
     lib().orc_dequant_q4_k_blocks(_p(raw), nb, _p(out))
+    return out
+
+
+BLOCK_FORMATS = {"Q4_K": (3, 256, 144), "Q8_0": (4, 32, 34), "Q5_K": (5, 256, 176), "Q6_K": (6, 256, 210)}
+
+
+def dequant_blocks(raw, kind: str) -> np.ndarray:
+    """Whole blocks of a GGUF block format -> f32 (gguf.rs:1535-1543 Q8_0, 1701-1726 Q4_K,
+    1731-1765 Q5_K, 1769-1797 Q6_K)."""
+    code, elems, nbytes = BLOCK_FORMATS[kind]
+    raw = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
+    assert raw.size % nbytes == 0, "whole blocks"
+    nb = raw.size // nbytes
+    out = np.empty(nb * elems, dtype=np.float32)
+    rc = lib().orc_dequant_blocks(code, _p(raw), nb, _p(out))
+    assert rc == 0
     return out
 
 

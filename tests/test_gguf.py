@@ -158,11 +158,11 @@ def test_loader_refuses_what_the_bank_cannot_take(tmp_path):
             ("blk.0.ffn_gate_exps.weight", [H, I, E], "Q4_K", z(q)),
             ("blk.0.ffn_up_exps.weight", [H, I, E], "Q4_K", z(q)),
             ("blk.0.ffn_down_exps.weight", [I, H, E], "Q4_K", z(q))]
-    # a bank stored as Q6_K: a real type, but not one this path computes from
+    # a bank stored as Q3_K: a real type, but not one this path computes from
     t = list(base)
-    t[3] = ("blk.0.ffn_down_exps.weight", [I, H, E], "Q6_K", z(E * I * H // 256 * 210))
+    t[3] = ("blk.0.ffn_down_exps.weight", [I, H, E], "Q3_K", z(E * I * H // 256 * 110))
     gguf.write_gguf(p, META, t)
-    with pytest.raises(NotImplementedError, match="Q6_K"):
+    with pytest.raises(NotImplementedError, match="Q3_K"):
         gguf.load_moe_layer(gguf.GgufFile.open(p), 0)
     # mixed bank types
     t = list(base)

@@ -104,8 +104,16 @@ static void free_scratch(MummuMoe* m) {
     m->cap_tokens = 0;
 }
 
+void clear_host_graphs(MummuMoe* m) {
+    for (auto& kv : m->host_graphs)
+        if (kv.second) cudaGraphExecDestroy(kv.second);
+    m->host_graphs.clear();
+    m->host_calls.clear();
+}
+
 int ensure_scratch(MummuMoe* m, int64_t tokens) {
     if (tokens <= m->cap_tokens) return MUMMU_OK;
+    clear_host_graphs(m);
     if (m->scratch_borrowed) {
         set_error("MoE: %lld tokens exceed the %lld the adopted scratch was sized for", (long long)tokens,
                   (long long)m->cap_tokens);
@@ -287,6 +295,7 @@ int32_t mummu_moe_destroy(MummuMoe* m) {
     {
         DeviceGuard guard(m->cfg.device);
         if (m->stream) cudaStreamSynchronize(m->stream);
+        clear_host_graphs(m);
         free_scratch(m);
         cudaFree(m->router_w); cudaFree(m->router_wt); cudaFree(m->router_bias);
         for (int b = 0; b < 3; ++b) cudaFree(m->bank[b]);
@@ -306,6 +315,7 @@ int32_t mummu_moe_set_router(MummuMoe* m, const void* w, int32_t dtype, int32_t 
                   "router weight dtype %d is not F32, F16 or BF16", dtype);
     MUMMU_REQUIRE(layout == MUMMU_ROUTER_IN_OUT || layout == MUMMU_ROUTER_OUT_IN, "router layout %d", layout);
     std::lock_guard<std::mutex> lock(m->mu);
+    clear_host_graphs(m);
     DeviceGuard guard(m->cfg.device);
     const int H = m->cfg.hidden, E = m->cfg.experts;
     std::vector<float> host((size_t)H * E);
@@ -355,10 +365,50 @@ int32_t mummu_moe_set_bank(MummuMoe* m, int32_t which, const void* data, size_t 
                   "mummu_moe_set_bank: bank %d needs %zu bytes ([experts %d, out, in]), got %zu", which,
                   m->bank_bytes[which], m->cfg.experts_local, bytes);
     std::lock_guard<std::mutex> lock(m->mu);
+    clear_host_graphs(m);
     DeviceGuard guard(m->cfg.device);
     MUMMU_CUDA_TRY(cudaMemcpy(m->bank[which], data, bytes,
                               on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
     m->bank_set[which] = true;
+    return MUMMU_OK;
+}
+
+// io_x -> io_y for a host-pointer call.  Decode-sized Q4_K calls are launch-bound: from the third
+// call with the same (tokens, top_k, norm) on, the layer's launches are replayed from a CUDA graph
+// captured on the second (the first runs eagerly so that one-time attribute calls are done).
+static int forward_host_staged(MummuMoe* m, int64_t tokens, int top_k, int norm, cudaStream_t s) {
+    static const bool enabled = !getenv("MUMMU_CUDA_NO_HOST_GRAPH");
+    if (!enabled || m->prof.enabled || !decode_q4k_supported(m->cfg, tokens))
+        return forward_device(m, m->io_x, m->io_y, tokens, top_k, norm, s);
+    const uint64_t key = ((uint64_t)tokens << 20) | ((uint64_t)top_k << 1) | (uint64_t)(norm != 0);
+    auto it = m->host_graphs.find(key);
+    if (it != m->host_graphs.end()) {
+        if (!it->second) return forward_device(m, m->io_x, m->io_y, tokens, top_k, norm, s);
+        MUMMU_CUDA_TRY(cudaGraphLaunch(it->second, s));
+        m->launches += m->host_calls[key];
+        return MUMMU_OK;
+    }
+    if (m->host_calls[key]++ == 0) return forward_device(m, m->io_x, m->io_y, tokens, top_k, norm, s);
+    // second call: capture
+    cudaGraphExec_t exec = nullptr;
+    cudaGraph_t graph = nullptr;
+    const int64_t before = m->launches;
+    if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        const int rc = forward_device(m, m->io_x, m->io_y, tokens, top_k, norm, s);
+        const cudaError_t end = cudaStreamEndCapture(s, &graph);
+        if (rc == MUMMU_OK && end == cudaSuccess && graph) {
+            if (cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) exec = nullptr;
+        }
+        if (graph) cudaGraphDestroy(graph);
+    }
+    cudaGetLastError();                         // a failed capture leaves a sticky-free error behind
+    m->host_graphs[key] = exec;
+    m->host_calls[key] = (int)(m->launches - before);   // launches one replay stands for
+    if (!exec) {
+        m->launches = before;
+        return forward_device(m, m->io_x, m->io_y, tokens, top_k, norm, s);
+    }
+    MUMMU_CUDA_TRY(cudaGraphLaunch(exec, s));
     return MUMMU_OK;
 }
 
@@ -382,7 +432,7 @@ int32_t mummu_moe_forward(MummuMoe* m, const void* x, void* y, int32_t tokens, i
     size_t bytes = (size_t)tokens * m->cfg.hidden * dtype_size(m->cfg.act_dtype);
     if (on_device) return forward_device(m, x, y, tokens, top_k, norm, s);
     MUMMU_CUDA_TRY(cudaMemcpyAsync(m->io_x, x, bytes, cudaMemcpyHostToDevice, s));
-    if ((rc = forward_device(m, m->io_x, m->io_y, tokens, top_k, norm, s))) return rc;
+    if ((rc = forward_host_staged(m, tokens, top_k, norm, s))) return rc;
     MUMMU_CUDA_TRY(cudaMemcpyAsync(y, m->io_y, bytes, cudaMemcpyDeviceToHost, s));
     return read_status(m, s);
 }
@@ -568,6 +618,7 @@ int32_t mummu_moe_adopt_scratch(MummuMoe* m, MummuMoe* donor) {
                       a.top_k == b.top_k && a.act_dtype == b.act_dtype && !donor->scratch_borrowed,
                   "mummu_moe_adopt_scratch: the two layers must have the same shape, dtype and device");
     std::lock_guard<std::mutex> lock(m->mu);
+    clear_host_graphs(m);
     DeviceGuard guard(a.device);
     MUMMU_CUDA_TRY(cudaDeviceSynchronize());
     free_scratch(m);

@@ -208,6 +208,10 @@ struct MummuMoe {
     const void* q4k_map128_base[3] = {nullptr, nullptr, nullptr};
     int64_t launches = 0;
     mummu::Profiler prof;
+    // host-pointer decode calls: the layer's launches captured once per (tokens, top_k, norm) and
+    // replayed (every pointer inside is the handle's own); value null = capture failed, stay eager
+    std::map<uint64_t, cudaGraphExec_t> host_graphs;
+    std::map<uint64_t, int> host_calls;
 };
 
 namespace mummu {
@@ -215,6 +219,7 @@ namespace mummu {
 size_t bank_row_bytes(const MummuMoeConfig& c, int which);
 size_t bank_total_bytes(const MummuMoeConfig& c, int which);
 int ensure_scratch(MummuMoe* m, int64_t tokens);
+void clear_host_graphs(MummuMoe* m);
 
 // Opt a kernel into the full 227 KB of dynamic shared memory, once per (kernel, device): the
 // attribute call is kept out of the steady state so that a layer call can be stream-captured.

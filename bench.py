@@ -282,7 +282,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         roof = {"bound": "hbm", "kernel": "q4k_gate_up", "achieved": ach, "peak": peak, "unit": "GB/s",
                 "frac": ach / peak, "peak_kind": peak_kind,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this very shape
-                # (T=64, 64 experts hit), from the ncu capture summarised in profiles/decode_q4k_gate_up_T64.md
+                # (T=64, 64 experts hit), from the ncu capture summarised in profiles/decode_q4k_tma_gate_up_T64.md
                 "traffic": 156.7e6 if (T == 64 and u_mean == 64.0) else None,
                 "algorithmic_bytes_per_launch": gu_bytes, "frac_of_nominal_8TBs": ach / 8000.0}
     layer_bytes = u_mean * EXPERT_BYTES_Q4K + H * E * 4 + 2 * T * H * 2
@@ -290,9 +290,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # ---- end to end through the host-pointer C ABI call: pinned host buffers in and out ----
     hx = [x.cpu().pin_memory() for x in xs]
     hx_np = [h.numpy() for h in hx]
+    hy_np = [torch.empty_like(h).pin_memory().numpy() for h in hx]      # results land in pinned memory too
     def e2e_step():
-        for m, xn in zip(layers, hx_np):
-            m.forward(xn, K, False)     # H2D copy, layer, D2H copy, stream sync: all inside the call
+        for m, xn, yn in zip(layers, hx_np, hy_np):
+            m.forward(xn, K, False, out=yn)     # H2D copy, layer, D2H copy, stream sync: all inside the call
     for _ in range(3):
         e2e_step()
     torch.cuda.synchronize()

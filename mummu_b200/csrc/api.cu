@@ -175,8 +175,14 @@ static int check_top_k(const MummuMoe* m, int top_k) {
 
 static int read_status(MummuMoe* m, cudaStream_t s) {
     int32_t st = 0;
-    MUMMU_CUDA_TRY(cudaMemcpyAsync(&st, m->status, sizeof(st), cudaMemcpyDeviceToHost, s));
-    MUMMU_CUDA_TRY(cudaStreamSynchronize(s));
+    if (m->status_host) {
+        MUMMU_CUDA_TRY(cudaMemcpyAsync(m->status_host, m->status, sizeof(st), cudaMemcpyDeviceToHost, s));
+        MUMMU_CUDA_TRY(cudaStreamSynchronize(s));
+        st = *m->status_host;
+    } else {
+        MUMMU_CUDA_TRY(cudaMemcpyAsync(&st, m->status, sizeof(st), cudaMemcpyDeviceToHost, s));
+        MUMMU_CUDA_TRY(cudaStreamSynchronize(s));
+    }
     if (st == 0) return MUMMU_OK;
     MUMMU_CUDA_TRY(cudaMemsetAsync(m->status, 0, sizeof(int32_t), s));
     if (st & STATUS_TIMEOUT) {
@@ -280,6 +286,10 @@ int32_t mummu_moe_create(const MummuMoeConfig* cfg, MummuMoe** out) {
         if ((rc = dev_alloc(&m->status, 1))) break;
         cudaMemset(m->hits, 0, sizeof(unsigned long long) * cfg->experts);
         cudaMemset(m->status, 0, sizeof(int32_t));
+        if (cudaHostAlloc((void**)&m->status_host, sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess) {
+            m->status_host = nullptr;       // pageable reads still work
+            cudaGetLastError();
+        }
         if (cfg->max_tokens > 0) rc = ensure_scratch(m, cfg->max_tokens);
     } while (0);
     if (rc) {
@@ -300,6 +310,7 @@ int32_t mummu_moe_destroy(MummuMoe* m) {
         cudaFree(m->router_w); cudaFree(m->router_wt); cudaFree(m->router_bias);
         for (int b = 0; b < 3; ++b) cudaFree(m->bank[b]);
         cudaFree(m->counts); cudaFree(m->offsets); cudaFree(m->hits); cudaFree(m->status);
+        if (m->status_host) cudaFreeHost(m->status_host);
         cudaFree(m->active); cudaFree(m->n_active);
         for (auto& p : m->prof.pending) { cudaEventDestroy(p.a); cudaEventDestroy(p.b); }
         for (auto e : m->prof.pool) cudaEventDestroy(e);

@@ -201,6 +201,7 @@ struct MummuMoe {
     void* io_y = nullptr;
     unsigned long long* hits = nullptr;  // [experts]
     int32_t* status = nullptr;      // device status word
+    int32_t* status_host = nullptr; // pinned landing place for reads of the status word
     // cached tensor maps (CUtensorMap, 128 B each) of the Q4_K banks as [rows, row_bytes] byte views
     alignas(64) unsigned char q4k_map[3][128];
     const void* q4k_map_base[3] = {nullptr, nullptr, nullptr};

@@ -155,8 +155,9 @@ class SparseMoe:
         self.set_bank(L.BANK_DOWN, down)
 
     # -- the layer ----------------------------------------------------------------------------
-    def forward(self, x, top_k: int, norm_topk_prob: bool):
-        """[b, t, hidden] -> [b, t, hidden] (nn/moe.rs:116-177, 214-219)."""
+    def forward(self, x, top_k: int, norm_topk_prob: bool, out=None):
+        """[b, t, hidden] -> [b, t, hidden] (nn/moe.rs:116-177, 214-219).  `out`: optional host
+        array for the result of a host-pointer call (e.g. pinned memory; same shape and dtype)."""
         shape = tuple(x.shape)
         h = shape[-1]
         if h != self.cfg.hidden_size:
@@ -172,7 +173,12 @@ class SparseMoe:
                                            int(bool(norm_topk_prob)), 1, _torch_stream()))
             return y.view(shape)
         xa = self._host_act(x)
-        y = np.empty_like(xa)
+        if out is None:
+            y = np.empty_like(xa)
+        else:
+            y = out
+            if y.dtype != xa.dtype or y.size != xa.size or not y.flags["C_CONTIGUOUS"]:
+                raise MoeContractError("MoE forward: `out` must be a contiguous array of the input's dtype and size")
         _check(L.lib.mummu_moe_forward(self._h, xa.ctypes.data, y.ctypes.data, tokens, top_k,
                                        int(bool(norm_topk_prob)), 0, None))
         return y.reshape(shape)

@@ -335,6 +335,40 @@ def test_q4k_grouped_rows_many_passes(M, cuda_lib, olmoe_q4k_layer):
     m.close()
 
 
+def test_host_pointer_calls_replay_a_graph(M, cuda_lib):
+    """Host-pointer decode calls: the first runs eagerly, the second is captured, later ones are
+    replayed.  Same bits every time, on new inputs, into a caller-provided output array, and after
+    the router or a bank changed (which drops the captured graphs)."""
+    L = cuda_lib
+    H, I, E, K, T = 1024, 512, 16, 4, 24
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=4)
+    banks = [q4k.quantize(b) for b in (gate, up, down)]
+    a = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, *banks)
+    b = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, *banks)     # only ever called once per state
+    xh = x.astype(np.float16)
+    first = b.forward(xh, K, False)
+    for _ in range(5):
+        assert np.array_equal(a.forward(xh, K, False), first)
+    x2 = (xh * 0.5).astype(np.float16)
+    out = np.empty_like(x2)
+    got = a.forward(x2, K, False, out=out)
+    assert got.base is out or got is out
+    assert np.array_equal(out, b.forward(x2, K, False))
+    a.set_router(router * 2.0)
+    b.set_router(router * 2.0)
+    assert np.array_equal(a.forward(x2, K, False), b.forward(x2, K, False))
+    swapped = np.ascontiguousarray(banks[2].reshape(E, -1)[::-1])          # experts in reverse order
+    a.set_bank(L.BANK_DOWN, swapped)
+    b.set_bank(L.BANK_DOWN, swapped)
+    for _ in range(3):
+        ya = a.forward(x2, K, False)
+    assert np.array_equal(ya, b.forward(x2, K, False))
+    with pytest.raises(M.MoeContractError):
+        a.forward(x2, K, False, out=np.empty((3, 3), np.float16))
+    a.close()
+    b.close()
+
+
 def test_q4k_small_golden(M, cuda_lib):
     L = cuda_lib
     gold = np.load(os.path.join(HERE, "golden", "q4k_small.npz"))

@@ -1039,7 +1039,8 @@ template <typename T> __device__ __forceinline__ void store8(T* p, const float (
     *reinterpret_cast<Vec8<T>*>(p) = r;
 }
 
-template <typename TY, typename TO>
+// BATCH expert rows in flight per thread: 8 for decode-sized calls (latency), 4 for large T (occupancy)
+template <typename TY, typename TO, int BATCH>
 __global__ void __launch_bounds__(256) combine_vec8_kernel(const TY* ys, const int32_t* ids, const float* w,
                                                            const int32_t* pos, int top_k, int H, TO* out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -1059,13 +1060,13 @@ __global__ void __launch_bounds__(256) combine_vec8_kernel(const TY* ys, const i
     __syncthreads();
     for (int h = (blockIdx.y * blockDim.x + threadIdx.x) * 8; h < H; h += gridDim.y * blockDim.x * 8) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int r0 = 0; r0 < top_k; r0 += 8) {
-            float v[8][8];   // eight experts' rows in flight at once
+        for (int r0 = 0; r0 < top_k; r0 += BATCH) {
+            float v[BATCH][8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
+            for (int u = 0; u < BATCH; ++u)
                 if (r0 + u < top_k) load8(ys + (size_t)s_pos[r0 + u] * H + h, v[u]);
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
+            for (int u = 0; u < BATCH; ++u)
                 if (r0 + u < top_k) {
                     const float wv = s_w[r0 + u];
 #pragma unroll
@@ -1091,13 +1092,16 @@ static int launch_combine_y(MummuMoe* m, const void* ys, const int32_t* ids, con
     if (vec) {
         switch (m->cfg.act_dtype) {
             case MUMMU_F32:
-                combine_vec8_kernel<TY, float><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
+                if (tokens < 128) combine_vec8_kernel<TY, float, 8><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
+                else combine_vec8_kernel<TY, float, 4><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (float*)out);
                 break;
             case MUMMU_F16:
-                combine_vec8_kernel<TY, __half><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__half*)out);
+                if (tokens < 128) combine_vec8_kernel<TY, __half, 8><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__half*)out);
+                else combine_vec8_kernel<TY, __half, 4><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__half*)out);
                 break;
             case MUMMU_BF16:
-                combine_vec8_kernel<TY, __nv_bfloat16><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__nv_bfloat16*)out);
+                if (tokens < 128) combine_vec8_kernel<TY, __nv_bfloat16, 8><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__nv_bfloat16*)out);
+                else combine_vec8_kernel<TY, __nv_bfloat16, 4><<<grid, vthreads, smem, s>>>((const TY*)ys, ids, w, pos, top_k, H, (__nv_bfloat16*)out);
                 break;
         }
         MUMMU_CUDA_TRY(cudaGetLastError());

@@ -282,7 +282,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         roof = {"bound": "hbm", "kernel": "q4k_gate_up", "achieved": ach, "peak": peak, "unit": "GB/s",
                 "frac": ach / peak, "peak_kind": peak_kind,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this very shape
-                # (T=64, 64 experts hit), from the ncu capture summarised in profiles/decode_q4k_tma_gate_up_T64.md
+                # (T=64, 64 experts hit), from an ncu capture of this kernel (summary under profiles/)
                 "traffic": 156.7e6 if (T == 64 and u_mean == 64.0) else None,
                 "algorithmic_bytes_per_launch": gu_bytes, "frac_of_nominal_8TBs": ach / 8000.0}
     layer_bytes = u_mean * EXPERT_BYTES_Q4K + H * E * 4 + 2 * T * H * 2

@@ -1,4 +1,4 @@
-// Decode-regime expert bank over GGUF Q4_K weights (tokens <= 64, f16 activations).
+// Decode-regime expert bank over GGUF Q4_K weights (tokens <= 256, f16 activations).
 //
 // HBM-bound: every routed expert's gate/up/down bytes are streamed once, the activations are tiny.
 // Two kernels share one body:
@@ -726,7 +726,9 @@ decode_q4k_tma_kernel(DecodeArgs a, const __grid_constant__ CUtensorMap map0, co
 }
 
 bool decode_q4k_supported(const MummuMoeConfig& c, int64_t tokens) {
-    return c.weight_dtype == MUMMU_Q4_K && c.act_dtype == MUMMU_F16 && tokens >= 1 && tokens <= 64 &&
+    // up to 256 tokens: beyond one 16-row token tile per expert the kernels make several passes
+    // (shared between CTAs), still far ahead of the generic bank
+    return c.weight_dtype == MUMMU_Q4_K && c.act_dtype == MUMMU_F16 && tokens >= 1 && tokens <= 256 &&
            c.hidden % 256 == 0 && c.inter % 256 == 0 && c.hidden <= 8192 && c.inter <= 8192;
 }
 

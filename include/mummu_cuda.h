@@ -13,7 +13,12 @@
  *    MUMMU_ERR_CONTRACT with a message that carries the reference's panic stem ("top_k",
  *    "num_experts_per_tok", ...), so a Rust wrapper can re-raise the panic the reference raises
  *    (nn/moe.rs:62-76, 119-126, 250-253).
- *  - A handle serialises its own calls with an internal lock; distinct handles are independent.
+ *  - A handle serialises the HOST side of its calls with an internal lock; distinct handles are
+ *    independent.  The device side is ordered by the stream a call is given: calls of one handle on
+ *    two different streams share the handle's scratch buffers and must not overlap on the GPU
+ *    (order them with events, or give each stream its own handle; handles can share weights'
+ *    source buffers but not scratch).  mummu_moe_set_router / mummu_moe_set_bank wait for the
+ *    handle's own stream; work the caller queued on its own streams must have finished first.
  *  - Matrices are row-major.  Router weight: [hidden, experts] (burn `Linear` stores [in, out],
  *    nn/moe.rs:1642) or [experts, hidden] (GGUF `ffn_gate_inp`, models/olmoe.rs:338-339), chosen by
  *    a flag.  Banks: [experts, out, in], byte-identical to GGUF `ffn_{gate,up,down}_exps`
@@ -146,6 +151,11 @@ int32_t mummu_moe_permute(MummuMoe* moe, const int32_t* ids, int32_t tokens, int
  * down(silu(gate x) * (up x)) per row. */
 int32_t mummu_moe_experts_grouped(MummuMoe* moe, const void* xs, const int32_t* counts,
                                   int32_t rows, void* ys, void* stream);
+/* The same when the handle already holds the experts' first rows and work order for `counts`
+ * (left there by mummu_ep_dispatch, which plans them from the gathered counts): saves the launch
+ * that derives them. */
+int32_t mummu_moe_experts_planned(MummuMoe* moe, const void* xs, const int32_t* counts,
+                                  int32_t rows, void* ys, void* stream);
 
 /* Weighted un-permute — the scatter-add of nn/moe.rs:317-325 / 1589-1602 as a gather: for every
  * token, out = sum over its top_k slots in ASCENDING EXPERT ID of (w * y) with the product and the
@@ -171,42 +181,48 @@ int32_t mummu_ep_open(int32_t device, const uint8_t* handle64, void** ptr);
 int32_t mummu_ep_close(void* ptr);
 int32_t mummu_ep_free(void* ptr);
 
-/* From the all-gathered row counts all_counts[world, experts] (device): dst_base[experts] = first
- * row, in the owning rank's buffers, of THIS rank's rows for each global expert;
- * local_counts[experts_local] = rows per local expert over all sources.  Buffers are expert-major
- * with sources in rank order inside an expert, so every expert's rows are in a fixed order. */
-int32_t mummu_ep_plan(MummuMoe* moe, const int32_t* all_counts, int32_t rank, int32_t world,
-                      int32_t* dst_base, int32_t* local_counts, void* stream);
-
-/* Device-side signalling between the ranks of an expert-parallel group (one rank per GPU), so that
- * a step needs no library collective and can be replayed from a CUDA graph.  Every rank allocates
- * mummu_ep_sync_bytes(world, experts) with mummu_ep_alloc (which zeroes it) and maps the peers'
- * blocks; peer_sync[r] is rank r's block as seen from this device.
- *   mummu_ep_exchange_plan: all-gather of the per-expert row counts by peer stores + what
- *     mummu_ep_plan computes, in one launch (replaces the counts all-gather of nn/moe.rs's host
- *     exchange, crates/mummu/src/backend.rs:128-143).
- *   mummu_ep_barrier: every rank's earlier work on `stream` is visible to every rank after it.
- * Waits are bounded (about a second); on expiry the status word is raised (MUMMU_ERR_TIMEOUT from
- * the next mummu_moe_sync) and the kernel returns.  Every rank must issue the same sequence. */
+/* One expert-parallel layer on one rank is four stages that signal each other ONE WAY through the
+ * ranks' sync blocks (every rank allocates mummu_ep_sync_bytes(world, experts) with mummu_ep_alloc,
+ * which zeroes it, and maps the peers' blocks; peer_sync[r] is rank r's block as seen from this
+ * device): a stage's last block stores its epoch into a flag of every peer, a later stage polls its
+ * own flags.  No kernel both signals and waits, no library collective and no host round trip is
+ * inside a step, so a step can be replayed from a CUDA graph; and the stages of several rank
+ * handles may be issued stage by stage on one stream of ONE device (how the exchange is tested on
+ * a single GPU).  Every rank issues the same sequence.  Waits are bounded (switch WAIT_POLLS; the
+ * default is a few seconds): on expiry the stage skips its data movement, raises the status word
+ * (MUMMU_ERR_TIMEOUT from the next mummu_moe_sync) and returns; the group must then be re-zeroed
+ * with mummu_ep_reset on every rank, behind a host barrier, before it is used again.
+ *
+ *   mummu_ep_post_counts  stage 1: counts[experts] (this rank's rows per global expert, device)
+ *                         -> every rank; replaces the host exchange of backend.rs:128-143.
+ *   mummu_ep_dispatch     stage 2: waits for every rank's counts; computes dst_base[experts] (first
+ *                         row, in the owning rank's buffers, of THIS rank's rows per expert; buffers
+ *                         are expert-major with sources in rank order, so every expert's rows are in
+ *                         a fixed order) and local_counts[experts_local]; copies x[row_token[p]] for
+ *                         every sorted row p (mummu_moe_permute order) into the owner's receive
+ *                         buffer peer_recv[owner] ([cap_rows, hidden], 16-bit) with peer stores.  A
+ *                         row that would land at or beyond cap_rows is dropped and reported
+ *                         (MUMMU_ERR_CONTRACT from the next mummu_moe_sync).
+ *   mummu_ep_experts      stage 3: waits for every rank's rows; runs this rank's experts over its
+ *                         receive buffer into its output buffer ys_own ([cap_rows, hidden]).
+ *   mummu_ep_combine      stage 4: waits for every rank's outputs; mummu_moe_combine reading each
+ *                         expert output row from its owner's buffer peer_ys[owner] with peer loads. */
 size_t mummu_ep_sync_bytes(int32_t world, int32_t experts);
-int32_t mummu_ep_exchange_plan(MummuMoe* moe, const int32_t* counts, void* const* peer_sync,
-                               int32_t rank, int32_t world, int32_t* dst_base,
-                               int32_t* local_counts, void* stream);
-int32_t mummu_ep_barrier(MummuMoe* moe, void* const* peer_sync, int32_t rank, int32_t world,
-                         void* stream);
-
-/* Dispatch: for every sorted row p of this rank (mummu_moe_permute order) copy x[row_token[p]]
- * into the owner's receive buffer at dst_base[e] + (p - offsets[e]), with peer stores.
- * peer_recv: HOST array of `world` device pointers ([cap_rows, hidden], 16-bit activations). */
+int32_t mummu_ep_reset(int32_t device, void* own_sync, int32_t world, int32_t experts);
+int32_t mummu_ep_post_counts(MummuMoe* moe, const int32_t* counts, void* const* peer_sync,
+                             int32_t rank, int32_t world, void* stream);
 int32_t mummu_ep_dispatch(MummuMoe* moe, const void* x, const int32_t* row_token,
-                          const int32_t* offsets, const int32_t* dst_base, void* const* peer_recv,
-                          int32_t world, int32_t rows, void* stream);
-
-/* Combine: mummu_moe_combine, reading each expert output row from its owner's buffer peer_ys[rank]
- * (same row numbering as the receive buffer) with peer loads. */
-int32_t mummu_ep_combine(MummuMoe* moe, void* const* peer_ys, const int32_t* ids, const float* w,
-                         const int32_t* pos, const int32_t* offsets, const int32_t* dst_base,
-                         int32_t tokens, int32_t top_k, int32_t world, void* out, void* stream);
+                          const int32_t* offsets, void* const* peer_sync, void* const* peer_recv,
+                          int32_t rank, int32_t world, int32_t rows, int64_t cap_rows,
+                          int32_t* dst_base, int32_t* local_counts, void* stream);
+int32_t mummu_ep_experts(MummuMoe* moe, void* const* peer_sync, int32_t rank, int32_t world,
+                         const void* recv_own, const int32_t* local_counts, int64_t rows_cap,
+                         void* ys_own, void* stream);
+int32_t mummu_ep_combine(MummuMoe* moe, void* const* peer_sync, void* const* peer_ys,
+                         const int32_t* ids, const float* w, const int32_t* pos,
+                         const int32_t* offsets, const int32_t* dst_base, int32_t rank,
+                         int32_t world, int32_t tokens, int32_t top_k, int64_t cap_rows, void* out,
+                         void* stream);
 
 /* -------- parity taps and counters ----------------------------------------------------------- */
 
@@ -232,6 +248,15 @@ int32_t mummu_moe_take_profile(MummuMoe* moe, char* names, size_t cap);
 
 /* Number of kernels this handle has launched (for accounting in benchmarks). */
 int64_t mummu_moe_launch_count(const MummuMoe* moe);
+
+/* Kernel-variant switches of one handle.  They are read once from the environment when the handle
+ * is created (MUMMU_CUDA_<NAME>, as the reference reads MUMMU_PACKED_GEMV / MUMMU_GEMV_SPLIT once,
+ * nn/packed_gemv.rs:85-92, 686-694); this call changes one afterwards.  Names: NO_TC, NO_HOST_GRAPH,
+ * ROUTER_PLAIN, DECODE_NO_PDL, DECODE_NT, DECODE_STREAM_MIN, DECODE_RB_GATEUP, DECODE_RB_DOWN,
+ * CHECKED (kernels verify their indices and raise the status word: the reference arms CubeCL's
+ * check_mode = "validate" for its test suites, burn.toml:17), WAIT_POLLS (bound of the
+ * device-side waits on peers, in polls of about 0.2 us; 0 = the default of a few seconds). */
+int32_t mummu_moe_set_switch(MummuMoe* moe, const char* name, int32_t value);
 
 /* -------- Q4_K helpers (no counterpart in the reference: it only dequantises Q4_K) ----------- */
 
@@ -259,6 +284,11 @@ int32_t mummu_q4k_dequantize(const void* src, float* dst, int64_t n_superblocks,
  * selects, plus a few counters; about 1 MiB) is a fixed array inside the library's device image,
  * held by every GPU that loads the library until the process exits.  Limits, refused with
  * MUMMU_ERR_CONTRACT and a message: tokens <= 1024, tokens * experts <= 262144, experts <= 256.
+ * router_w must be 16-byte aligned (the kernel reads it in 128-bit words; a pointer into the
+ * middle of a packed buffer is refused with MUMMU_ERR_CONTRACT rather than left to fault on the
+ * device); the other pointers need the alignment of their element type.  hidden is limited by the
+ * shared memory the kernel stages one 8-expert weight slice and 4 token rows in (48 * hidden + 2 KB
+ * <= 220 KB, so hidden <= about 4600): wider inputs return MUMMU_ERR_UNSUPPORTED.
  * The first call on a device looks the array's address up (cudaGetSymbolAddress); make that first
  * call before any stream capture.  All calls on a device share the one array: two calls whose
  * kernels may overlap on the GPU (different streams, no dependency) race on it and give wrong

@@ -44,23 +44,26 @@ SYMBOLS = {
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "mummu_moe_experts_grouped": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                               C.c_void_p, C.c_void_p]),
+    "mummu_moe_experts_planned": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                              C.c_void_p, C.c_void_p]),
     "mummu_moe_combine": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "mummu_ep_alloc": (C.c_int32, [C.c_int32, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
     "mummu_ep_open": (C.c_int32, [C.c_int32, C.c_char_p, C.POINTER(C.c_void_p)]),
     "mummu_ep_close": (C.c_int32, [C.c_void_p]),
     "mummu_ep_free": (C.c_int32, [C.c_void_p]),
-    "mummu_ep_plan": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
-                                  C.c_void_p]),
     "mummu_ep_sync_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
-    "mummu_ep_exchange_plan": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
-                                           C.c_void_p, C.c_void_p, C.c_void_p]),
-    "mummu_ep_barrier": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p]),
-    "mummu_ep_dispatch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                      C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p]),
-    "mummu_ep_combine": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p,
-                                     C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
-                                     C.c_void_p]),
+    "mummu_ep_reset": (C.c_int32, [C.c_int32, C.c_void_p, C.c_int32, C.c_int32]),
+    "mummu_ep_post_counts": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
+                                         C.c_void_p]),
+    "mummu_ep_dispatch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p),
+                                      C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_int64,
+                                      C.c_void_p, C.c_void_p, C.c_void_p]),
+    "mummu_ep_experts": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p,
+                                     C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "mummu_ep_combine": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p,
+                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                     C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p]),
     "mummu_expert_run": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "mummu_moe_dequant_bank": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "mummu_moe_take_hits": (C.c_int32, [C.c_void_p, C.c_void_p]),
@@ -68,6 +71,7 @@ SYMBOLS = {
     "mummu_moe_set_profiling": (C.c_int32, [C.c_void_p, C.c_int32]),
     "mummu_moe_take_profile": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_size_t]),
     "mummu_moe_launch_count": (C.c_int64, [C.c_void_p]),
+    "mummu_moe_set_switch": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32]),
     "mummu_q4k_quantize": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "mummu_q4k_dequantize": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "mummu_moe_route_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,

@@ -143,6 +143,36 @@ int ensure_scratch(MummuMoe* m, int64_t tokens) {
     return MUMMU_OK;
 }
 
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    if (!v) return dflt;
+    return *v ? atoi(v) : 1;         // a variable set to the empty string counts as "on"
+}
+
+struct SwitchName {
+    const char* name;
+    int MummuSwitches::*field;
+};
+static const SwitchName kSwitches[] = {
+    {"NO_TC", &MummuSwitches::no_tc},
+    {"NO_HOST_GRAPH", &MummuSwitches::no_host_graph},
+    {"ROUTER_PLAIN", &MummuSwitches::router_plain},
+    {"DECODE_NO_PDL", &MummuSwitches::decode_no_pdl},
+    {"DECODE_NT", &MummuSwitches::decode_nt},
+    {"DECODE_STREAM_MIN", &MummuSwitches::decode_stream_min},
+    {"DECODE_RB_GATEUP", &MummuSwitches::decode_rb_gateup},
+    {"DECODE_RB_DOWN", &MummuSwitches::decode_rb_down},
+    {"CHECKED", &MummuSwitches::checked},
+};
+
+static void switches_from_env(MummuSwitches& sw) {
+    for (const SwitchName& e : kSwitches) {
+        const std::string var = std::string("MUMMU_CUDA_") + e.name;
+        sw.*(e.field) = env_int(var.c_str(), 0);
+    }
+    sw.wait_polls = (uint32_t)env_int("MUMMU_CUDA_WAIT_POLLS", 0);
+}
+
 struct DeviceGuard {
     int prev = -1;
     explicit DeviceGuard(int dev) {
@@ -189,6 +219,11 @@ static int read_status(MummuMoe* m, cudaStream_t s) {
         set_error("a bounded device-side wait ran out");
         return MUMMU_ERR_TIMEOUT;
     }
+    if (st & STATUS_BOUNDS) {
+        set_error("an index left its buffer on the device (a receive buffer smaller than the rows routed to it, "
+                  "or a checked kernel caught a bad index); the access was skipped");
+        return MUMMU_ERR_CONTRACT;
+    }
     set_error("router logit is not finite (NaN or infinity in the activations or router weight)");
     return MUMMU_ERR_NUMERIC;
 }
@@ -210,8 +245,7 @@ static int forward_device(MummuMoe* m, const void* x, void* y, int64_t tokens, i
         return launch_combine(m, m->ys, MUMMU_F32, m->ids, m->wts, m->pos, tokens, top_k, y, s);
     }
     if ((rc = launch_router(m, x, tokens, top_k, norm, m->ids, m->wts, m->counts, s))) return rc;
-    if (prefill_tc_supported(c, tokens * top_k) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
-               !getenv("MUMMU_CUDA_NO_TC")) {
+    if (prefill_tc_supported(c, tokens * top_k) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && !m->sw.no_tc) {
         // tensor-core path: sorted copy of the routed rows, two grouped GEMMs, 16-bit expert outputs
         if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
         if ((rc = launch_gather_rows(m, x, m->row_token, m->xs, tokens * top_k, s))) return rc;
@@ -268,6 +302,7 @@ int32_t mummu_moe_create(const MummuMoeConfig* cfg, MummuMoe** out) {
     DeviceGuard guard(cfg->device);
     MummuMoe* m = new MummuMoe();
     m->cfg = *cfg;
+    switches_from_env(m->sw);
     int rc = MUMMU_OK;
     do {
         cudaError_t err = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
@@ -339,6 +374,9 @@ int32_t mummu_moe_set_router(MummuMoe* m, const void* w, int32_t dtype, int32_t 
             else v = __bfloat162float(((const __nv_bfloat16*)w)[src]);
             host[(size_t)i * E + e] = v;
         }
+    // work queued on the handle's stream may still read the old weights; the copies below run on
+    // the legacy default stream, which the handle's non-blocking stream is not ordered with
+    MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
     MUMMU_CUDA_TRY(cudaMemcpy(m->router_w, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice));
     if (H % 32 == 0 && E % 8 == 0) {
         // image of the decode router's shared-memory slice, so that a block fetches its 8 experts
@@ -361,7 +399,6 @@ int32_t mummu_moe_set_router(MummuMoe* m, const void* w, int32_t dtype, int32_t 
         }
         MUMMU_CUDA_TRY(cudaMemcpy(m->router_bias, bias, sizeof(float) * E, cudaMemcpyHostToDevice));
     } else if (m->router_bias) {
-        MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
         cudaFree(m->router_bias);
         m->router_bias = nullptr;
     }
@@ -378,8 +415,17 @@ int32_t mummu_moe_set_bank(MummuMoe* m, int32_t which, const void* data, size_t 
     std::lock_guard<std::mutex> lock(m->mu);
     clear_host_graphs(m);
     DeviceGuard guard(m->cfg.device);
-    MUMMU_CUDA_TRY(cudaMemcpy(m->bank[which], data, bytes,
-                              on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+    // Earlier calls on the handle's own stream may still read the bank; the handle's stream is
+    // non-blocking, so the legacy-stream copy below is not ordered with it by itself.  Work the
+    // caller queued on its own streams is the caller's to finish first (said in the header).
+    MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    if (on_device) {
+        // a device-to-device cudaMemcpy may return before the copy has run
+        MUMMU_CUDA_TRY(cudaMemcpyAsync(m->bank[which], data, bytes, cudaMemcpyDeviceToDevice, m->stream));
+        MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    } else {
+        MUMMU_CUDA_TRY(cudaMemcpy(m->bank[which], data, bytes, cudaMemcpyHostToDevice));
+    }
     m->bank_set[which] = true;
     return MUMMU_OK;
 }
@@ -388,8 +434,7 @@ int32_t mummu_moe_set_bank(MummuMoe* m, int32_t which, const void* data, size_t 
 // call with the same (tokens, top_k, norm) on, the layer's launches are replayed from a CUDA graph
 // captured on the second (the first runs eagerly so that one-time attribute calls are done).
 static int forward_host_staged(MummuMoe* m, int64_t tokens, int top_k, int norm, cudaStream_t s) {
-    static const bool enabled = !getenv("MUMMU_CUDA_NO_HOST_GRAPH");
-    if (!enabled || m->prof.enabled || !decode_q4k_supported(m->cfg, tokens))
+    if (m->sw.no_host_graph || m->prof.enabled || !decode_q4k_supported(m->cfg, tokens))
         return forward_device(m, m->io_x, m->io_y, tokens, top_k, norm, s);
     const uint64_t key = ((uint64_t)tokens << 20) | ((uint64_t)top_k << 1) | (uint64_t)(norm != 0);
     auto it = m->host_graphs.find(key);
@@ -507,21 +552,21 @@ int32_t mummu_moe_permute(MummuMoe* m, const int32_t* ids, int32_t tokens, int32
     return launch_permute(m, ids, tokens, top_k, cnt, offsets, row_token, pos, s);
 }
 
-int32_t mummu_moe_experts_grouped(MummuMoe* m, const void* xs, const int32_t* counts, int32_t rows,
-                                  void* ys, void* stream) {
-    MUMMU_REQUIRE(m && counts, "mummu_moe_experts_grouped: null argument");
-    MUMMU_REQUIRE(rows >= 0, "mummu_moe_experts_grouped: negative row count %d", rows);
+static int32_t experts_rows(MummuMoe* m, const void* xs, const int32_t* counts, int32_t rows, void* ys,
+                            void* stream, bool planned, const char* who) {
+    MUMMU_REQUIRE(m && counts, "%s: null argument", who);
+    MUMMU_REQUIRE(rows >= 0, "%s: negative row count %d", who, rows);
     int rc;
     if ((rc = check_ready(m, false, true))) return rc;
     if (rows == 0) return MUMMU_OK;
-    MUMMU_REQUIRE(xs && ys, "mummu_moe_experts_grouped: null activation pointer");
+    MUMMU_REQUIRE(xs && ys, "%s: null activation pointer", who);
     std::lock_guard<std::mutex> lock(m->mu);
     DeviceGuard guard(m->cfg.device);
     int64_t tokens_equiv = ((int64_t)rows + m->cfg.top_k - 1) / m->cfg.top_k;
     if ((rc = ensure_scratch(m, tokens_equiv))) return rc;
     cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
-    if ((rc = launch_offsets_from_counts(m, counts, m->cfg.experts_local, m->offsets, s))) return rc;
-    if (prefill_tc_supported(m->cfg, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !getenv("MUMMU_CUDA_NO_TC"))
+    if (!planned && (rc = launch_offsets_from_counts(m, counts, m->cfg.experts_local, m->offsets, s))) return rc;
+    if (prefill_tc_supported(m->cfg, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !m->sw.no_tc)
         return launch_experts_tc(m, xs, rows, counts, m->offsets, ys, m->cfg.act_dtype, s);
     if (m->cfg.weight_dtype == MUMMU_Q4_K && m->cfg.act_dtype == MUMMU_F16 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 &&
         rows <= 8192 && m->cfg.hidden <= 8192 && m->cfg.inter <= 8192) {
@@ -531,6 +576,16 @@ int32_t mummu_moe_experts_grouped(MummuMoe* m, const void* xs, const int32_t* co
     }
     return launch_experts_simt(m, xs, m->cfg.act_dtype, nullptr, counts, m->offsets, rows, rows, ys,
                                m->cfg.act_dtype, -1, s);
+}
+
+int32_t mummu_moe_experts_grouped(MummuMoe* m, const void* xs, const int32_t* counts, int32_t rows,
+                                  void* ys, void* stream) {
+    return experts_rows(m, xs, counts, rows, ys, stream, false, "mummu_moe_experts_grouped");
+}
+
+int32_t mummu_moe_experts_planned(MummuMoe* m, const void* xs, const int32_t* counts, int32_t rows,
+                                  void* ys, void* stream) {
+    return experts_rows(m, xs, counts, rows, ys, stream, true, "mummu_moe_experts_planned");
 }
 
 int32_t mummu_moe_combine(MummuMoe* m, const void* ys, const int32_t* ids, const float* w,
@@ -686,6 +741,24 @@ int32_t mummu_moe_take_profile(MummuMoe* m, char* names, size_t cap) {
 }
 
 int64_t mummu_moe_launch_count(const MummuMoe* m) { return m ? m->launches : 0; }
+
+int32_t mummu_moe_set_switch(MummuMoe* m, const char* name, int32_t value) {
+    MUMMU_REQUIRE(m && name, "mummu_moe_set_switch: null argument");
+    std::lock_guard<std::mutex> lock(m->mu);
+    if (!strcmp(name, "WAIT_POLLS")) {
+        MUMMU_REQUIRE(value >= 0, "mummu_moe_set_switch: WAIT_POLLS %d", value);
+        m->sw.wait_polls = (uint32_t)value;
+        return MUMMU_OK;
+    }
+    for (const SwitchName& e : kSwitches)
+        if (!strcmp(name, e.name)) {
+            m->sw.*(e.field) = value;
+            clear_host_graphs(m);      // captured replays hold the old variant
+            return MUMMU_OK;
+        }
+    set_error("mummu_moe_set_switch: no switch named %s", name);
+    return MUMMU_ERR_CONTRACT;
+}
 
 int32_t mummu_q4k_quantize(const float* src, void* dst, int64_t n_superblocks, int32_t device, void* stream) {
     MUMMU_REQUIRE(src && dst && n_superblocks >= 0, "mummu_q4k_quantize: bad argument");

@@ -42,6 +42,7 @@ void set_error(const char* fmt, ...);
 // device status word bits (sticky until mummu_moe_sync reads them)
 constexpr int STATUS_NONFINITE = 1;
 constexpr int STATUS_TIMEOUT = 2;
+constexpr int STATUS_BOUNDS = 4;
 
 // ---------------------------------------------------------------------------------------------
 // dtype helpers
@@ -166,8 +167,25 @@ struct Profiler {
 
 }  // namespace mummu
 
+// Kernel-variant switches of one handle.  Read once from the environment when the handle is
+// created (MUMMU_CUDA_* variables, the way the reference reads its MUMMU_* switches once into
+// OnceLocks, nn/packed_gemv.rs:85-92, 686-694); mummu_moe_set_switch changes one afterwards.
+struct MummuSwitches {
+    int no_tc = 0;            // MUMMU_CUDA_NO_TC: never take the tcgen05 grouped GEMM
+    int no_host_graph = 0;    // MUMMU_CUDA_NO_HOST_GRAPH: host-pointer decode calls stay eager
+    int router_plain = 0;     // MUMMU_CUDA_ROUTER_PLAIN: decode router without the bulk-copied slice image
+    int decode_no_pdl = 0;    // MUMMU_CUDA_DECODE_NO_PDL: no programmatic dependent launch of the down kernel
+    int decode_nt = 0;        // MUMMU_CUDA_DECODE_NT: 1 forces one 8-token tile per pass
+    int decode_stream_min = 0;// MUMMU_CUDA_DECODE_STREAM_MIN: row tiles from which the streaming variant runs
+    int decode_rb_gateup = 0; // MUMMU_CUDA_DECODE_RB_GATEUP / _DOWN: row tiles per CTA (0 = planned)
+    int decode_rb_down = 0;
+    int checked = 0;          // MUMMU_CUDA_CHECKED: kernels verify their indices and raise the status word
+    uint32_t wait_polls = 0;  // bound of the device-side peer waits in polls (0 = the default, seconds)
+};
+
 struct MummuMoe {
     MummuMoeConfig cfg{};
+    MummuSwitches sw{};
     std::mutex mu;
     cudaStream_t stream = nullptr;
 
@@ -205,8 +223,6 @@ struct MummuMoe {
     // cached tensor maps (CUtensorMap, 128 B each) of the Q4_K banks as [rows, row_bytes] byte views
     alignas(64) unsigned char q4k_map[3][128];
     const void* q4k_map_base[3] = {nullptr, nullptr, nullptr};
-    alignas(64) unsigned char q4k_map128[3][128];   // same views with a 128-row box
-    const void* q4k_map128_base[3] = {nullptr, nullptr, nullptr};
     int64_t launches = 0;
     mummu::Profiler prof;
     // host-pointer decode calls: the layer's launches captured once per (tokens, top_k, norm) and
@@ -277,10 +293,6 @@ int launch_experts_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32
 
 // ---- decode_q4k.cu ----
 bool decode_q4k_supported(const MummuMoeConfig& c, int64_t tokens);
-// ---- decode_umma.cu ----
-bool decode_umma_supported(const MummuMoeConfig& c);
-int launch_decode_umma(MummuMoe* m, bool gateup, const void* x, const int32_t* row_token, const int32_t* counts,
-                       const int32_t* offsets, int n_experts_max, void* out, cudaStream_t s);
 int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cudaStream_t s);
 int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token, const int32_t* counts,
                            const int32_t* offsets, int64_t rows_total, float* ys, cudaStream_t s);

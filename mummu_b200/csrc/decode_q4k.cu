@@ -23,8 +23,6 @@
 // Work split: one CTA = (active expert, a run of 16-row tiles); its 8 warps split K by
 // super-block (and, when K has fewer than 8 super-blocks, take several row tiles at once); the
 // token tile sits in shared memory already in MMA fragment order.
-#include <cstdlib>
-
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -182,12 +180,6 @@ __device__ __forceinline__ void load_unit(UnitRegs& r, const uint8_t* row0, cons
     r.qa[1] = __ldcs(reinterpret_cast<const uint4*>(row1 + 16 + 32 * t));
     r.qb[1] = __ldcs(reinterpret_cast<const uint4*>(row1 + 32 + 32 * t));
 }
-
-__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
@@ -368,150 +360,6 @@ __global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_kernel(DecodeArgs a)
     }
 }
 
-
-// Row-tile loop of the streaming variant for NTC token tiles in use (a compile-time count, so
-// the inner loop carries no per-tile branches).
-template <int NT, int NTC, bool GATEUP>
-__device__ __forceinline__ void stream_rows(const DecodeArgs& a, uint32_t frag_base, uint32_t sxh_base,
-                                            const uint8_t* w0e, const uint8_t* w1e, int rt_first, int rt_end,
-                                            int nsb, int g, int t, bool upper, uint32_t sel, int first_row,
-                                            int npass, uint32_t slot) {
-    const size_t half_tile = (size_t)8 * a.row_bytes;
-    for (int rt = rt_first; rt < rt_end; rt += DQ_WARPS) {
-        // row g of matrix 0 / matrix 1 at super-block 0
-        const uint8_t* r0p = w0e + (size_t)(GATEUP ? rt * 16 + g : rt * 32 + g) * a.row_bytes;
-        const uint8_t* r1p = w1e + (size_t)(GATEUP ? rt * 16 + g : rt * 32 + 16 + g) * a.row_bytes;
-        float y[2][NTC][4];
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-            for (int nt = 0; nt < NTC; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) y[mt][nt][i] = 0.0f;
-        // The next unit's 96 bytes per lane travel global -> shared with cp.async (no registers
-        // held while in flight); each lane owns six private 16-byte slots, so no cross-lane hazard.
-        auto prefetch = [&](const uint8_t* row0) {
-            const uint8_t* row1 = row0 + half_tile;
-            cp_async16(slot + 0 * 512, row0);
-            cp_async16(slot + 1 * 512, row0 + 16 + 32 * t);
-            cp_async16(slot + 2 * 512, row0 + 32 + 32 * t);
-            cp_async16(slot + 3 * 512, row1);
-            cp_async16(slot + 4 * 512, row1 + 16 + 32 * t);
-            cp_async16(slot + 5 * 512, row1 + 32 + 32 * t);
-            cp_async_commit();
-        };
-        auto take = [&](UnitRegs& u) {
-            cp_async_wait_all();
-            u.hdr[0] = lds128(slot + 0 * 512);
-            u.qa[0] = lds128(slot + 1 * 512);
-            u.qb[0] = lds128(slot + 2 * 512);
-            u.hdr[1] = lds128(slot + 3 * 512);
-            u.qa[1] = lds128(slot + 4 * 512);
-            u.qb[1] = lds128(slot + 5 * 512);
-        };
-        uint32_t frag_addr = frag_base + (uint32_t)((g * 4 + t) * 16);
-        uint32_t sxh_addr = sxh_base + (uint32_t)((g * 8 + 2 * t) * 2);
-        if (NTC >= 2) {
-            // two token tiles leave no registers for a second unit: prefetch through shared memory
-            UnitRegs un;
-            prefetch(r0p);
-            for (int sb = 0; sb < nsb; ++sb) {
-                take(un);
-                prefetch(r1p);                                    // matrix 1 of this super-block
-                unit_terms<NT, NTC>(un, upper, sel, frag_addr, sxh_addr, y[0]);
-                r0p += Q4K_BLOCK_BYTES;
-                take(un);
-                if (sb + 1 < nsb) prefetch(r0p);                  // matrix 0 of the next super-block
-                unit_terms<NT, NTC>(un, upper, sel, frag_addr, sxh_addr, y[1]);
-                r1p += Q4K_BLOCK_BYTES;
-                frag_addr += (uint32_t)(NT * 64 * 4 * 16);
-                sxh_addr += (uint32_t)(NT * 8 * 8 * 2);
-            }
-        } else {
-            // one token tile: the next unit waits in a second set of registers
-            UnitRegs ua, ub;
-            load_unit(ua, r0p, r0p + half_tile, t);
-            for (int sb = 0; sb < nsb; ++sb) {
-                load_unit(ub, r1p, r1p + half_tile, t);
-                r1p += Q4K_BLOCK_BYTES;
-                r0p += Q4K_BLOCK_BYTES;
-                unit_terms<NT, NTC>(ua, upper, sel, frag_addr, sxh_addr, y[0]);
-                if (sb + 1 < nsb) load_unit(ua, r0p, r0p + half_tile, t);
-                unit_terms<NT, NTC>(ub, upper, sel, frag_addr, sxh_addr, y[1]);
-                frag_addr += (uint32_t)(NT * 64 * 4 * 16);
-                sxh_addr += (uint32_t)(NT * 8 * 8 * 2);
-            }
-        }
-        // epilogue from registers: lane (g, t) holds rows g, g+8 x tokens 2t, 2t+1
-#pragma unroll
-        for (int nt = 0; nt < NTC; ++nt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int slot = nt * 8 + 2 * t + (i & 1);
-                const int row = g + ((i >> 1) << 3);
-                if (slot < npass) {
-                    const size_t orow = (size_t)(first_row + slot);
-                    if (GATEUP) {
-                        const float s0 = y[0][nt][i], s1 = y[1][nt][i];
-                        const float v = (s0 / (1.0f + expf(-s0))) * s1;
-                        reinterpret_cast<__half*>(a.out)[orow * a.ld_out + rt * 16 + row] = __float2half_rn(v);
-                    } else {
-                        float* o32 = reinterpret_cast<float*>(a.out);
-                        o32[orow * a.ld_out + rt * 32 + row] = y[0][nt][i];
-                        o32[orow * a.ld_out + rt * 32 + 16 + row] = y[1][nt][i];
-                    }
-                }
-            }
-    }
-}
-
-
-// Streaming variant for large work: one warp owns a 16-row tile over ALL of K, so nothing is
-// folded across warps and the epilogue runs from registers.  The (super-block, matrix) units are
-// software pipelined through two register buffers: the loads of unit u+1 are in flight while
-// unit u is decoded and multiplied.
-template <int NT, bool GATEUP>
-__global__ void __launch_bounds__(DQ_THREADS, 2) decode_q4k_stream_kernel(DecodeArgs a) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int nsb = a.K >> 8;
-    uint4* s_frag = reinterpret_cast<uint4*>(smem_raw);
-    __half* s_sxh = reinterpret_cast<__half*>(s_frag + (size_t)nsb * NT * 256);
-    const uint32_t frag_base = (uint32_t)__cvta_generic_to_shared(s_frag);
-    const uint32_t sxh_base = (uint32_t)__cvta_generic_to_shared(s_sxh);
-
-    const int ai = blockIdx.x / a.ctas_per_expert;
-    const int cb = blockIdx.x - ai * a.ctas_per_expert;
-    if (ai >= *a.n_active) return;
-    const int e = a.active[ai];
-    const int cnt = a.counts[e];
-    const int base = a.offsets[e];
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const bool upper = t >= 2;
-    const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
-    // per-lane prefetch slots: [warp][6 chunks][32 lanes] x 16 B, after the token tile
-    const uint32_t slot = sxh_base + (uint32_t)(nsb * NT * 128) + (uint32_t)(warp * 6 * 512 + lane * 16);
-    const int rt_begin = cb * a.rb;
-    const int rt_end = min(a.n_rt, rt_begin + a.rb);
-    const uint8_t* w0e = a.w0 + (size_t)e * a.expert_stride;
-    const uint8_t* w1e = GATEUP ? a.w1 + (size_t)e * a.expert_stride : w0e;
-
-    for (int pass0 = 0; pass0 < cnt; pass0 += 8 * NT) {
-        const int npass = min(8 * NT, cnt - pass0);
-        const int nt_count = (npass + 7) >> 3;
-        __syncthreads();
-        stage_token_tile<NT>(a, s_frag, s_sxh, base + pass0, npass, nt_count, tid);
-        __syncthreads();
-
-        if (NT == 1 || nt_count == 1)
-            stream_rows<NT, 1, GATEUP>(a, frag_base, sxh_base, w0e, w1e, rt_begin + warp, rt_end, nsb, g, t, upper,
-                                       sel, base + pass0, npass, slot);
-        else
-            stream_rows<NT, NT, GATEUP>(a, frag_base, sxh_base, w0e, w1e, rt_begin + warp, rt_end, nsb, g, t, upper,
-                                        sel, base + pass0, npass, slot);
-    }
-}
 
 // ------------------------------------------------------------------------------------------------
 // Streaming variant with the weights staged by the copy engine.
@@ -746,17 +594,11 @@ static int bank_map(MummuMoe* m, int which, int row_bytes, int64_t rows, const C
     return MUMMU_OK;
 }
 
-static bool use_tma_ring() {
-    static int v = -1;
-    if (v < 0) v = getenv("MUMMU_CUDA_DECODE_NO_TMA") ? 0 : 1;
-    return v == 1;
-}
-
 template <int NT, bool GATEUP>
 static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream, cudaStream_t s,
                       const char* name, bool pdl = false, bool* used_tma = nullptr) {
     const int nsb = a.K >> 8;
-    if (stream && use_tma_ring()) {
+    if (stream) {
         // deepest ring (2..4 stages per warp) that still lets two CTAs share an SM
         int depth = 4;
         while (depth > 2 && 2 * (dq_ring_smem_bytes<NT>(nsb, depth) + 1024) > 227 * 1024) --depth;
@@ -792,20 +634,15 @@ static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream
             return MUMMU_OK;
         }
     }
-    size_t smem = dq_smem_bytes<NT>(nsb);
-    if (stream) smem = (size_t)nsb * NT * 4096 + (size_t)nsb * NT * 128 + (size_t)DQ_WARPS * 6 * 512;
+    // (a token tile too wide to share the SM with a weight ring: the split-K kernel takes the call)
+    const size_t smem = dq_smem_bytes<NT>(nsb);
     if (smem > 200 * 1024) {
         set_error("decode_q4k: %zu bytes of shared memory needed for K=%d", smem, a.K);
         return MUMMU_ERR_UNSUPPORTED;
     }
     LaunchScope scope(m, s, name);
-    if (stream) {
-        MUMMU_CUDA_TRY(allow_big_smem(decode_q4k_stream_kernel<NT, GATEUP>, m->cfg.device));
-        decode_q4k_stream_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a);
-    } else {
-        MUMMU_CUDA_TRY(allow_big_smem(decode_q4k_kernel<NT, GATEUP>, m->cfg.device));
-        decode_q4k_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a);
-    }
+    MUMMU_CUDA_TRY(allow_big_smem(decode_q4k_kernel<NT, GATEUP>, m->cfg.device));
+    decode_q4k_kernel<NT, GATEUP><<<n_experts_max * a.ctas_per_expert, DQ_THREADS, smem, s>>>(a);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }
@@ -814,15 +651,13 @@ static int launch_one(MummuMoe* m, DecodeArgs& a, int n_experts_max, bool stream
 // tiles for a fair share of the 148 SMs x 16 resident warps (measured at the OLMoE shape: 36.9 us
 // against 35.3 us for split-K with 8 experts, 39 against 51 with 15, 48 against 72 with 27);
 // below that the split-K variant spreads each row tile over up to 8 warps.
-static void plan(DecodeArgs& a, int experts_est, int64_t rows_total, int nt, bool& stream) {
+static void plan(const MummuSwitches& sw, DecodeArgs& a, int experts_est, int64_t rows_total, int nt, bool& stream) {
     const int nsb = a.K >> 8;
     // expected passes per expert from the row bound the caller gave (1 in plain decode calls)
     int64_t per_expert = (rows_total + experts_est - 1) / experts_est;
     a.pass_split = (int)std::min<int64_t>(4, std::max<int64_t>(1, (per_expert + 8 * nt - 1) / (8 * nt)));
-    static const int stream_min = [] {
-        const char* env = getenv("MUMMU_CUDA_DECODE_STREAM_MIN");
-        return env ? atoi(env) : 148 * 5;   // measured: streaming wins from about 15 experts' row tiles on
-    }();
+    // measured: streaming wins from about 15 experts' row tiles on
+    const int stream_min = sw.decode_stream_min > 0 ? sw.decode_stream_min : 148 * 5;
     stream = (int64_t)experts_est * a.n_rt * a.pass_split >= stream_min;
     if (stream) {
         a.rb = DQ_WARPS;                       // one row tile per warp
@@ -834,10 +669,8 @@ static void plan(DecodeArgs& a, int experts_est, int64_t rows_total, int nt, boo
         a.rb = rg;
         while (a.rb * 2 <= a.n_rt && (int64_t)experts_est * (a.n_rt / (a.rb * 2)) >= 148 * 3) a.rb *= 2;
     }
-    if (const char* env = getenv(a.w1 ? "MUMMU_CUDA_DECODE_RB_GATEUP" : "MUMMU_CUDA_DECODE_RB_DOWN")) {
-        const int v = atoi(env);
-        if (v >= 1 && v <= a.n_rt) a.rb = v;
-    }
+    const int forced_rb = a.w1 ? sw.decode_rb_gateup : sw.decode_rb_down;
+    if (forced_rb >= 1 && forced_rb <= a.n_rt) a.rb = forced_rb;
     a.ctas_per_expert = (a.n_rt + a.rb - 1) / a.rb;
 }
 
@@ -851,7 +684,7 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     int32_t* n_active = m->n_active;
     int experts_est = (int)std::min<int64_t>(c.experts_local, rows_total);
     bool nt2 = rows_total > 8;
-    if (const char* env = getenv("MUMMU_CUDA_DECODE_NT")) nt2 = nt2 && atoi(env) >= 2;
+    if (m->sw.decode_nt == 1) nt2 = false;
 
     DecodeArgs g{};
     g.x = (const __half*)x;
@@ -867,13 +700,7 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     g.K = c.hidden;
     g.n_rt = c.inter / 16;
     bool g_stream;
-    plan(g, experts_est, rows_total, nt2 ? 2 : 1, g_stream);
-    if (g_stream && decode_umma_supported(c)) {
-        // enough routed experts to fill the GPU with 128-row tiles: tensor-core variant
-        int rc = launch_decode_umma(m, true, x, row_token, counts, offsets, experts_est, m->hact, s);
-        if (rc) return rc;
-        return launch_decode_umma(m, false, m->hact, nullptr, counts, offsets, experts_est, ys, s);
-    }
+    plan(m->sw, g, experts_est, rows_total, nt2 ? 2 : 1, g_stream);
     g.ld_out = c.inter;
     g.out = m->hact;
     g.rows_per_expert = c.inter;
@@ -881,7 +708,7 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     // Programmatic dependent launch of the down kernel behind gate/up (measured: 2 % of the layer
     // at T=64, 6-8 % at T=8..32; MUMMU_CUDA_DECODE_NO_PDL=1 turns it off); profiling brackets
     // every launch with events, which would serialise the pair anyway.
-    const bool want_pdl = !getenv("MUMMU_CUDA_DECODE_NO_PDL") && !m->prof.enabled;
+    const bool want_pdl = !m->sw.decode_no_pdl && !m->prof.enabled;
     g.pdl = want_pdl ? 1 : 0;
     bool g_tma = false;
     int rc = nt2 ? launch_one<2, true>(m, g, experts_est, g_stream, s, "q4k_gate_up", false, &g_tma)
@@ -904,7 +731,7 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     d.K = c.inter;
     d.n_rt = c.hidden / 32;
     bool d_stream;
-    plan(d, experts_est, rows_total, nt2 ? 2 : 1, d_stream);
+    plan(m->sw, d, experts_est, rows_total, nt2 ? 2 : 1, d_stream);
     d.pdl = pdl ? 1 : 0;
     d.ld_out = c.hidden;
     d.out = ys;

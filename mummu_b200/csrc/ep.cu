@@ -1,15 +1,29 @@
 // Expert-parallel exchange over peer memory (NVLink / NVSwitch): no host synchronisation, no
-// staging copies.  The reference has no collective for this path (its devices exchange through
-// host memory: crates/mummu/src/backend.rs:128-143, nn/moe.rs:1219-1272).
+// staging copies, no library collective inside a step.  The reference has no collective for this
+// path (its devices exchange through host memory: crates/mummu/src/backend.rs:128-143,
+// nn/moe.rs:1219-1272).
 //
-// Every rank owns a contiguous block of experts and two peer-visible buffers:
+// Every rank owns a contiguous block of experts and three peer-visible buffers:
 //   recv_x [cap_rows, hidden]  rows routed to its experts, expert-major (sources in rank order)
 //   ys     [cap_rows, hidden]  its experts' outputs for those rows
-// From the all-gathered per-expert row counts every rank computes, on the device, where each of
-// its sorted rows lives in the owner's buffers (ep_plan).  Dispatch is a gather from the layer
-// input straight into the owners' recv_x with 16-byte peer stores (ep_dispatch); combine reads
-// the expert outputs with peer loads, in ascending expert id with the reference's two roundings
-// (ep_combine).  Plain peer loads and stores only.
+//   sync   flags, epochs and the gathered per-expert row counts (layout below)
+//
+// One layer on one rank is four stages, each signalling the next ONE WAY: the producer's last
+// block stores its epoch into a flag in every peer's sync block (system-scope release), and the
+// consumer polls its own flags (system-scope acquire) in the head of a later kernel.  No kernel
+// both signals and waits, so the stages of several ranks may also be issued one after another on
+// a single stream (rank 0's stage, rank 1's stage, ..., then the next stage): nothing then waits
+// for a kernel that has not run.  That is how the exchange is tested on one GPU.
+//
+//   post     : counts of this rank's rows per global expert -> counts_in[rank] of every rank; S1
+//   dispatch : wait S1; plan from the gathered counts (where each sorted row lives in its owner's
+//              buffers; rows, offsets and work order of the local experts); rows -> owners' recv_x
+//              with 16-byte peer stores; S2
+//   experts  : wait S2; the local experts over recv_x -> ys; S3
+//   combine  : wait S3; per token, ascending expert id, scaled = w * y; out += scaled, y read from
+//              the owner's ys with peer loads
+// Plain peer loads and stores only.  Every wait is bounded: when it runs out the kernel raises
+// the status word, skips its data movement and returns.
 #include <cstring>
 
 #include "common.cuh"
@@ -22,40 +36,17 @@ struct PeerTable {
     void* ptr[EP_MAX_RANKS];
 };
 
-// all_counts [world, E]: rows rank s routes to global expert e.
-// dst_base[e]   : first row, in the owner's buffers, of THIS rank's rows for expert e
-// local_counts[le], local_offsets[le] : rows / first row of local expert le, all sources together
-__global__ void ep_plan_kernel(const int32_t* all_counts, int world, int rank, int E, int EL,
-                               int32_t* dst_base, int32_t* local_counts) {
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        const int d = e / EL, le = e - d * EL;
-        int base = 0;
-        for (int l2 = 0; l2 < le; ++l2)                       // local experts of rank d before le: all sources
-            for (int s = 0; s < world; ++s) base += all_counts[s * E + d * EL + l2];
-        for (int s = 0; s < rank; ++s) base += all_counts[s * E + e];   // lower ranks' rows of this expert
-        dst_base[e] = base;
-    }
-    for (int le = threadIdx.x; le < EL; le += blockDim.x) {
-        int c = 0;
-        for (int s = 0; s < world; ++s) c += all_counts[s * E + rank * EL + le];
-        local_counts[le] = c;
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// Device-side signalling between the ranks (one rank per GPU), so that a whole expert-parallel
-// step holds no library collective and no host round trip and can be replayed from a CUDA graph.
-// Every rank owns a peer-visible block of 32-bit words, zeroed by its owner before the peers map it:
-//   [0]                  epoch of the owner's last signal (touched by the owner only)
-//   [16 .. 16+R)         flag[s]: last epoch rank s has signalled to this rank
-//   [64 .. 64+R*E)       counts_in[s][e]: rank s's per-expert row counts for the current layer
-// A signal is a system-scope release store of the sender's epoch into flag[sender] of every rank;
-// a wait polls the own flags with system-scope acquire loads until all have reached the epoch.
-// Epochs only grow, so a rank that is already one signal ahead is harmless.  Polls are bounded
-// (a second or two): when they run out the kernel raises the status word and returns.
-// ---------------------------------------------------------------------------------------------
-constexpr int EP_SYNC_FLAGS = 16, EP_SYNC_COUNTS = 64;
-constexpr uint32_t EP_WAIT_LIMIT = 1u << 23;
+// sync block, 32-bit words (zeroed by its owner before the peers map it):
+//   [0..3)    epoch of the owner's last signal per channel        (owner only)
+//   [4..7)    epoch the owner last waited for per channel         (owner only)
+//   [8..12)   arrival counters of multi-block kernels             (owner only)
+//   [16 + 16*ch + s]  flag: last epoch rank s signalled to this rank on channel ch
+//   [64 + s*E + e]    counts_in: rank s's rows for global expert e, this layer
+// Epochs only grow; every rank issues the same sequence of stages, so "the next epoch" is the
+// same number everywhere.
+constexpr int EP_W_SIG = 0, EP_W_WAIT = 4, EP_W_DONE = 8, EP_W_FLAGS = 16, EP_W_COUNTS = 64;
+constexpr int EP_CH_COUNTS = 0, EP_CH_ROWS = 1, EP_CH_OUT = 2;
+constexpr uint32_t EP_WAIT_POLLS_DEFAULT = 1u << 24;   // x (0.2 us sleep + a load): a few seconds
 
 __device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
     asm volatile("st.release.sys.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
@@ -66,143 +57,234 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
     return v;
 }
 
-// one warp: lane s talks to rank s
-__device__ void ep_signal_and_wait(const PeerTable& sync, int rank, int world, int32_t* status) {
+// One warp of one block per kernel: everything this grid wrote before is visible to a rank that
+// sees the new epoch.
+__device__ void ep_signal(const PeerTable& sync, int rank, int world, int ch) {
     const int lane = threadIdx.x & 31;
     int32_t* own = reinterpret_cast<int32_t*>(sync.ptr[rank]);
     int32_t epoch = 0;
     if (lane == 0) {
-        epoch = own[0] + 1;
-        own[0] = epoch;
+        epoch = own[EP_W_SIG + ch] + 1;
+        own[EP_W_SIG + ch] = epoch;
     }
     epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);
     __threadfence_system();
-    if (lane < world) {
-        st_release_sys(reinterpret_cast<int32_t*>(sync.ptr[lane]) + EP_SYNC_FLAGS + rank, epoch);
-        const int32_t* flag = own + EP_SYNC_FLAGS + lane;
+    if (lane < world) st_release_sys(reinterpret_cast<int32_t*>(sync.ptr[lane]) + EP_W_FLAGS + 16 * ch + rank, epoch);
+}
+
+// Threads 0..world-1 of a block poll this rank's own flags of channel ch until every rank has
+// signalled the next epoch.  Returns false (and raises the status word) when the polls run out.
+// Uniform over the block: ends with a block barrier.
+__device__ bool ep_wait(const PeerTable& sync, int rank, int world, int ch, uint32_t limit, int32_t* status) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if ((int)threadIdx.x < world) {
+        const int32_t* own = reinterpret_cast<const int32_t*>(sync.ptr[rank]);
+        const int32_t target = *reinterpret_cast<const volatile int32_t*>(own + EP_W_WAIT + ch) + 1;
+        const int32_t* flag = own + EP_W_FLAGS + 16 * ch + threadIdx.x;
         uint32_t polls = 0;
-        while (ld_acquire_sys(flag) - epoch < 0) {
+        while (ld_acquire_sys(flag) - target < 0) {
             if (++polls > 64) __nanosleep(200);
-            if (polls > EP_WAIT_LIMIT) {
+            if (polls > limit) {
                 atomicOr(status, STATUS_TIMEOUT);
+                s_ok = 0;
                 break;
             }
         }
     }
-    __syncwarp();
+    __syncthreads();
     __threadfence_system();
+    return s_ok != 0;
 }
 
-__global__ void __launch_bounds__(32) ep_barrier_kernel(PeerTable sync, int rank, int world, int32_t* status) {
-    ep_signal_and_wait(sync, rank, world, status);
+// Arrival of one block of a multi-block kernel (call with the whole block, after the block's last
+// global access).  Returns true in the block that arrived last, with the counter reset.
+__device__ bool ep_last_block(int32_t* counter) {
+    __shared__ int s_last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int done = atomicAdd(counter, 1);
+        s_last = (done == (int)(gridDim.x * gridDim.y) - 1);
+        if (s_last) *counter = 0;
+    }
+    __syncthreads();
+    if (s_last) __threadfence_system();
+    return s_last != 0;
 }
 
-// counts all-gather + plan in one launch: every rank stores its counts into counts_in[rank] of
-// every rank, signals, waits for the others' counts, then computes what ep_plan_kernel computes.
-__global__ void __launch_bounds__(256) ep_exchange_plan_kernel(const int32_t* counts, PeerTable sync, int world,
-                                                               int rank, int E, int EL, int32_t* dst_base,
-                                                               int32_t* local_counts, int32_t* status) {
+// ---- post -----------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) ep_post_counts_kernel(const int32_t* counts, PeerTable sync, int world, int rank,
+                                                             int E) {
     for (int idx = threadIdx.x; idx < world * E; idx += blockDim.x) {
         const int s = idx / E, e = idx - s * E;
-        reinterpret_cast<int32_t*>(sync.ptr[s])[EP_SYNC_COUNTS + rank * E + e] = counts[e];
+        reinterpret_cast<int32_t*>(sync.ptr[s])[EP_W_COUNTS + rank * E + e] = counts[e];
     }
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x < 32) ep_signal_and_wait(sync, rank, world, status);
-    __syncthreads();
-    // the gathered counts once into shared memory (coalesced), then the plan from there: read one
-    // by one from global memory the dependent loads below cost tens of microseconds
-    extern __shared__ int32_t all_counts[];                    // [world][E]
-    {
-        const volatile int32_t* src = reinterpret_cast<const volatile int32_t*>(sync.ptr[rank]) + EP_SYNC_COUNTS;
-        for (int i = threadIdx.x; i < world * E; i += blockDim.x) all_counts[i] = src[i];
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        const int d = e / EL, le = e - d * EL;
-        int base = 0;
-        for (int l2 = 0; l2 < le; ++l2)
-            for (int s = 0; s < world; ++s) base += all_counts[s * E + d * EL + l2];
-        for (int s = 0; s < rank; ++s) base += all_counts[s * E + e];
-        dst_base[e] = base;
-    }
-    for (int le = threadIdx.x; le < EL; le += blockDim.x) {
-        int c = 0;
-        for (int s = 0; s < world; ++s) c += all_counts[s * E + rank * EL + le];
-        local_counts[le] = c;
-    }
+    if (threadIdx.x < 32) ep_signal(sync, rank, world, EP_CH_COUNTS);
 }
 
-// one block per sorted row p: recv_x[owner][dst_base[e] + (p - offsets[e])] = x[row_token[p]]
-__global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* x, const int32_t* row_token,
-                                                          const int32_t* offsets, const int32_t* dst_base,
-                                                          PeerTable recv, int E, int EL, int vec_per_row,
-                                                          int64_t rows) {
-    __shared__ int s_e;
-    for (int64_t p = blockIdx.x; p < rows; p += gridDim.x) {
-        if (threadIdx.x == 0) {
-            int lo = 0, hi = E;                               // last e with offsets[e] <= p
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (offsets[mid] <= p) lo = mid; else hi = mid;
-            }
-            s_e = lo;
+// ---- dispatch ----------------------------------------------------------------------------------
+struct DispatchArgs {
+    const uint4* x;               // [tokens, hidden] 16-bit
+    const int32_t* row_token;     // sorted row -> token
+    const int32_t* offsets;       // [E + 1] first sorted row per global expert (this rank's rows)
+    PeerTable sync, recv;
+    int world, rank, E, EL, vec_per_row;
+    int64_t rows, cap_rows;
+    int32_t* dst_base;            // out [E]: first row, in the owner's buffers, of this rank's rows per expert
+    int32_t* local_counts;        // out [EL]: rows per local expert over all sources
+    int32_t* local_offsets;       // out [EL + 1]
+    int32_t* active;              // out [EL]: local experts with rows, heaviest first
+    int32_t* n_active;            // out [1]
+    uint32_t wait_polls;
+    int32_t* status;
+};
+
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
+    extern __shared__ int32_t s_dyn[];
+    int32_t* all_counts = s_dyn;                       // [world][E]
+    int32_t* s_base = all_counts + a.world * a.E;      // [E]
+    int32_t* s_lc = s_base + a.E;                      // [EL]
+    int32_t* own = reinterpret_cast<int32_t*>(a.sync.ptr[a.rank]);
+    const bool ok = ep_wait(a.sync, a.rank, a.world, EP_CH_COUNTS, a.wait_polls, a.status);
+    if (ok) {
+        const volatile int32_t* src = own + EP_W_COUNTS;
+        for (int i = threadIdx.x; i < a.world * a.E; i += blockDim.x) all_counts[i] = src[i];
+        __syncthreads();
+        // buffers are expert-major with the sources in rank order inside an expert
+        for (int le = threadIdx.x; le < a.EL; le += blockDim.x) {
+            int c = 0;
+            for (int s = 0; s < a.world; ++s) c += all_counts[s * a.E + a.rank * a.EL + le];
+            s_lc[le] = c;
+        }
+        for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
+            const int d = e / a.EL, le = e - d * a.EL;
+            int base = 0;
+            for (int l2 = 0; l2 < le; ++l2)
+                for (int s = 0; s < a.world; ++s) base += all_counts[s * a.E + d * a.EL + l2];
+            for (int s = 0; s < a.rank; ++s) base += all_counts[s * a.E + e];
+            s_base[e] = base;
         }
         __syncthreads();
-        const int e = s_e;
-        const int d = e / EL;
-        const int64_t drow = (int64_t)dst_base[e] + (p - offsets[e]);
-        const uint4* src = x + (size_t)row_token[p] * vec_per_row;
-        uint4* dst = reinterpret_cast<uint4*>(recv.ptr[d]) + (size_t)drow * vec_per_row;
-        for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = src[i];
-        __syncthreads();
+        if (blockIdx.x == 0) {
+            for (int e = threadIdx.x; e < a.E; e += blockDim.x) a.dst_base[e] = s_base[e];
+            // what the expert kernels need: rows, first row and work order (most rows first, then
+            // lower id) of the local experts
+            for (int le = threadIdx.x; le < a.EL; le += blockDim.x) {
+                const int c = s_lc[le];
+                int off = 0, before = 0;
+                for (int i = 0; i < a.EL; ++i) {
+                    const int ci = s_lc[i];
+                    if (i < le) off += ci;
+                    before += (ci > c || (ci == c && i < le)) && ci > 0;
+                }
+                a.local_counts[le] = c;
+                a.local_offsets[le] = off;
+                if (c > 0) a.active[before] = le;
+                if (le == a.EL - 1) a.local_offsets[a.EL] = off + c;
+            }
+            if (threadIdx.x == 0) {
+                int nz = 0;
+                for (int i = 0; i < a.EL; ++i) nz += s_lc[i] > 0;
+                *a.n_active = nz;
+            }
+        }
+        __shared__ int s_e;
+        for (int64_t p = blockIdx.x; p < a.rows; p += gridDim.x) {
+            if (threadIdx.x == 0) {
+                int lo = 0, hi = a.E;                          // last e with offsets[e] <= p
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if (a.offsets[mid] <= p) lo = mid; else hi = mid;
+                }
+                s_e = lo;
+            }
+            __syncthreads();
+            const int e = s_e;
+            const int64_t drow = (int64_t)s_base[e] + (p - a.offsets[e]);
+            if (drow >= 0 && drow < a.cap_rows) {
+                const uint4* src = a.x + (size_t)a.row_token[p] * a.vec_per_row;
+                uint4* dst = reinterpret_cast<uint4*>(a.recv.ptr[e / a.EL]) + (size_t)drow * a.vec_per_row;
+                for (int i = threadIdx.x; i < a.vec_per_row; i += blockDim.x) dst[i] = src[i];
+            } else if (threadIdx.x == 0) {
+                atomicOr(a.status, STATUS_BOUNDS);               // the owner's buffer is too small: row dropped
+            }
+            __syncthreads();
+        }
+    }
+    if (ep_last_block(own + EP_W_DONE + 0)) {
+        if (threadIdx.x == 0) own[EP_W_WAIT + EP_CH_COUNTS] += 1;
+        if (ok && threadIdx.x < 32) ep_signal(a.sync, a.rank, a.world, EP_CH_ROWS);
     }
 }
 
-// per token: ascending expert id, scaled = w * y; out += scaled — y read from the owner's buffer
+// ---- experts: a wait before, a signal after ----------------------------------------------------
+__global__ void __launch_bounds__(32) ep_wait_kernel(PeerTable sync, int rank, int world, int ch, uint32_t wait_polls,
+                                                     int32_t* status) {
+    ep_wait(sync, rank, world, ch, wait_polls, status);
+    if (threadIdx.x == 0) reinterpret_cast<int32_t*>(sync.ptr[rank])[EP_W_WAIT + ch] += 1;
+}
+
+__global__ void __launch_bounds__(32) ep_signal_kernel(PeerTable sync, int rank, int world, int ch) {
+    ep_signal(sync, rank, world, ch);
+}
+
+// ---- combine -----------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) ep_combine_kernel(PeerTable ys, const int32_t* ids, const float* w,
-                                                         const int32_t* pos, const int32_t* offsets,
-                                                         const int32_t* dst_base, int top_k, int H, int EL,
+__global__ void __launch_bounds__(256) ep_combine_kernel(PeerTable sync, PeerTable ys, const int32_t* ids,
+                                                         const float* w, const int32_t* pos, const int32_t* offsets,
+                                                         const int32_t* dst_base, int rank, int world, int top_k, int H,
+                                                         int EL, int64_t cap_rows, uint32_t wait_polls, int32_t* status,
                                                          T* out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const T** s_row = reinterpret_cast<const T**>(smem_raw);
     float* s_w = reinterpret_cast<float*>(s_row + top_k);
-    const int64_t t = blockIdx.x;
-    for (int r = threadIdx.x; r < top_k; r += blockDim.x) {
-        const int id = ids[t * top_k + r];
-        int rank = 0;
-        for (int q = 0; q < top_k; ++q) {
-            const int other = ids[t * top_k + q];
-            rank += (other < id || (other == id && q < r)) ? 1 : 0;
+    int32_t* own = reinterpret_cast<int32_t*>(sync.ptr[rank]);
+    const bool ok = ep_wait(sync, rank, world, EP_CH_OUT, wait_polls, status);
+    if (ok) {
+        const int64_t t = blockIdx.x;
+        for (int r = threadIdx.x; r < top_k; r += blockDim.x) {
+            const int id = ids[t * top_k + r];
+            int rk = 0;
+            for (int q = 0; q < top_k; ++q) {
+                const int other = ids[t * top_k + q];
+                rk += (other < id || (other == id && q < r)) ? 1 : 0;
+            }
+            const int64_t drow = (int64_t)dst_base[id] + (pos[t * top_k + r] - offsets[id]);
+            const bool inside = drow >= 0 && drow < cap_rows;
+            if (!inside) atomicOr(status, STATUS_BOUNDS);
+            s_row[rk] = inside ? reinterpret_cast<const T*>(ys.ptr[id / EL]) + (size_t)drow * H : nullptr;
+            s_w[rk] = w[t * top_k + r];
         }
-        const int64_t drow = (int64_t)dst_base[id] + (pos[t * top_k + r] - offsets[id]);
-        s_row[rank] = reinterpret_cast<const T*>(ys.ptr[id / EL]) + (size_t)drow * H;
-        s_w[rank] = w[t * top_k + r];
-    }
-    __syncthreads();
-    for (int h = (blockIdx.y * blockDim.x + threadIdx.x) * 8; h < H; h += gridDim.y * blockDim.x * 8) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int r0 = 0; r0 < top_k; r0 += 4) {
-            uint4 raw[4];
+        __syncthreads();
+        for (int h = (blockIdx.y * blockDim.x + threadIdx.x) * 8; h < H; h += gridDim.y * blockDim.x * 8) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int r0 = 0; r0 < top_k; r0 += 4) {
+                uint4 raw[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (r0 + u < top_k) raw[u] = *reinterpret_cast<const uint4*>(s_row[r0 + u] + h);
+                for (int u = 0; u < 4; ++u)
+                    if (r0 + u < top_k)
+                        raw[u] = s_row[r0 + u] ? *reinterpret_cast<const uint4*>(s_row[r0 + u] + h) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (r0 + u < top_k) {
-                    const T* v = reinterpret_cast<const T*>(&raw[u]);
-                    const float wv = s_w[r0 + u];
+                for (int u = 0; u < 4; ++u)
+                    if (r0 + u < top_k) {
+                        const T* v = reinterpret_cast<const T*>(&raw[u]);
+                        const float wv = s_w[r0 + u];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(wv, to_f32(v[i])));
-                }
+                        for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(wv, to_f32(v[i])));
+                    }
+            }
+            uint4 o;
+            T* ov = reinterpret_cast<T*>(&o);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ov[i] = from_f32<T>(acc[i]);
+            *reinterpret_cast<uint4*>(out + t * H + h) = o;
         }
-        uint4 o;
-        T* ov = reinterpret_cast<T*>(&o);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ov[i] = from_f32<T>(acc[i]);
-        *reinterpret_cast<uint4*>(out + t * H + h) = o;
     }
+    if (ep_last_block(own + EP_W_DONE + 1) && threadIdx.x == 0) own[EP_W_WAIT + EP_CH_OUT] += 1;
 }
 
 }  // namespace mummu
@@ -257,107 +339,149 @@ int32_t mummu_ep_free(void* ptr) {
     return MUMMU_OK;
 }
 
-int32_t mummu_ep_plan(MummuMoe* m, const int32_t* all_counts, int32_t rank, int32_t world,
-                      int32_t* dst_base, int32_t* local_counts, void* stream) {
-    MUMMU_REQUIRE(m && all_counts && dst_base && local_counts, "mummu_ep_plan: null argument");
-    MUMMU_REQUIRE(world >= 1 && world <= EP_MAX_RANKS && rank >= 0 && rank < world &&
-                      m->cfg.experts % world == 0 && m->cfg.experts_local == m->cfg.experts / world,
-                  "mummu_ep_plan: rank %d of %d with %d local experts of %d", rank, world,
-                  m->cfg.experts_local, m->cfg.experts);
-    std::lock_guard<std::mutex> lock(m->mu);
-    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
-    LaunchScope scope(m, s, "ep_plan");
-    ep_plan_kernel<<<1, 256, 0, s>>>(all_counts, world, rank, m->cfg.experts, m->cfg.experts_local, dst_base,
-                                     local_counts);
-    MUMMU_CUDA_TRY(cudaGetLastError());
+size_t mummu_ep_sync_bytes(int32_t world, int32_t experts) {
+    return (size_t)(EP_W_COUNTS + (size_t)world * experts) * 4;
+}
+
+int32_t mummu_ep_reset(int32_t device, void* own_sync, int32_t world, int32_t experts) {
+    MUMMU_REQUIRE(own_sync && world >= 1 && experts >= 1, "mummu_ep_reset: bad argument");
+    int prev = -1;
+    MUMMU_CUDA_TRY(cudaGetDevice(&prev));
+    if (prev != device) MUMMU_CUDA_TRY(cudaSetDevice(device));
+    cudaError_t err = cudaDeviceSynchronize();
+    if (err == cudaSuccess) err = cudaMemset(own_sync, 0, mummu_ep_sync_bytes(world, experts));
+    if (err == cudaSuccess) err = cudaDeviceSynchronize();
+    if (prev != device) cudaSetDevice(prev);
+    if (err != cudaSuccess) {
+        set_error("mummu_ep_reset: %s", cudaGetErrorString(err));
+        return MUMMU_ERR_DEVICE;
+    }
     return MUMMU_OK;
 }
 
 static int ep_check_ranks(MummuMoe* m, int32_t rank, int32_t world, const char* who) {
     MUMMU_REQUIRE(world >= 1 && world <= EP_MAX_RANKS && rank >= 0 && rank < world &&
-                      m->cfg.experts % world == 0 && m->cfg.experts_local == m->cfg.experts / world,
-                  "%s: rank %d of %d with %d local experts of %d", who, rank, world, m->cfg.experts_local,
-                  m->cfg.experts);
+                      m->cfg.experts % world == 0 && m->cfg.experts_local == m->cfg.experts / world &&
+                      m->cfg.expert_first == rank * m->cfg.experts_local,
+                  "%s: rank %d of %d with local experts [%d, %d) of %d", who, rank, world, m->cfg.expert_first,
+                  m->cfg.expert_first + m->cfg.experts_local, m->cfg.experts);
     return MUMMU_OK;
 }
 
-size_t mummu_ep_sync_bytes(int32_t world, int32_t experts) {
-    return (size_t)(EP_SYNC_COUNTS + (size_t)world * experts) * 4;
+static PeerTable peer_table(void* const* ptrs, int world) {
+    PeerTable t{};
+    for (int i = 0; i < world; ++i) t.ptr[i] = ptrs[i];
+    return t;
 }
 
-int32_t mummu_ep_exchange_plan(MummuMoe* m, const int32_t* counts, void* const* peer_sync, int32_t rank,
-                               int32_t world, int32_t* dst_base, int32_t* local_counts, void* stream) {
-    MUMMU_REQUIRE(m && counts && peer_sync && dst_base && local_counts, "mummu_ep_exchange_plan: null argument");
-    int rc = ep_check_ranks(m, rank, world, "mummu_ep_exchange_plan");
+static uint32_t wait_polls_of(const MummuMoe* m) { return m->sw.wait_polls ? m->sw.wait_polls : EP_WAIT_POLLS_DEFAULT; }
+
+int32_t mummu_ep_post_counts(MummuMoe* m, const int32_t* counts, void* const* peer_sync, int32_t rank,
+                             int32_t world, void* stream) {
+    MUMMU_REQUIRE(m && counts && peer_sync, "mummu_ep_post_counts: null argument");
+    int rc = ep_check_ranks(m, rank, world, "mummu_ep_post_counts");
     if (rc) return rc;
     std::lock_guard<std::mutex> lock(m->mu);
     cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
-    PeerTable t{};
-    for (int i = 0; i < world; ++i) t.ptr[i] = peer_sync[i];
-    LaunchScope scope(m, s, "ep_exchange_plan");
-    ep_exchange_plan_kernel<<<1, 256, (size_t)world * m->cfg.experts * sizeof(int32_t), s>>>(counts, t, world, rank, m->cfg.experts, m->cfg.experts_local, dst_base,
-                                              local_counts, m->status);
-    MUMMU_CUDA_TRY(cudaGetLastError());
-    return MUMMU_OK;
-}
-
-int32_t mummu_ep_barrier(MummuMoe* m, void* const* peer_sync, int32_t rank, int32_t world, void* stream) {
-    MUMMU_REQUIRE(m && peer_sync, "mummu_ep_barrier: null argument");
-    int rc = ep_check_ranks(m, rank, world, "mummu_ep_barrier");
-    if (rc) return rc;
-    std::lock_guard<std::mutex> lock(m->mu);
-    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
-    PeerTable t{};
-    for (int i = 0; i < world; ++i) t.ptr[i] = peer_sync[i];
-    LaunchScope scope(m, s, "ep_barrier");
-    ep_barrier_kernel<<<1, 32, 0, s>>>(t, rank, world, m->status);
+    LaunchScope scope(m, s, "ep_post_counts");
+    ep_post_counts_kernel<<<1, 256, 0, s>>>(counts, peer_table(peer_sync, world), world, rank, m->cfg.experts);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }
 
 int32_t mummu_ep_dispatch(MummuMoe* m, const void* x, const int32_t* row_token, const int32_t* offsets,
-                          const int32_t* dst_base, void* const* peer_recv, int32_t world, int32_t rows,
-                          void* stream) {
-    MUMMU_REQUIRE(m && x && row_token && offsets && dst_base && peer_recv, "mummu_ep_dispatch: null argument");
-    MUMMU_REQUIRE(world >= 1 && world <= EP_MAX_RANKS, "mummu_ep_dispatch: %d ranks", world);
+                          void* const* peer_sync, void* const* peer_recv, int32_t rank, int32_t world,
+                          int32_t rows, int64_t cap_rows, int32_t* dst_base, int32_t* local_counts, void* stream) {
+    MUMMU_REQUIRE(m && x && row_token && offsets && peer_sync && peer_recv && dst_base && local_counts,
+                  "mummu_ep_dispatch: null argument");
+    int rc = ep_check_ranks(m, rank, world, "mummu_ep_dispatch");
+    if (rc) return rc;
     MUMMU_REQUIRE(dtype_size(m->cfg.act_dtype) == 2 && m->cfg.hidden % 8 == 0,
                   "mummu_ep_dispatch: 16-bit activations with hidden %% 8 == 0 only");
-    if (rows == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(rows >= 0 && cap_rows >= 0, "mummu_ep_dispatch: rows %d, cap_rows %lld", rows, (long long)cap_rows);
     std::lock_guard<std::mutex> lock(m->mu);
     cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
-    PeerTable t{};
-    for (int i = 0; i < world; ++i) t.ptr[i] = peer_recv[i];
-    const int64_t blocks = rows < 148 * 16 ? rows : 148 * 16;
+    DispatchArgs a{};
+    a.x = (const uint4*)x;
+    a.row_token = row_token;
+    a.offsets = offsets;
+    a.sync = peer_table(peer_sync, world);
+    a.recv = peer_table(peer_recv, world);
+    a.world = world;
+    a.rank = rank;
+    a.E = m->cfg.experts;
+    a.EL = m->cfg.experts_local;
+    a.vec_per_row = m->cfg.hidden * 2 / 16;
+    a.rows = rows;
+    a.cap_rows = cap_rows;
+    a.dst_base = dst_base;
+    a.local_counts = local_counts;
+    a.local_offsets = m->offsets;
+    a.active = m->active;
+    a.n_active = m->n_active;
+    a.wait_polls = wait_polls_of(m);
+    a.status = m->status;
+    // even a rank without rows takes part: its block plans the local experts and signals
+    const int64_t blocks = rows < 1 ? 1 : (rows < 148 * 16 ? rows : 148 * 16);
+    const size_t smem = ((size_t)world * a.E + a.E + a.EL) * sizeof(int32_t);
     LaunchScope scope(m, s, "ep_dispatch");
-    ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint4*)x, row_token, offsets, dst_base, t,
-                                                        m->cfg.experts, m->cfg.experts_local,
-                                                        m->cfg.hidden * 2 / 16, rows);
+    ep_dispatch_kernel<<<(unsigned)blocks, 256, smem, s>>>(a);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }
 
-int32_t mummu_ep_combine(MummuMoe* m, void* const* peer_ys, const int32_t* ids, const float* w,
-                         const int32_t* pos, const int32_t* offsets, const int32_t* dst_base,
-                         int32_t tokens, int32_t top_k, int32_t world, void* out, void* stream) {
-    MUMMU_REQUIRE(m && peer_ys && ids && w && pos && offsets && dst_base && out, "mummu_ep_combine: null argument");
-    MUMMU_REQUIRE(world >= 1 && world <= EP_MAX_RANKS, "mummu_ep_combine: %d ranks", world);
+int32_t mummu_ep_experts(MummuMoe* m, void* const* peer_sync, int32_t rank, int32_t world, const void* recv_own,
+                         const int32_t* local_counts, int64_t rows_cap, void* ys_own, void* stream) {
+    MUMMU_REQUIRE(m && peer_sync && recv_own && local_counts && ys_own, "mummu_ep_experts: null argument");
+    int rc = ep_check_ranks(m, rank, world, "mummu_ep_experts");
+    if (rc) return rc;
+    MUMMU_REQUIRE(rows_cap >= 0 && rows_cap <= INT32_MAX, "mummu_ep_experts: rows_cap %lld", (long long)rows_cap);
+    cudaStream_t s;
+    const PeerTable t = peer_table(peer_sync, world);
+    {
+        std::lock_guard<std::mutex> lock(m->mu);
+        s = stream ? (cudaStream_t)stream : m->stream;
+        LaunchScope scope(m, s, "ep_wait_rows");
+        ep_wait_kernel<<<1, 32, 0, s>>>(t, rank, world, EP_CH_ROWS, wait_polls_of(m), m->status);
+        MUMMU_CUDA_TRY(cudaGetLastError());
+    }
+    // the dispatch stage left the local experts' offsets and work order in the handle
+    if ((rc = mummu_moe_experts_planned(m, recv_own, local_counts, (int32_t)rows_cap, ys_own, s))) return rc;
+    std::lock_guard<std::mutex> lock(m->mu);
+    LaunchScope scope(m, s, "ep_signal_out");
+    ep_signal_kernel<<<1, 32, 0, s>>>(t, rank, world, EP_CH_OUT);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+int32_t mummu_ep_combine(MummuMoe* m, void* const* peer_sync, void* const* peer_ys, const int32_t* ids,
+                         const float* w, const int32_t* pos, const int32_t* offsets, const int32_t* dst_base,
+                         int32_t rank, int32_t world, int32_t tokens, int32_t top_k, int64_t cap_rows, void* out,
+                         void* stream) {
+    MUMMU_REQUIRE(m && peer_sync && peer_ys && ids && w && pos && offsets && dst_base && out,
+                  "mummu_ep_combine: null argument");
+    int rc = ep_check_ranks(m, rank, world, "mummu_ep_combine");
+    if (rc) return rc;
     MUMMU_REQUIRE(dtype_size(m->cfg.act_dtype) == 2 && m->cfg.hidden % 8 == 0,
                   "mummu_ep_combine: 16-bit activations with hidden %% 8 == 0 only");
-    if (tokens == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(tokens >= 0 && top_k >= 1, "mummu_ep_combine: tokens %d, top_k %d", tokens, top_k);
     std::lock_guard<std::mutex> lock(m->mu);
     cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
-    PeerTable t{};
-    for (int i = 0; i < world; ++i) t.ptr[i] = peer_ys[i];
     const int H = m->cfg.hidden;
-    const dim3 grid((unsigned)tokens, tokens < 512 ? (unsigned)((H / 8 + 255) / 256) : 1u);
+    // a rank without tokens still consumes the epoch
+    const dim3 grid((unsigned)(tokens < 1 ? 1 : tokens), tokens < 512 ? (unsigned)((H / 8 + 255) / 256) : 1u);
     const size_t smem = (size_t)top_k * (sizeof(void*) + sizeof(float));
+    const PeerTable ts = peer_table(peer_sync, world), ty = peer_table(peer_ys, world);
+    const int k_eff = tokens < 1 ? 0 : top_k;
     LaunchScope scope(m, s, "ep_combine");
     if (m->cfg.act_dtype == MUMMU_F16)
-        ep_combine_kernel<__half><<<grid, 256, smem, s>>>(t, ids, w, pos, offsets, dst_base, top_k, H,
-                                                         m->cfg.experts_local, (__half*)out);
+        ep_combine_kernel<__half><<<grid, 256, smem, s>>>(ts, ty, ids, w, pos, offsets, dst_base, rank, world, k_eff, tokens < 1 ? 0 : H,
+                                                         m->cfg.experts_local, cap_rows, wait_polls_of(m), m->status,
+                                                         (__half*)out);
     else
-        ep_combine_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(t, ids, w, pos, offsets, dst_base, top_k, H,
-                                                                m->cfg.experts_local, (__nv_bfloat16*)out);
+        ep_combine_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(ts, ty, ids, w, pos, offsets, dst_base, rank, world, k_eff,
+                                                                tokens < 1 ? 0 : H, m->cfg.experts_local, cap_rows,
+                                                                wait_polls_of(m), m->status, (__nv_bfloat16*)out);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }

@@ -588,109 +588,6 @@ static size_t router_wide_smem(int H, int E, int e_pad, int k, int nwarps, int R
 }
 
 
-// Large-T router, register tiled like an SGEMM but with the oracle's exact arithmetic.  A block of
-// 8 warps owns 16 tokens and walks the experts in tiles of 32; warp j owns lane j of the 8-lane dot
-// (k = 8i + j, one fused multiply-add per step in ascending i); inside a warp, thread (tg, eg) owns
-// 4 tokens x 4 experts.  x and W chunks of 64 k sit in shared memory - x as [token][lane][i] so a
-// thread reads four consecutive steps of its lane with one 16-byte load - and the next chunk's
-// global loads are in flight while the current one is multiplied: 8 FMAs per shared load.
-constexpr int RT_KC = 64;       // k per chunk = 8 steps of every lane
-constexpr int RT_TM = 16;       // tokens per block
-constexpr int RT_TE = 32;       // experts per tile
-template <typename TX>
-__global__ void __launch_bounds__(256) router_tiled_kernel(RouterArgs a) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* xs = reinterpret_cast<float*>(smem_raw);             // [16 tokens][8 lanes][8 steps]
-    float* ws = xs + RT_TM * RT_KC;                              // [64 k][32 experts]
-    float* parts = ws + RT_KC * RT_TE;                           // [16 tokens][32 experts][8 lanes]
-    float* tk = parts + RT_TM * RT_TE * 8;                       // top-k scratch, 8 warps
-    const int H = a.H, E = a.E;
-    const int tid = threadIdx.x, j = tid >> 5, lane = tid & 31;
-    const int tg = lane >> 3, eg = lane & 7;                     // tokens 4tg.., experts 4eg..
-    const int t0 = blockIdx.x * RT_TM;
-    const TX* x = reinterpret_cast<const TX*>(a.x);
-    const int n_chunks = H / RT_KC;
-    // loaders: x chunk = 16 x 64 values (4 per thread), W chunk = 64 x 32 floats (8 per thread)
-    const int x_tok = tid >> 4, x_k = (tid & 15) * 4;
-    const int w_row = tid >> 2, w_col = (tid & 3) * 8;
-
-    for (int e0 = 0; e0 < E; e0 += RT_TE) {
-        float acc[4][4];
-#pragma unroll
-        for (int p = 0; p < 4; ++p)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) acc[p][q] = 0.0f;
-        float xr[4];
-        float4 wr[2];
-        auto load_chunk = [&](int c) {
-            const int t = t0 + x_tok;
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                xr[u] = t < a.T ? to_f32(x[(size_t)t * H + c * RT_KC + x_k + u]) : 0.0f;
-            const float* wp = a.w + (size_t)(c * RT_KC + w_row) * E + e0 + w_col;
-            wr[0] = __ldg(reinterpret_cast<const float4*>(wp));
-            wr[1] = __ldg(reinterpret_cast<const float4*>(wp + 4));
-        };
-        load_chunk(0);
-        for (int c = 0; c < n_chunks; ++c) {
-            __syncthreads();
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int k = x_k + u;                           // lane k & 7, step k >> 3
-                xs[(x_tok * 8 + (k & 7)) * 8 + (k >> 3)] = xr[u];
-            }
-            *reinterpret_cast<float4*>(ws + w_row * RT_TE + w_col) = wr[0];
-            *reinterpret_cast<float4*>(ws + w_row * RT_TE + w_col + 4) = wr[1];
-            __syncthreads();
-            if (c + 1 < n_chunks) load_chunk(c + 1);
-            float xv[4][8];
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                const float4 lo = *reinterpret_cast<const float4*>(xs + ((tg * 4 + p) * 8 + j) * 8);
-                const float4 hi = *reinterpret_cast<const float4*>(xs + ((tg * 4 + p) * 8 + j) * 8 + 4);
-                xv[p][0] = lo.x; xv[p][1] = lo.y; xv[p][2] = lo.z; xv[p][3] = lo.w;
-                xv[p][4] = hi.x; xv[p][5] = hi.y; xv[p][6] = hi.z; xv[p][7] = hi.w;
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 wv = *reinterpret_cast<const float4*>(ws + (8 * i + j) * RT_TE + eg * 4);
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    acc[p][0] = __fmaf_rn(xv[p][i], wv.x, acc[p][0]);
-                    acc[p][1] = __fmaf_rn(xv[p][i], wv.y, acc[p][1]);
-                    acc[p][2] = __fmaf_rn(xv[p][i], wv.z, acc[p][2]);
-                    acc[p][3] = __fmaf_rn(xv[p][i], wv.w, acc[p][3]);
-                }
-            }
-        }
-        // fold the 8 lanes (one per warp) in the fixed order
-#pragma unroll
-        for (int p = 0; p < 4; ++p)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) parts[((tg * 4 + p) * RT_TE + eg * 4 + q) * 8 + j] = acc[p][q];
-        __syncthreads();
-        for (int o = tid; o < RT_TM * RT_TE; o += 256) {
-            const int tt = o / RT_TE, el = o - tt * RT_TE;
-            const int t = t0 + tt, e = e0 + el;
-            if (t < a.T && e < E) {
-                const float* l = parts + (size_t)o * 8;
-                float sacc = __fadd_rn(__fadd_rn(__fadd_rn(l[0], l[4]), __fadd_rn(l[1], l[5])),
-                                       __fadd_rn(__fadd_rn(l[2], l[6]), __fadd_rn(l[3], l[7])));
-                if (a.bias) sacc = __fadd_rn(sacc, a.bias[e]);
-                a.logits[(size_t)t * E + e] = sacc;
-            }
-        }
-    }
-    __threadfence_block();
-    __syncthreads();
-    const int per_warp = E + 2 * a.k;
-    float* sm_v = tk + (size_t)j * per_warp;
-    for (int tt = j; tt < RT_TM; tt += 8) {
-        const int t = t0 + tt;
-        if (t < a.T) warp_softmax_topk(a, t, sm_v, sm_v + E, reinterpret_cast<int32_t*>(sm_v + E + a.k));
-    }
-}
-
 static size_t router_smem(int H, int E, int k, int TT) {
     size_t H8 = (size_t)(H & ~7);
     return (H8 * R_ES + (size_t)TT * H + (size_t)TT * 64 + (size_t)8 * (E + 2 * k)) * 4;
@@ -699,14 +596,6 @@ static size_t router_smem(int H, int E, int k, int TT) {
 template <typename TX>
 static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
     const int e_pad = (a.E + 31) & ~31;
-    if (a.T >= 256 && a.E % RT_TE == 0 && a.H % RT_KC == 0 && (e_pad > 128 || getenv("MUMMU_CUDA_ROUTER_TILED"))) {
-        const size_t smem = ((size_t)RT_TM * RT_KC + RT_KC * RT_TE + RT_TM * RT_TE * 8 + (size_t)8 * (a.E + 2 * a.k)) * 4;
-        MUMMU_CUDA_TRY(allow_big_smem(router_tiled_kernel<TX>, m->cfg.device));
-        LaunchScope scope(m, s, "router");
-        router_tiled_kernel<TX><<<(a.T + RT_TM - 1) / RT_TM, 256, smem, s>>>(a);
-        MUMMU_CUDA_TRY(cudaGetLastError());
-        return MUMMU_OK;
-    }
     if (a.T >= 256 && e_pad <= 128) {
         // up to 64 experts: 512 threads with 128 registers each take 16 tokens per block; wider
         // routers run 1024 threads (64 registers) and take 8
@@ -741,7 +630,7 @@ static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
     int tpt = a.T >= 2048 ? 4 : (a.T >= 256 ? 2 : 1);
     while (tpt > 1 && router_smem(a.H, a.E, a.k, 4 * tpt) > 200 * 1024) tpt >>= 1;
     if (tpt == 1 && sizeof(TX) == 2 && a.H % 32 == 0 && a.E % R_ES == 0 &&
-        a.wt != nullptr && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && !getenv("MUMMU_CUDA_ROUTER_PLAIN")) {
+        a.wt != nullptr && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && !m->sw.router_plain) {
         const int S = a.H / 8 + 4;
         const size_t smem_t = ((size_t)64 * S + (size_t)4 * 8 * S + 4 * 64 + (size_t)8 * (a.E + 2 * a.k)) * 4;
         if (smem_t <= 200 * 1024) {
@@ -1586,6 +1475,15 @@ extern "C" int32_t mummu_moe_route_noalloc(const void* x, int32_t act_dtype, con
                   tokens, experts, NOALLOC_MAX_TOKENS, NOALLOC_MAX_LOGITS);
     if (tokens == 0) return MUMMU_OK;
     MUMMU_REQUIRE(x && router_w && ids_out && w_out, "mummu_moe_route_noalloc: null pointer");
+    // the kernel reads eight experts of one router row as two 128-bit words: a pointer into the
+    // middle of a packed buffer that is only 4-byte aligned would fault on the device
+    MUMMU_REQUIRE((reinterpret_cast<uintptr_t>(router_w) & 15) == 0,
+                  "mummu_moe_route_noalloc: router_w must be 16-byte aligned (got %p)", (const void*)router_w);
+    MUMMU_REQUIRE((reinterpret_cast<uintptr_t>(x) & (act_dtype == MUMMU_F32 ? 3 : 1)) == 0 &&
+                      (reinterpret_cast<uintptr_t>(ids_out) & 3) == 0 &&
+                      (reinterpret_cast<uintptr_t>(w_out) & 3) == 0 &&
+                      (!bias || (reinterpret_cast<uintptr_t>(bias) & 3) == 0),
+                  "mummu_moe_route_noalloc: x, bias, ids_out and w_out must be aligned to their element size");
     int prev = -1;
     MUMMU_CUDA_TRY(cudaGetDevice(&prev));
     if (prev != device) MUMMU_CUDA_TRY(cudaSetDevice(device));

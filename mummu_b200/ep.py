@@ -16,8 +16,6 @@ ranks with the gloo backend; only steps 1, 2, 5 and 6 touch the CUDA library.
 """
 from __future__ import annotations
 
-import os
-
 from dataclasses import dataclass
 from typing import Optional
 
@@ -68,7 +66,7 @@ class PeerWorkspace:
         import ctypes as C
         import torch.distributed as dist
         from . import _lib as L
-        self.L, self.device = L, device
+        self.L, self.device, self.group = L, device, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.cap_rows, self.bytes = cap_rows, cap_rows * hidden * 2
         self.own, self.opened, handles = [], [], []
@@ -99,45 +97,106 @@ class PeerWorkspace:
         self.recv_table, self.ys_table, self.sync_table = self.tables
         self.recv_ptr, self.ys_ptr, self.sync_ptr = self.own
         self.experts = experts
-        if group is not None or dist.is_initialized():
-            dist.barrier(group=group)          # every peer has mapped every (zeroed) block
+        dist.barrier(group=group)          # every peer has mapped every (zeroed) block
+
+    def reset(self):
+        """After a timed-out step: every rank zeroes its own block of flags and epochs, between two
+        host barriers (nobody signals into a block that is about to be zeroed)."""
+        import torch.distributed as dist
+        dist.barrier(group=self.group)
+        rc = self.L.lib.mummu_ep_reset(self.device, self.sync_ptr, self.world, self.experts)
+        if rc:
+            raise RuntimeError(self.L.last_error())
+        dist.barrier(group=self.group)
 
     def close(self):
+        """Unmap the peers' blocks, wait until every rank has done so, then free the own blocks:
+        freeing exported memory that a peer still has mapped is undefined."""
+        import torch.distributed as dist
         for p in self.opened:
             self.L.lib.mummu_ep_close(p)
+        self.opened = []
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
         for p in self.own:
             self.L.lib.mummu_ep_free(p)
-        self.opened, self.own = [], []
+        self.own = []
+
+
+class LocalWorkspaces:
+    """`world` rank workspaces on ONE device in one process (no process group, no IPC): the peers'
+    blocks are plain device pointers.  For running the rank handles of a group stage by stage on a
+    single stream (tests on one GPU; never several streams or processes: a stage that waits for a
+    kernel that has not been scheduled would only run into its bound)."""
+
+    def __init__(self, device: int, world: int, cap_rows: int, hidden: int, experts: int):
+        import ctypes as C
+        from . import _lib as L
+        self.L, self.device, self.world, self.experts = L, device, world, experts
+        self.cap_rows = cap_rows
+        sync_bytes = int(L.lib.mummu_ep_sync_bytes(world, experts))
+        self.ptrs = [[], [], []]                       # recv, ys, sync per rank
+        for _ in range(world):
+            for which, nbytes in enumerate((cap_rows * hidden * 2, cap_rows * hidden * 2, sync_bytes)):
+                ptr, h = C.c_void_p(), C.create_string_buffer(64)
+                rc = L.lib.mummu_ep_alloc(device, nbytes, C.byref(ptr), h)
+                if rc:
+                    raise RuntimeError(L.last_error())
+                self.ptrs[which].append(ptr.value)
+        self.views = [_RankView(self, r) for r in range(world)]
+
+    def reset(self):
+        for p in self.ptrs[2]:
+            rc = self.L.lib.mummu_ep_reset(self.device, p, self.world, self.experts)
+            if rc:
+                raise RuntimeError(self.L.last_error())
+
+    def close(self):
+        for lst in self.ptrs:
+            for p in lst:
+                self.L.lib.mummu_ep_free(p)
+        self.ptrs = [[], [], []]
+
+
+class _RankView:
+    def __init__(self, ws: LocalWorkspaces, rank: int):
+        import ctypes as C
+        self.world, self.rank, self.cap_rows, self.experts = ws.world, rank, ws.cap_rows, ws.experts
+        mk = lambda lst: (C.c_void_p * ws.world)(*lst)
+        self.recv_table, self.ys_table, self.sync_table = mk(ws.ptrs[0]), mk(ws.ptrs[1]), mk(ws.ptrs[2])
+        self.recv_ptr, self.ys_ptr, self.sync_ptr = ws.ptrs[0][rank], ws.ptrs[1][rank], ws.ptrs[2][rank]
 
 
 class ExpertParallelMoe:
     """One MoE layer sharded over `group`; each rank calls forward on its own tokens.
 
-    With a `PeerWorkspace` (16-bit activations) rows move by peer stores and loads over NVLink and
+    With a workspace (16-bit activations) rows move by peer stores and loads over NVLink and
     nothing waits for the host; without one the exchange is two NCCL all-to-alls whose split sizes
-    are read back to the host."""
+    are read back to the host.  `rank`/`world` given explicitly (with a `LocalWorkspaces` view)
+    build one rank of a group that lives on a single device."""
 
     def __init__(self, cfg, group=None, device: Optional[int] = None, act_dtype: int = 2,
                  weight_dtype: Optional[int] = None, max_tokens: int = 0, workspace=None,
-                 scratch_donor=None):
+                 scratch_donor=None, rank: Optional[int] = None, world: Optional[int] = None):
         import torch
-        import torch.distributed as dist
         from . import moe
-        self.dist = dist
         self.group = group
-        self.rank = dist.get_rank(group)
-        self.world = dist.get_world_size(group)
+        if rank is None:
+            import torch.distributed as dist
+            self.dist = dist
+            self.rank = dist.get_rank(group)
+            self.world = dist.get_world_size(group)
+        else:
+            self.dist, self.rank, self.world = None, rank, world
         assert cfg.num_experts % self.world == 0, "experts must divide evenly over the ranks"
         self.el = cfg.num_experts // self.world
         self.cfg = cfg
         dev = torch.cuda.current_device() if device is None else device
         self.device = torch.device("cuda", dev)
-        import torch as _t  # noqa: F401
         # scratch for the local experts must hold the rows that can arrive: every rank's tokens * k
         self.workspace = workspace
-        # flags and counts in peer memory instead of NCCL calls (MUMMU_EP_NCCL_SYNC=1 keeps NCCL)
-        self.device_sync = (workspace is not None and cfg.num_experts <= getattr(workspace, "experts", 0)
-                            and not os.environ.get("MUMMU_EP_NCCL_SYNC"))
+        if workspace is not None:
+            assert cfg.num_experts <= workspace.experts, "workspace sync block too small for this router"
         self.moe = moe.SparseMoeConfig(cfg.hidden_size, cfg.expert_intermediate_size, cfg.num_experts,
                                        cfg.num_experts_per_tok).init(
             device=dev, act_dtype=act_dtype, weight_dtype=weight_dtype,
@@ -145,7 +204,6 @@ class ExpertParallelMoe:
             expert_first=self.rank * self.el, experts_local=self.el)
         if scratch_donor is not None:
             self.moe.adopt_scratch(scratch_donor.moe)
-        self._flag = torch.zeros(1, device=self.device)
 
     def set_router(self, weight, layout: int = 0, bias=None):
         self.moe.set_router(weight, layout, bias)
@@ -154,35 +212,42 @@ class ExpertParallelMoe:
         """Banks of this rank's experts only: [experts / world, out, in]."""
         self.moe.set_banks(gate, up, down)
 
-    def _barrier(self):
-        if self.device_sync:
-            self.moe.ep_barrier(self.workspace.sync_table, self.rank, self.world)
-        else:
-            self.dist.all_reduce(self._flag, group=self.group)   # device-side: nobody waits on the host
+    # ---- the four stages (see include/mummu_cuda.h); a rank runs them in this order ------------
+    def stage_route(self, x, top_k: int, norm_topk_prob: bool):
+        import torch
+        m, ws = self.moe, self.workspace
+        T = x.shape[0]
+        assert T * top_k * self.world <= ws.cap_rows, "workspace too small for the rows that may arrive"
+        st = dict(x=x, top_k=top_k)
+        st["ids"], st["w"], st["counts"], st["offsets"], st["row_token"], st["pos"] = m.route_grouped(x, top_k, norm_topk_prob)
+        m.ep_post_counts(st["counts"], ws.sync_table, self.rank, self.world)
+        i32 = dict(dtype=torch.int32, device=x.device)
+        st["dst_base"], st["local_counts"] = torch.empty(self.cfg.num_experts, **i32), torch.empty(self.el, **i32)
+        return st
+
+    def stage_dispatch(self, st):
+        ws = self.workspace
+        self.moe.ep_dispatch(st["x"], st["row_token"], st["offsets"], ws.sync_table, ws.recv_table, self.rank,
+                             self.world, ws.cap_rows, st["dst_base"], st["local_counts"])
+
+    def stage_experts(self, st):
+        ws = self.workspace
+        self.moe.ep_experts(ws.sync_table, self.rank, self.world, ws.recv_ptr, st["local_counts"], ws.cap_rows,
+                            ws.ys_ptr)
+
+    def stage_combine(self, st):
+        import torch
+        ws = self.workspace
+        y = torch.empty_like(st["x"])
+        self.moe.ep_combine(ws.sync_table, ws.ys_table, st["ids"], st["w"], st["pos"], st["offsets"], st["dst_base"],
+                            self.rank, self.world, ws.cap_rows, y)
+        return y
 
     def forward_p2p(self, x, top_k: int, norm_topk_prob: bool):
-        import torch
-        dist, m, ws = self.dist, self.moe, self.workspace
-        T, H = x.shape
-        E, R = self.cfg.num_experts, self.world
-        assert T * top_k * R <= ws.cap_rows, "workspace too small for the rows that may arrive"
-        i32 = dict(dtype=torch.int32, device=x.device)
-        ids, w, counts, offsets, row_token, pos = m.route_grouped(x, top_k, norm_topk_prob)
-        dst_base, local_counts = torch.empty(E, **i32), torch.empty(self.el, **i32)
-        if self.device_sync:
-            # counts all-gather, plan and both barriers on the device: the step holds no collective
-            m.ep_exchange_plan(counts, ws.sync_table, self.rank, R, dst_base, local_counts)
-        else:
-            all_counts = torch.empty(R, E, **i32)
-            dist.all_gather_into_tensor(all_counts, counts, group=self.group)
-            m.ep_plan(all_counts, self.rank, R, dst_base, local_counts)
-        m.ep_dispatch(x, row_token, offsets, dst_base, ws.recv_table, R)
-        self._barrier()                                           # every rank's rows have landed
-        m.experts_grouped_raw(ws.recv_ptr, local_counts, T * top_k * R, ws.ys_ptr)
-        self._barrier()                                           # every rank's outputs are written
-        y = torch.empty_like(x)
-        m.ep_combine(ws.ys_table, ids, w, pos, offsets, dst_base, R, y)
-        return y
+        st = self.stage_route(x, top_k, norm_topk_prob)
+        self.stage_dispatch(st)
+        self.stage_experts(st)
+        return self.stage_combine(st)
 
     def forward(self, x, top_k: int, norm_topk_prob: bool):
         if self.workspace is not None:

@@ -280,6 +280,11 @@ class SparseMoe:
     def launch_count(self) -> int:
         return int(L.lib.mummu_moe_launch_count(self._h))
 
+    def set_switch(self, name: str, value: int) -> None:
+        """One kernel-variant switch of this layer (the handle read MUMMU_CUDA_<name> when it was
+        created; the reference reads its MUMMU_* switches once too, nn/packed_gemv.rs:85-92)."""
+        _check(L.lib.mummu_moe_set_switch(self._h, name.encode(), int(value)))
+
     # -- staged calls (device tensors), used by the expert-parallel layer -----------------------
     def route_grouped(self, xt, top_k: int, norm_topk_prob: bool):
         """`route_flat` + `permute` on device tensors; one launch for decode-sized calls.
@@ -311,28 +316,27 @@ class SparseMoe:
         _check(L.lib.mummu_moe_experts_grouped(self._h, xs_ptr, counts.data_ptr(), rows, ys_ptr,
                                                _torch_stream()))
 
-    def ep_plan(self, all_counts, rank: int, world: int, dst_base, local_counts) -> None:
-        _check(L.lib.mummu_ep_plan(self._h, all_counts.data_ptr(), rank, world, dst_base.data_ptr(),
-                                   local_counts.data_ptr(), _torch_stream()))
+    # stages of the expert-parallel layer (peer memory; see include/mummu_cuda.h)
+    def ep_post_counts(self, counts, sync_table, rank: int, world: int) -> None:
+        _check(L.lib.mummu_ep_post_counts(self._h, counts.data_ptr(), sync_table, rank, world, _torch_stream()))
 
-    def ep_exchange_plan(self, counts, sync_table, rank: int, world: int, dst_base, local_counts) -> None:
-        """Counts all-gather by peer stores + plan, one launch, no collective library."""
-        _check(L.lib.mummu_ep_exchange_plan(self._h, counts.data_ptr(), sync_table, rank, world,
-                                            dst_base.data_ptr(), local_counts.data_ptr(), _torch_stream()))
-
-    def ep_barrier(self, sync_table, rank: int, world: int) -> None:
-        _check(L.lib.mummu_ep_barrier(self._h, sync_table, rank, world, _torch_stream()))
-
-    def ep_dispatch(self, x, row_token, offsets, dst_base, peer_table, world: int) -> None:
+    def ep_dispatch(self, x, row_token, offsets, sync_table, recv_table, rank: int, world: int, cap_rows: int,
+                    dst_base, local_counts) -> None:
         _check(L.lib.mummu_ep_dispatch(self._h, x.data_ptr(), row_token.data_ptr(), offsets.data_ptr(),
-                                       dst_base.data_ptr(), peer_table, world, row_token.numel(),
-                                       _torch_stream()))
+                                       sync_table, recv_table, rank, world, row_token.numel(), cap_rows,
+                                       dst_base.data_ptr(), local_counts.data_ptr(), _torch_stream()))
 
-    def ep_combine(self, peer_table, ids, w, pos, offsets, dst_base, world: int, out) -> None:
+    def ep_experts(self, sync_table, rank: int, world: int, recv_ptr: int, local_counts, rows_cap: int,
+                   ys_ptr: int) -> None:
+        _check(L.lib.mummu_ep_experts(self._h, sync_table, rank, world, recv_ptr, local_counts.data_ptr(),
+                                      rows_cap, ys_ptr, _torch_stream()))
+
+    def ep_combine(self, sync_table, ys_table, ids, w, pos, offsets, dst_base, rank: int, world: int,
+                   cap_rows: int, out) -> None:
         tokens, top_k = ids.shape
-        _check(L.lib.mummu_ep_combine(self._h, peer_table, ids.data_ptr(), w.data_ptr(), pos.data_ptr(),
-                                      offsets.data_ptr(), dst_base.data_ptr(), tokens, top_k, world,
-                                      out.data_ptr(), _torch_stream()))
+        _check(L.lib.mummu_ep_combine(self._h, sync_table, ys_table, ids.data_ptr(), w.data_ptr(), pos.data_ptr(),
+                                      offsets.data_ptr(), dst_base.data_ptr(), rank, world, tokens, top_k,
+                                      cap_rows, out.data_ptr(), _torch_stream()))
 
     def combine(self, ys, ids, w, pos, out) -> None:
         tokens, top_k = ids.shape

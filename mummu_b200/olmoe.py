@@ -205,6 +205,12 @@ class OlmoeDecoder:
         x = self._rms(x[:, -1], self.final_norm)
         return F.linear(x, self.lm_head).float()
 
+    def decode_step(self, ids, past: int):
+        """One shape-static decode step, eagerly: ids [B, 1] int64 at position `past` for every
+        sequence; logits [B, vocab].  The same code a captured step replays."""
+        pos = self.torch.tensor([past], device=self.dev)
+        return self._decode_static(ids, pos)
+
     def make_decode_graph(self, B: int):
         """Captures one decode step for batch B; returns (graph, ids_buf, pos_buf, logits_buf)."""
         t_ = self.torch

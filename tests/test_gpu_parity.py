@@ -269,23 +269,6 @@ def test_q4k_decode_olmoe_shape(M, cuda_lib, olmoe_q4k_layer, T):
     m.close()
 
 
-@pytest.mark.parametrize("T", [9, 64])
-def test_q4k_decode_tensor_core_variant(M, cuda_lib, olmoe_q4k_layer, T, monkeypatch):
-    """The opt-in tcgen05 variant of the decode bank (weights expanded into TMEM, accumulators in
-    TMEM) against the oracle and against the default kernels."""
-    L = cuda_lib
-    H, I, E, K, router, (gq, uq, dq), xh = olmoe_q4k_layer
-    m = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, gq, uq, dq)
-    base = m.forward(xh[:T], K, False).astype(np.float32)
-    monkeypatch.setenv("MUMMU_CUDA_DECODE_UMMA", "1")
-    y = m.forward(xh[:T], K, False).astype(np.float32)
-    monkeypatch.delenv("MUMMU_CUDA_DECODE_UMMA")
-    want, _, _ = O.moe_forward(xh[:T].astype(np.float32), router, gq, uq, dq, K, False, q4k=True)
-    assert rel_err(y, want) < TOL_16
-    assert rel_err(y, base) < TOL_16        # same exact products, different summation grouping
-    m.close()
-
-
 def test_q4k_decode_olmoe_shape_crowded_experts(M, cuda_lib, olmoe_q4k_layer):
     """Every token on the same experts: 64 rows per expert = four passes of the 16-token tile."""
     L = cuda_lib
@@ -512,8 +495,10 @@ def test_tensor_core_layer_against_oracle(M, cuda_lib, act, T, H, I, E, K):
 
 def test_tensor_core_prefill_config_shape(M, cuda_lib):
     """The prefill configuration's shape (T=4096, hidden 2048, 64 experts, top-8, intermediate 1024,
-    bf16, Zipf-skewed router bias): tensor-core path against the SIMT path of the same library on
-    the same inputs, routing against the oracle, and per-token position independence."""
+    bf16, Zipf-skewed router bias).  Routing of every token against the oracle, bit for bit; layer
+    outputs of a sample of tokens against the oracle (tokens are independent, so 40 rows of y cost
+    the oracle seconds): tokens of the hottest and of the coldest expert, the first and last rows,
+    a row present at two positions; and the whole output against the SIMT path of the library."""
     import torch
     L = cuda_lib
     H, I, E, K, T = 2048, 1024, 64, 8, 4096
@@ -523,13 +508,16 @@ def test_tensor_core_prefill_config_shape(M, cuda_lib):
     bias = synth.zipf_router_bias(E, alpha=1.0)
     m = M.SparseMoeConfig(H, I, E, K).init(act_dtype=L.BF16, weight_dtype=L.BF16, max_tokens=T)
     m.set_router(router, bias=bias)
-    m.set_bank(L.BANK_GATE, rnd(E, I, H).to(torch.bfloat16))
-    m.set_bank(L.BANK_UP, rnd(E, I, H).to(torch.bfloat16))
-    m.set_bank(L.BANK_DOWN, rnd(E, H, I).to(torch.bfloat16))
+    banks = [rnd(E, I, H).to(torch.bfloat16), rnd(E, I, H).to(torch.bfloat16), rnd(E, H, I).to(torch.bfloat16)]
+    m.set_banks(*banks)
     x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
     x[7] = x[3000]                                   # same row at two positions
     y = m.forward(x, K, False)
     m.sync()
+    m.set_profiling(True)
+    m.forward(x, K, False)
+    assert {"tc_gate_up", "tc_down"} <= set(m.take_profile())      # the tensor-core path ran
+    m.set_profiling(False)
     ids, w = m.route_flat(x, K, False)
     xf = x.float().cpu().numpy()
     oid, ow = O.route(O.router_logits(xf, router, bias), K, False)
@@ -538,12 +526,20 @@ def test_tensor_core_prefill_config_shape(M, cuda_lib):
     load = np.bincount(oid.reshape(-1), minlength=E)
     assert load.max() > 3 * load.mean()              # skewed: ragged, many-tile segments
     assert torch.equal(y[7], y[3000])
-    os.environ["MUMMU_CUDA_NO_TC"] = "1"
-    try:
-        y_simt = m.forward(x, K, False)
-        m.sync()
-    finally:
-        del os.environ["MUMMU_CUDA_NO_TC"]
+    # sampled rows against the oracle
+    hot, cold = int(load.argmax()), int(np.where(load > 0, load, load.max() + 1).argmin())
+    rows_of = lambda e: np.nonzero((oid == e).any(1))[0]
+    pick = sorted(set([0, 1, 7, 3000, T - 1] + rows_of(hot)[[0, len(rows_of(hot)) // 2, -1]].tolist()
+                      + rows_of(cold)[:3].tolist() + list(range(100, 4000, 150))))
+    gate, up, down = (b.float().cpu().numpy() for b in banks)
+    want, _, _ = O.moe_forward(xf[pick], router, gate, up, down, K, False, bias=bias)
+    got = y[pick].float().cpu().numpy()
+    assert rel_err(got, want) < TOL_16
+    assert len(pick) >= 32
+    m.set_switch("NO_TC", 1)
+    y_simt = m.forward(x, K, False)
+    m.sync()
+    m.set_switch("NO_TC", 0)
     err = (y.float() - y_simt.float()).abs().max().item() / y_simt.float().abs().max().item()
     assert err < TOL_16
     m.close()

@@ -91,3 +91,63 @@ def test_gpu_decoder_matches_restatement(cuda_lib, q4):
     b = dec.greedy_generate(ids, 4)
     assert torch.equal(a, b) and a.shape == (2, 4)
     dec.close()
+
+
+def full_state(torch, moe_mod, cfg, seed=21):
+    """Random weights of the full-model configuration, drawn on the device (seeded) and handed to
+    both sides as the same values: the trunk as the f16 values it will hold, the experts as the
+    Q4_K bytes of our encoder."""
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    rnd = lambda *s, std=0.02: torch.randn(*s, generator=gen, device="cuda") * std
+    h16 = lambda t: t.to(torch.float16).float().cpu().numpy()
+    H, I, E, V = cfg.hidden_size, cfg.intermediate_size, cfg.num_experts, cfg.vocab_size
+    st = dict(embed=h16(rnd(V, H, std=0.5)), lm_head=h16(rnd(V, H)), norm=(1 + rnd(H, std=0.05)).cpu().numpy())
+    for l in range(cfg.num_hidden_layers):
+        for name in ("q", "k", "v", "o"):
+            st[f"l{l}.{name}"] = h16(rnd(H, H))
+        for name in ("in_norm", "post_norm", "q_norm", "k_norm"):
+            st[f"l{l}.{name}"] = (1 + rnd(H, std=0.05)).cpu().numpy()
+        st[f"l{l}.router"] = rnd(H, E).cpu().numpy()
+        for name, shape in (("gate", (E, I, H)), ("up", (E, I, H)), ("down", (E, H, I))):
+            st[f"l{l}.{name}"] = moe_mod.q4k_quantize_device(rnd(*shape)).cpu().numpy()
+    return st
+
+
+@pytest.mark.gpu
+def test_gpu_decoder_full_model_shape(cuda_lib):
+    """The full-model configuration at its own shape: 16 layers, hidden 2048, 16 heads x 128, 64
+    experts top-8, intermediate 1024, vocabulary 50304, Q4_K experts, f16 trunk.  An 8-token prompt
+    and three teacher-forced decode steps, batch 1 and batch 2, logits against the CPU restatement
+    at 2e-2; the greedy token must agree wherever the restatement's top-1 / top-2 gap is clear of
+    the tolerance (either token is accepted inside it, and the restatement's token is fed to both
+    so that the sequences stay aligned)."""
+    import torch
+    from mummu_b200 import _lib as L, moe as moe_mod
+    from mummu_b200.olmoe import OlmoeDecoder
+    from oracle.olmoe_ref import RefOlmoe
+    cfg = OlmoeConfig()
+    st = full_state(torch, moe_mod, cfg)
+    rng = np.random.default_rng(4)
+    prompts = rng.integers(0, cfg.vocab_size, size=(2, 8)).tolist()
+    for B in (1, 2):
+        dec = OlmoeDecoder(cfg, device=0, expert_dtype=L.Q4_K, max_batch=B, max_ctx=16)
+        dec.load_state(st)
+        ids = torch.tensor(prompts[:B], device="cuda")
+        logits = dec.forward(ids, 0)
+        refs = [RefOlmoe(cfg, st, True) for _ in range(B)]
+        want = np.stack([r.forward(p, 0) for r, p in zip(refs, prompts[:B])])
+        assert np.abs(logits.cpu().numpy() - want).max() / np.abs(want).max() < 2e-2
+        past = 8
+        for _ in range(3):
+            nxt = want.argmax(-1)
+            logits = dec.decode_step(torch.tensor(nxt, device="cuda")[:, None], past)
+            want = np.stack([r.forward([int(t)], past) for r, t in zip(refs, nxt)])
+            scale = np.abs(want).max()
+            assert np.abs(logits.cpu().numpy() - want).max() / scale < 2e-2
+            top2 = np.sort(want, -1)[:, -2:]
+            clear = (top2[:, 1] - top2[:, 0]) > 2 * 2e-2 * scale
+            assert (logits.argmax(-1).cpu().numpy()[clear] == want.argmax(-1)[clear]).all()
+            past += 1
+        dec.close()
+        del dec
+        torch.cuda.empty_cache()

@@ -64,3 +64,22 @@ def test_noalloc_router_refuses_sizes_beyond_its_fixed_scratch(cuda_lib):
     rc = L.lib.mummu_moe_route_noalloc(x.data_ptr(), L.F32, wd.data_ptr(), None, 8, 64, 16, 17, 0,
                                        ids.data_ptr(), w.data_ptr(), 0, None)
     assert rc == L.ERR_CONTRACT and "top_k" in L.last_error()
+
+
+def test_noalloc_router_refuses_a_misaligned_weight_pointer(cuda_lib):
+    """A router weight that starts in the middle of a packed buffer (4-byte but not 16-byte
+    aligned) is refused on the host: the kernel would read it in 128-bit words.  Only the host-side
+    check runs here; nothing is launched with the bad pointer."""
+    import torch
+    L = cuda_lib
+    x = torch.zeros(8, 64, device="cuda")
+    packed = torch.zeros(64 * 16 + 4, device="cuda")
+    ids = torch.zeros(8, 2, dtype=torch.int32, device="cuda")
+    w = torch.zeros(8, 2, device="cuda")
+    rc = L.lib.mummu_moe_route_noalloc(x.data_ptr(), L.F32, packed.data_ptr() + 4, None, 8, 64, 16, 2, 0,
+                                       ids.data_ptr(), w.data_ptr(), 0, None)
+    assert rc == L.ERR_CONTRACT and "16-byte aligned" in L.last_error()
+    rc = L.lib.mummu_moe_route_noalloc(x.data_ptr(), L.F32, packed.data_ptr(), None, 8, 64, 16, 2, 0,
+                                       ids.data_ptr(), w.data_ptr(), 0, None)
+    assert rc == L.OK, L.last_error()
+    torch.cuda.synchronize()

@@ -569,7 +569,7 @@ def run_ep(args, rank: int, world: int, local_rank: int, shape: dict):
     # captured graph that held NCCL kernels kept the process group from shutting down, so the NCCL
     # exchange stays eager)
     run, graphed = step, False
-    device_sync = world > 1 and ws is not None and all(getattr(m, "device_sync", False) for m, _ in layers)
+    device_sync = world > 1 and ws is not None
     if q4 and (world == 1 or device_sync) and not os.environ.get("MUMMU_NO_GRAPH"):
         try:
             torch.cuda.synchronize()

@@ -91,6 +91,8 @@ static void free_scratch(MummuMoe* m) {
         m->logits = nullptr; m->tile_done = nullptr; m->ids = nullptr; m->wts = nullptr;
         m->row_token = nullptr; m->pos = nullptr; m->xs = nullptr; m->hact = nullptr; m->ys = nullptr;
         m->io_x = nullptr; m->io_y = nullptr;
+        m->xt = m->xsum = m->ht = nullptr;
+        m->tile_base = m->item_gu = m->item_dn = m->work = nullptr;
         m->cap_tokens = 0;
         m->scratch_borrowed = false;
         return;
@@ -98,6 +100,10 @@ static void free_scratch(MummuMoe* m) {
     cudaFree(m->logits); cudaFree(m->tile_done); cudaFree(m->ids); cudaFree(m->wts);
     cudaFree(m->row_token); cudaFree(m->pos); cudaFree(m->xs); cudaFree(m->hact); cudaFree(m->ys);
     cudaFree(m->io_x); cudaFree(m->io_y);
+    cudaFree(m->xt); cudaFree(m->xsum); cudaFree(m->ht);
+    cudaFree(m->tile_base); cudaFree(m->item_gu); cudaFree(m->item_dn); cudaFree(m->work);
+    m->xt = m->xsum = m->ht = nullptr;
+    m->tile_base = m->item_gu = m->item_dn = m->work = nullptr;
     m->logits = nullptr; m->tile_done = nullptr; m->ids = nullptr; m->wts = nullptr;
     m->row_token = nullptr; m->pos = nullptr; m->xs = nullptr; m->hact = nullptr; m->ys = nullptr;
     m->io_x = nullptr; m->io_y = nullptr;
@@ -139,6 +145,18 @@ int ensure_scratch(MummuMoe* m, int64_t tokens) {
     if ((rc = dev_alloc((float**)&m->ys, (size_t)rows * c.hidden))) return rc;
     if ((rc = dev_alloc((uint8_t**)&m->io_x, (size_t)T * c.hidden * act))) return rc;
     if ((rc = dev_alloc((uint8_t**)&m->io_y, (size_t)T * c.hidden * act))) return rc;
+    if (c.weight_dtype == MUMMU_Q4_K && c.act_dtype == MUMMU_F16 && c.hidden % 256 == 0 && c.inter % 256 == 0 &&
+        rows <= 8192) {
+        // token tiles of the streaming decode kernels: 8 rows each, every expert rounded up
+        const size_t tiles = (size_t)rows / 8 + (size_t)c.experts_local + 1;
+        if ((rc = dev_alloc((uint8_t**)&m->xt, tiles * (c.hidden / 256) * 4096))) return rc;
+        if ((rc = dev_alloc((uint8_t**)&m->xsum, tiles * (c.hidden / 256) * 128))) return rc;
+        if ((rc = dev_alloc((uint8_t**)&m->ht, tiles * (c.inter / 256) * 4096))) return rc;
+        if ((rc = dev_alloc(&m->tile_base, (size_t)c.experts_local))) return rc;
+        if ((rc = dev_alloc(&m->item_gu, (size_t)c.experts_local + 1))) return rc;
+        if ((rc = dev_alloc(&m->item_dn, (size_t)c.experts_local + 1))) return rc;
+        if ((rc = dev_alloc(&m->work, 2))) return rc;
+    }
     m->cap_tokens = T;
     return MUMMU_OK;
 }
@@ -159,6 +177,7 @@ static const SwitchName kSwitches[] = {
     {"ROUTER_PLAIN", &MummuSwitches::router_plain},
     {"DECODE_NO_PDL", &MummuSwitches::decode_no_pdl},
     {"DECODE_NT", &MummuSwitches::decode_nt},
+    {"DECODE_OLD_STREAM", &MummuSwitches::decode_old_stream},
     {"DECODE_STREAM_MIN", &MummuSwitches::decode_stream_min},
     {"DECODE_RB_GATEUP", &MummuSwitches::decode_rb_gateup},
     {"DECODE_RB_DOWN", &MummuSwitches::decode_rb_down},
@@ -420,7 +439,9 @@ int32_t mummu_moe_set_bank(MummuMoe* m, int32_t which, const void* data, size_t 
     // caller queued on its own streams is the caller's to finish first (said in the header).
     MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
     if (on_device) {
-        // a device-to-device cudaMemcpy may return before the copy has run
+        // the source may still be being written on whatever stream the caller used, and a
+        // device-to-device cudaMemcpy may return before the copy has run: wait on both sides
+        MUMMU_CUDA_TRY(cudaDeviceSynchronize());
         MUMMU_CUDA_TRY(cudaMemcpyAsync(m->bank[which], data, bytes, cudaMemcpyDeviceToDevice, m->stream));
         MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
     } else {
@@ -691,6 +712,8 @@ int32_t mummu_moe_adopt_scratch(MummuMoe* m, MummuMoe* donor) {
     m->logits = donor->logits; m->tile_done = donor->tile_done; m->ids = donor->ids; m->wts = donor->wts;
     m->row_token = donor->row_token; m->pos = donor->pos; m->xs = donor->xs; m->hact = donor->hact;
     m->ys = donor->ys; m->io_x = donor->io_x; m->io_y = donor->io_y;
+    m->xt = donor->xt; m->xsum = donor->xsum; m->ht = donor->ht; m->tile_base = donor->tile_base;
+    m->item_gu = donor->item_gu; m->item_dn = donor->item_dn; m->work = donor->work;
     m->cap_tokens = donor->cap_tokens;
     m->scratch_borrowed = true;
     return MUMMU_OK;

@@ -170,6 +170,25 @@ int32_t mummu_moe_combine(MummuMoe* moe, const void* ys, const int32_t* ids, con
  * `rows` f32 rows from host memory, f32 rows back to host memory. */
 int32_t mummu_expert_run(MummuMoe* moe, int32_t expert, const float* x, int32_t rows, float* y);
 
+/* `ExpertExec::run_tensor` / `run_tensor_resident` (nn/moe.rs:366-412): the same expert on `rows`
+ * DEVICE rows of act_dtype, result left on the device, queued on `stream` without waiting (the
+ * caller moves or reads it later, batched with every other partial, nn/moe.rs:358-367). */
+int32_t mummu_expert_run_device(MummuMoe* moe, int32_t expert, const void* x, int32_t rows, void* y,
+                                void* stream);
+
+/* `ExpertExec::gate_energy` (nn/moe.rs:413-418): per row, the sum over the expert's intermediate
+ * columns of silu(x . gate_row)^2; x and energy are HOST f32 arrays ([rows, hidden] and [rows]). */
+int32_t mummu_expert_gate_energy(MummuMoe* moe, int32_t expert, const float* x, int32_t rows,
+                                 float* energy);
+
+/* `ExpertExec::resident_bytes` (nn/moe.rs:351-352): bytes one expert's gate, up and down weights
+ * hold on the device (0 for a bad argument). */
+uint64_t mummu_expert_resident_bytes(const MummuMoe* moe, int32_t expert);
+
+/* The configuration a handle was created with: device and weight dtype are what
+ * `ExpertExec::tier` (nn/moe.rs:349-350) reports as the expert's (device, precision). */
+int32_t mummu_moe_get_config(const MummuMoe* moe, MummuMoeConfig* out);
+
 /* -------- expert parallelism over peer memory (no counterpart in the reference: its devices
  * exchange through host memory, backend.rs:128-143, nn/moe.rs:1219-1272) ----------------------- */
 
@@ -298,6 +317,75 @@ int32_t mummu_moe_route_noalloc(const void* x, int32_t act_dtype, const float* r
                                 const float* bias, int32_t tokens, int32_t hidden,
                                 int32_t experts, int32_t top_k, int32_t norm_topk_prob,
                                 int32_t* ids_out, float* w_out, int32_t device, void* stream);
+
+/* -------- decode trunk: what a token passes between two expert banks ------------------------ */
+
+/* The fixed-shape decode step of the OLMoE decoder around the expert bank, for `slots` independent
+ * sequences with one new token each: the arithmetic of `LoadedOlmoe::forward` (models/olmoe.rs:
+ * 522-587) and `Attention` (nn/attention.rs:182-295: RMSNorm of q and k over the whole projection
+ * :196-200, f32 scores :275-289, the -1e4 causal mask :28-48; RoPE nn/rope.rs:21-105) laid out as
+ * `StaticDecode::forward_static` wants it (capture.rs:48-107, nn/static_kv.rs:36-72): a
+ * preallocated cache [slots, kv_heads, max_ctx, head_dim] per layer written in place at each
+ * slot's position, positions read on the device, nothing uploaded inside a step - so a step can be
+ * captured.  f16 weights and activations, f32 norms, f32 accumulation. */
+typedef struct MummuTrunk MummuTrunk;
+
+typedef struct {
+    int32_t device;
+    int32_t hidden;
+    int32_t heads;
+    int32_t kv_heads;
+    int32_t head_dim;
+    int32_t layers;
+    int32_t vocab;
+    int32_t slots;           /* sequences decoded per step (`StaticKvConfig::slots`), 1..=64 */
+    int32_t max_ctx;         /* positions each slot can hold                                  */
+    float rope_theta;
+    float rms_eps;
+} MummuTrunkConfig;
+
+#define MUMMU_TRUNK_EMBED      0   /* [vocab, hidden] f16            */
+#define MUMMU_TRUNK_LM_HEAD    1   /* [vocab, hidden] f16            */
+#define MUMMU_TRUNK_FINAL_NORM 2   /* [hidden] f32                   */
+#define MUMMU_TRUNK_IN_NORM    3   /* per layer from here: [hidden] f32 */
+#define MUMMU_TRUNK_POST_NORM  4
+#define MUMMU_TRUNK_Q          5   /* [heads*head_dim, hidden] f16   */
+#define MUMMU_TRUNK_K          6   /* [kv_heads*head_dim, hidden]    */
+#define MUMMU_TRUNK_V          7
+#define MUMMU_TRUNK_O          8   /* [hidden, heads*head_dim] f16   */
+#define MUMMU_TRUNK_Q_NORM     9   /* [heads*head_dim] f32           */
+#define MUMMU_TRUNK_K_NORM     10  /* [kv_heads*head_dim] f32        */
+
+/* `StaticDecode::static_bytes` (capture.rs:77-79): bytes of the cache a state of this shape holds. */
+uint64_t mummu_trunk_static_bytes(const MummuTrunkConfig* cfg);
+/* Weights, the zeroed cache (`StaticDecode::static_state`, capture.rs:81-83) and RoPE tables. */
+int32_t mummu_trunk_create(const MummuTrunkConfig* cfg, MummuTrunk** out);
+int32_t mummu_trunk_destroy(MummuTrunk* trunk);
+/* One weight (MUMMU_TRUNK_*), row-major as the checkpoint stores `Linear` weights [out, in]
+ * (models/olmoe.rs:319-349); `layer` is ignored for the first three.  Copied. */
+int32_t mummu_trunk_set_weight(MummuTrunk* trunk, int32_t which, int32_t layer, const void* data,
+                               size_t bytes, int32_t on_device);
+/* x[slot] = embedding of tokens[slot] (device int32) - models/olmoe.rs:550. */
+int32_t mummu_trunk_embed(MummuTrunk* trunk, const int32_t* tokens, int32_t slots, void* x,
+                          void* stream);
+/* One layer's attention half (models/olmoe.rs:561-566): h = rmsnorm(x); q, k, v; q/k norm; RoPE at
+ * positions[slot] (device int32); k, v stored at that position; attention over the keys up to it
+ * inside the bucket of `key_len` keys; x += o-projection; h2 = rmsnorm(x) with the
+ * post-attention weight - the input of the layer's expert bank.  x: device f16 [slots, hidden],
+ * updated in place; h2: device f16 [slots, hidden]. */
+int32_t mummu_trunk_attention_step(MummuTrunk* trunk, int32_t layer, void* x, const int32_t* positions,
+                                   int32_t slots, int32_t key_len, void* h2, void* stream);
+/* x += y (the expert bank's output joins the residual stream, models/olmoe.rs:567-571). */
+int32_t mummu_trunk_add(MummuTrunk* trunk, void* x, const void* y, int32_t slots, void* stream);
+/* Final norm, lm_head and the greedy pick (models/olmoe.rs:573-585; decode.rs:33-48: the largest
+ * logit, ties to the lowest id).  logits: device f32 [slots, vocab]; argmax: device int32 [slots]
+ * or NULL. */
+int32_t mummu_trunk_head(MummuTrunk* trunk, const void* x, int32_t slots, float* logits,
+                         int32_t* argmax, void* stream);
+/* `StaticDecode::seed_static` (capture.rs:105-106): copy `count` prefilled positions of one slot,
+ * k and v as device f16 [kv_heads, count, head_dim], into the cache from position `first`. */
+int32_t mummu_trunk_kv_write(MummuTrunk* trunk, int32_t layer, int32_t slot, int32_t first,
+                             int32_t count, const void* k, const void* v, void* stream);
 
 const char* mummu_cuda_last_error(void);
 const char* mummu_cuda_version(void);

@@ -27,6 +27,17 @@ class MummuMoeConfig(C.Structure):
     ]
 
 
+class MummuTrunkConfig(C.Structure):
+    _fields_ = [
+        ("device", C.c_int32), ("hidden", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("layers", C.c_int32), ("vocab", C.c_int32), ("slots", C.c_int32),
+        ("max_ctx", C.c_int32), ("rope_theta", C.c_float), ("rms_eps", C.c_float),
+    ]
+
+
+(TRUNK_EMBED, TRUNK_LM_HEAD, TRUNK_FINAL_NORM, TRUNK_IN_NORM, TRUNK_POST_NORM, TRUNK_Q, TRUNK_K, TRUNK_V, TRUNK_O,
+ TRUNK_Q_NORM, TRUNK_K_NORM) = range(11)
+
 # name -> (restype, argtypes); every symbol include/mummu_cuda.h declares
 SYMBOLS = {
     "mummu_moe_create": (C.c_int32, [C.POINTER(MummuMoeConfig), C.POINTER(C.c_void_p)]),
@@ -65,6 +76,10 @@ SYMBOLS = {
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                      C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p]),
     "mummu_expert_run": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
+    "mummu_expert_run_device": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
+    "mummu_expert_gate_energy": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
+    "mummu_expert_resident_bytes": (C.c_uint64, [C.c_void_p, C.c_int32]),
+    "mummu_moe_get_config": (C.c_int32, [C.c_void_p, C.POINTER(MummuMoeConfig)]),
     "mummu_moe_dequant_bank": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "mummu_moe_take_hits": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "mummu_moe_sync": (C.c_int32, [C.c_void_p, C.c_void_p]),
@@ -77,6 +92,17 @@ SYMBOLS = {
     "mummu_moe_route_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
                                             C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                             C.c_void_p, C.c_int32, C.c_void_p]),
+    "mummu_trunk_static_bytes": (C.c_uint64, [C.POINTER(MummuTrunkConfig)]),
+    "mummu_trunk_create": (C.c_int32, [C.POINTER(MummuTrunkConfig), C.POINTER(C.c_void_p)]),
+    "mummu_trunk_destroy": (C.c_int32, [C.c_void_p]),
+    "mummu_trunk_set_weight": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_int32]),
+    "mummu_trunk_embed": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
+    "mummu_trunk_attention_step": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                               C.c_void_p, C.c_void_p]),
+    "mummu_trunk_add": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "mummu_trunk_head": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "mummu_trunk_kv_write": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                         C.c_void_p, C.c_void_p]),
     "mummu_cuda_last_error": (C.c_char_p, []),
     "mummu_cuda_version": (C.c_char_p, []),
 }

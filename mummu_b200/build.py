@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmummu_cuda.so")
-SOURCES = ["api.cu", "kernels_basic.cu", "decode_q4k.cu", "decode_stream.cu", "prefill_tc.cu", "ep.cu"]
+SOURCES = ["api.cu", "kernels_basic.cu", "decode_q4k.cu", "prefill_tc.cu", "trunk.cu", "ep.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

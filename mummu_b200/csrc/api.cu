@@ -91,8 +91,6 @@ static void free_scratch(MummuMoe* m) {
         m->logits = nullptr; m->tile_done = nullptr; m->ids = nullptr; m->wts = nullptr;
         m->row_token = nullptr; m->pos = nullptr; m->xs = nullptr; m->hact = nullptr; m->ys = nullptr;
         m->io_x = nullptr; m->io_y = nullptr;
-        m->xt = m->xsum = m->ht = nullptr;
-        m->tile_base = m->item_gu = m->item_dn = m->work = nullptr;
         m->cap_tokens = 0;
         m->scratch_borrowed = false;
         return;
@@ -100,10 +98,6 @@ static void free_scratch(MummuMoe* m) {
     cudaFree(m->logits); cudaFree(m->tile_done); cudaFree(m->ids); cudaFree(m->wts);
     cudaFree(m->row_token); cudaFree(m->pos); cudaFree(m->xs); cudaFree(m->hact); cudaFree(m->ys);
     cudaFree(m->io_x); cudaFree(m->io_y);
-    cudaFree(m->xt); cudaFree(m->xsum); cudaFree(m->ht);
-    cudaFree(m->tile_base); cudaFree(m->item_gu); cudaFree(m->item_dn); cudaFree(m->work);
-    m->xt = m->xsum = m->ht = nullptr;
-    m->tile_base = m->item_gu = m->item_dn = m->work = nullptr;
     m->logits = nullptr; m->tile_done = nullptr; m->ids = nullptr; m->wts = nullptr;
     m->row_token = nullptr; m->pos = nullptr; m->xs = nullptr; m->hact = nullptr; m->ys = nullptr;
     m->io_x = nullptr; m->io_y = nullptr;
@@ -145,18 +139,6 @@ int ensure_scratch(MummuMoe* m, int64_t tokens) {
     if ((rc = dev_alloc((float**)&m->ys, (size_t)rows * c.hidden))) return rc;
     if ((rc = dev_alloc((uint8_t**)&m->io_x, (size_t)T * c.hidden * act))) return rc;
     if ((rc = dev_alloc((uint8_t**)&m->io_y, (size_t)T * c.hidden * act))) return rc;
-    if (c.weight_dtype == MUMMU_Q4_K && c.act_dtype == MUMMU_F16 && c.hidden % 256 == 0 && c.inter % 256 == 0 &&
-        rows <= 8192) {
-        // token tiles of the streaming decode kernels: 8 rows each, every expert rounded up
-        const size_t tiles = (size_t)rows / 8 + (size_t)c.experts_local + 1;
-        if ((rc = dev_alloc((uint8_t**)&m->xt, tiles * (c.hidden / 256) * 4096))) return rc;
-        if ((rc = dev_alloc((uint8_t**)&m->xsum, tiles * (c.hidden / 256) * 128))) return rc;
-        if ((rc = dev_alloc((uint8_t**)&m->ht, tiles * (c.inter / 256) * 4096))) return rc;
-        if ((rc = dev_alloc(&m->tile_base, (size_t)c.experts_local))) return rc;
-        if ((rc = dev_alloc(&m->item_gu, (size_t)c.experts_local + 1))) return rc;
-        if ((rc = dev_alloc(&m->item_dn, (size_t)c.experts_local + 1))) return rc;
-        if ((rc = dev_alloc(&m->work, 2))) return rc;
-    }
     m->cap_tokens = T;
     return MUMMU_OK;
 }
@@ -177,7 +159,6 @@ static const SwitchName kSwitches[] = {
     {"ROUTER_PLAIN", &MummuSwitches::router_plain},
     {"DECODE_NO_PDL", &MummuSwitches::decode_no_pdl},
     {"DECODE_NT", &MummuSwitches::decode_nt},
-    {"DECODE_OLD_STREAM", &MummuSwitches::decode_old_stream},
     {"DECODE_STREAM_MIN", &MummuSwitches::decode_stream_min},
     {"DECODE_RB_GATEUP", &MummuSwitches::decode_rb_gateup},
     {"DECODE_RB_DOWN", &MummuSwitches::decode_rb_down},
@@ -361,7 +342,7 @@ int32_t mummu_moe_destroy(MummuMoe* m) {
         if (m->stream) cudaStreamSynchronize(m->stream);
         clear_host_graphs(m);
         free_scratch(m);
-        cudaFree(m->router_w); cudaFree(m->router_wt); cudaFree(m->router_bias);
+        cudaFree(m->router_w); cudaFree(m->router_wt); cudaFree(m->router_bias); cudaFree(m->ex_io);
         for (int b = 0; b < 3; ++b) cudaFree(m->bank[b]);
         cudaFree(m->counts); cudaFree(m->offsets); cudaFree(m->hits); cudaFree(m->status);
         if (m->status_host) cudaFreeHost(m->status_host);
@@ -619,37 +600,114 @@ int32_t mummu_moe_combine(MummuMoe* m, const void* ys, const int32_t* ids, const
     return launch_combine(m, ys, m->cfg.act_dtype, ids, w, pos, tokens, top_k, out, s);
 }
 
-int32_t mummu_expert_run(MummuMoe* m, int32_t expert, const float* x, int32_t rows, float* y) {
-    MUMMU_REQUIRE(m, "mummu_expert_run: null handle");
+// f32 staging of the one-expert calls: kept in the handle, grown when a larger call arrives
+static int ensure_ex_io(MummuMoe* m, size_t elems) {
+    if (elems <= m->ex_io_elems) return MUMMU_OK;
+    MUMMU_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    cudaFree(m->ex_io);
+    m->ex_io = nullptr;
+    m->ex_io_elems = 0;
+    int rc = dev_alloc(&m->ex_io, elems);
+    if (rc) return rc;
+    m->ex_io_elems = elems;
+    return MUMMU_OK;
+}
+
+// One expert over `rows` device rows of the activation dtype, through the same kernels a layer
+// call uses (tensor-core grouped GEMM, packed decode kernels, generic bank).
+static int expert_rows_device(MummuMoe* m, int expert, const void* xs, int rows, void* ys, cudaStream_t s) {
+    const MummuMoeConfig& c = m->cfg;
+    int rc;
+    if ((rc = launch_single_expert_plan(m, expert, rows, s))) return rc;
+    if (prefill_tc_supported(c, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !m->sw.no_tc)
+        return launch_experts_tc(m, xs, rows, m->counts, m->offsets, ys, c.act_dtype, s);
+    if (c.weight_dtype == MUMMU_Q4_K && c.act_dtype == MUMMU_F16 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 &&
+        rows <= 8192 && c.hidden <= 8192 && c.inter <= 8192) {
+        if ((rc = launch_decode_q4k_rows(m, xs, nullptr, m->counts, m->offsets, rows, (float*)m->ys, s))) return rc;
+        return launch_narrow((const float*)m->ys, ys, c.act_dtype, (int64_t)rows * c.hidden, s);
+    }
+    return launch_experts_simt(m, xs, c.act_dtype, nullptr, nullptr, nullptr, rows, rows, ys, c.act_dtype, expert, s);
+}
+
+static int expert_args(MummuMoe* m, int32_t expert, int32_t rows, const char* who) {
+    MUMMU_REQUIRE(m, "%s: null handle", who);
     MUMMU_REQUIRE(expert >= 0 && expert < m->cfg.experts_local, "expert %d out of range (%d)", expert,
                   m->cfg.experts_local);
-    MUMMU_REQUIRE(rows >= 0, "mummu_expert_run: negative row count %d", rows);
+    MUMMU_REQUIRE(rows >= 0, "%s: negative row count %d", who, rows);
+    return check_ready(m, false, true);
+}
+
+int32_t mummu_expert_run(MummuMoe* m, int32_t expert, const float* x, int32_t rows, float* y) {
     int rc;
-    if ((rc = check_ready(m, false, true))) return rc;
+    if ((rc = expert_args(m, expert, rows, "mummu_expert_run"))) return rc;
     if (rows == 0) return MUMMU_OK;
     MUMMU_REQUIRE(x && y, "mummu_expert_run: null pointer");
     std::lock_guard<std::mutex> lock(m->mu);
     DeviceGuard guard(m->cfg.device);
+    const MummuMoeConfig& c = m->cfg;
+    int64_t tokens_equiv = ((int64_t)rows + c.top_k - 1) / c.top_k;
+    if ((rc = ensure_scratch(m, tokens_equiv))) return rc;
+    const size_t n = (size_t)rows * c.hidden;
+    if ((rc = ensure_ex_io(m, 3 * n))) return rc;
+    cudaStream_t s = m->stream;
+    float *dx = m->ex_io, *dy = m->ex_io + n;
+    void* y_act = m->ex_io + 2 * n;          // the expert's output rows in the activation dtype
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(dx, x, n * sizeof(float), cudaMemcpyHostToDevice, s));
+    if (c.act_dtype == MUMMU_F32) {
+        // f32 handle: the generic bank takes the f32 rows as they are
+        if ((rc = launch_experts_simt(m, dx, MUMMU_F32, nullptr, nullptr, nullptr, rows, rows, dy, MUMMU_F32, expert, s)))
+            return rc;
+    } else {
+        // 16-bit handle: rows narrowed to the activation dtype (as the reference's DeviceExpert casts
+        // to its device's float type, nn/moe.rs:448-462), the layer's own kernels, widened back
+        if ((rc = launch_narrow(dx, m->xs, c.act_dtype, (int64_t)n, s))) return rc;
+        if ((rc = expert_rows_device(m, expert, m->xs, rows, y_act, s))) return rc;
+        if ((rc = launch_widen(y_act, c.act_dtype, dy, (int64_t)n, s))) return rc;
+    }
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(y, dy, n * sizeof(float), cudaMemcpyDeviceToHost, s));
+    return read_status(m, s);
+}
+
+int32_t mummu_expert_run_device(MummuMoe* m, int32_t expert, const void* x, int32_t rows, void* y, void* stream) {
+    int rc;
+    if ((rc = expert_args(m, expert, rows, "mummu_expert_run_device"))) return rc;
+    if (rows == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(x && y, "mummu_expert_run_device: null pointer");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
     int64_t tokens_equiv = ((int64_t)rows + m->cfg.top_k - 1) / m->cfg.top_k;
     if ((rc = ensure_scratch(m, tokens_equiv))) return rc;
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    return expert_rows_device(m, expert, x, rows, y, s);
+}
+
+int32_t mummu_expert_gate_energy(MummuMoe* m, int32_t expert, const float* x, int32_t rows, float* energy) {
+    int rc;
+    if ((rc = expert_args(m, expert, rows, "mummu_expert_gate_energy"))) return rc;
+    if (rows == 0) return MUMMU_OK;
+    MUMMU_REQUIRE(x && energy, "mummu_expert_gate_energy: null pointer");
+    std::lock_guard<std::mutex> lock(m->mu);
+    DeviceGuard guard(m->cfg.device);
+    const size_t n = (size_t)rows * m->cfg.hidden;
+    if ((rc = ensure_ex_io(m, n + (size_t)rows))) return rc;
     cudaStream_t s = m->stream;
-    float *dx = nullptr, *dy = nullptr;
-    size_t n = (size_t)rows * m->cfg.hidden;
-    if ((rc = dev_alloc(&dx, n))) return rc;
-    if ((rc = dev_alloc(&dy, n))) { cudaFree(dx); return rc; }
-    cudaError_t err = cudaMemcpyAsync(dx, x, n * sizeof(float), cudaMemcpyHostToDevice, s);
-    if (err == cudaSuccess) {
-        rc = launch_experts_simt(m, dx, MUMMU_F32, nullptr, nullptr, nullptr, rows, rows, dy, MUMMU_F32, expert, s);
-        if (!rc) err = cudaMemcpyAsync(y, dy, n * sizeof(float), cudaMemcpyDeviceToHost, s);
-    }
-    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
-    cudaFree(dx);
-    cudaFree(dy);
-    if (rc) return rc;
-    if (err != cudaSuccess) {
-        set_error("mummu_expert_run: %s", cudaGetErrorString(err));
-        return MUMMU_ERR_DEVICE;
-    }
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(m->ex_io, x, n * sizeof(float), cudaMemcpyHostToDevice, s));
+    if ((rc = launch_gate_energy(m, expert, m->ex_io, rows, m->ex_io + n, s))) return rc;
+    MUMMU_CUDA_TRY(cudaMemcpyAsync(energy, m->ex_io + n, (size_t)rows * sizeof(float), cudaMemcpyDeviceToHost, s));
+    MUMMU_CUDA_TRY(cudaStreamSynchronize(s));
+    return MUMMU_OK;
+}
+
+uint64_t mummu_expert_resident_bytes(const MummuMoe* m, int32_t expert) {
+    if (!m || expert < 0 || expert >= m->cfg.experts_local) return 0;
+    uint64_t total = 0;
+    for (int b = 0; b < 3; ++b) total += (uint64_t)(bank_total_bytes(m->cfg, b) / (size_t)m->cfg.experts_local);
+    return total;
+}
+
+int32_t mummu_moe_get_config(const MummuMoe* m, MummuMoeConfig* out) {
+    MUMMU_REQUIRE(m && out, "mummu_moe_get_config: null argument");
+    *out = m->cfg;
     return MUMMU_OK;
 }
 
@@ -712,8 +770,6 @@ int32_t mummu_moe_adopt_scratch(MummuMoe* m, MummuMoe* donor) {
     m->logits = donor->logits; m->tile_done = donor->tile_done; m->ids = donor->ids; m->wts = donor->wts;
     m->row_token = donor->row_token; m->pos = donor->pos; m->xs = donor->xs; m->hact = donor->hact;
     m->ys = donor->ys; m->io_x = donor->io_x; m->io_y = donor->io_y;
-    m->xt = donor->xt; m->xsum = donor->xsum; m->ht = donor->ht; m->tile_base = donor->tile_base;
-    m->item_gu = donor->item_gu; m->item_dn = donor->item_dn; m->work = donor->work;
     m->cap_tokens = donor->cap_tokens;
     m->scratch_borrowed = true;
     return MUMMU_OK;

@@ -176,7 +176,6 @@ struct MummuSwitches {
     int router_plain = 0;     // MUMMU_CUDA_ROUTER_PLAIN: decode router without the bulk-copied slice image
     int decode_no_pdl = 0;    // MUMMU_CUDA_DECODE_NO_PDL: no programmatic dependent launch of the down kernel
     int decode_nt = 0;        // MUMMU_CUDA_DECODE_NT: 1 forces one 8-token tile per pass
-    int decode_old_stream = 0;// MUMMU_CUDA_DECODE_OLD_STREAM: the per-CTA-staged streaming kernels
     int decode_stream_min = 0;// MUMMU_CUDA_DECODE_STREAM_MIN: row tiles from which the streaming variant runs
     int decode_rb_gateup = 0; // MUMMU_CUDA_DECODE_RB_GATEUP / _DOWN: row tiles per CTA (0 = planned)
     int decode_rb_down = 0;
@@ -218,21 +217,14 @@ struct MummuMoe {
     void* ys = nullptr;             // [tokens * k, hidden] f32
     void* io_x = nullptr;           // device staging for host-pointer calls
     void* io_y = nullptr;
+    float* ex_io = nullptr;         // f32 staging of the one-expert calls, grown on demand
+    size_t ex_io_elems = 0;
     unsigned long long* hits = nullptr;  // [experts]
     int32_t* status = nullptr;      // device status word
     int32_t* status_host = nullptr; // pinned landing place for reads of the status word
     // cached tensor maps (CUtensorMap, 128 B each) of the Q4_K banks as [rows, row_bytes] byte views
-    // slots 0-2: gate, up, down with a 16-row box; 3, 4: gate, up with an 8-row box
-    alignas(64) unsigned char q4k_map[5][128];
-    const void* q4k_map_base[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
-    // streaming Q4_K decode: the routed rows as MMA-fragment-ordered tiles of 8 rows
-    void* xt = nullptr;             // input tiles   [tiles][hidden/256][8][8][4] x 16 B
-    void* xsum = nullptr;           // their f16 sub-block sums [tiles][hidden/256][8][8]
-    void* ht = nullptr;             // SwiGLU intermediate as tiles [tiles][inter/256][8][8][4] x 16 B
-    int32_t* tile_base = nullptr;   // [experts_local] first tile of each expert
-    int32_t* item_gu = nullptr;     // [experts_local + 1] work-item prefixes of the two expert kernels
-    int32_t* item_dn = nullptr;
-    int32_t* work = nullptr;        // [2] their item counters
+    alignas(64) unsigned char q4k_map[3][128];
+    const void* q4k_map_base[3] = {nullptr, nullptr, nullptr};
     int64_t launches = 0;
     mummu::Profiler prof;
     // host-pointer decode calls: the layer's launches captured once per (tokens, top_k, norm) and
@@ -288,6 +280,8 @@ int launch_experts_simt(MummuMoe* m, const void* x, int x_dtype, const int32_t* 
                         const int32_t* counts, const int32_t* offsets, int64_t max_rows_per_expert,
                         int64_t total_rows, void* ys, int ys_dtype, int expert_only,
                         cudaStream_t s);
+int launch_single_expert_plan(MummuMoe* m, int expert, int rows, cudaStream_t s);
+int launch_gate_energy(MummuMoe* m, int expert, const float* x, int rows, float* energy, cudaStream_t s);
 int launch_q4k_dequant(const void* src, float* dst, int64_t n_blocks, cudaStream_t s);
 int launch_q4k_quantize(const float* src, void* dst, int64_t n_blocks, cudaStream_t s);
 int launch_widen(const void* src, int dtype, float* dst, int64_t n, cudaStream_t s);
@@ -307,9 +301,4 @@ int launch_decode_q4k(MummuMoe* m, const void* x, int64_t tokens, int top_k, cud
 int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token, const int32_t* counts,
                            const int32_t* offsets, int64_t rows_total, float* ys, cudaStream_t s);
 int launch_narrow(const float* src, void* dst, int dtype, int64_t n, cudaStream_t s);
-// ---- decode_stream.cu ----
-bool decode_stream_supported(const MummuMoe* m);
-int launch_decode_stream(MummuMoe* m, const void* x, const int32_t* row_token, const int32_t* counts,
-                         const int32_t* offsets, int64_t rows_bound, float* ys, cudaStream_t s);
-
 }  // namespace mummu

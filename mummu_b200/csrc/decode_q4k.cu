@@ -487,8 +487,6 @@ int launch_decode_q4k_rows(MummuMoe* m, const void* x, const int32_t* row_token,
     g.n_rt = c.inter / 16;
     bool g_stream;
     plan(m->sw, g, experts_est, rows_total, nt2 ? 2 : 1, g_stream);
-    if (g_stream && !m->sw.decode_old_stream && decode_stream_supported(m))
-        return launch_decode_stream(m, x, row_token, counts, offsets, rows_total, ys, s);
     g.ld_out = c.inter;
     g.out = m->hact;
     g.rows_per_expert = c.inter;

@@ -1404,6 +1404,89 @@ int launch_widen(const void* src, int dtype, float* dst, int64_t n, cudaStream_t
 }
 
 // ---------------------------------------------------------------------------------------------
+// one expert on its own (ExpertExec::run and friends)
+// ---------------------------------------------------------------------------------------------
+// counts / offsets / work order for "`rows` rows, all of expert e"
+__global__ void single_expert_plan_kernel(int e, int rows, int E, int32_t* counts, int32_t* offsets, int32_t* active,
+                                          int32_t* n_active) {
+    for (int i = threadIdx.x; i <= E; i += blockDim.x) {
+        if (i < E) counts[i] = i == e ? rows : 0;
+        offsets[i] = i <= e ? 0 : rows;
+    }
+    if (threadIdx.x == 0) {
+        active[0] = e;
+        *n_active = rows > 0 ? 1 : 0;
+    }
+}
+
+int launch_single_expert_plan(MummuMoe* m, int expert, int rows, cudaStream_t s) {
+    LaunchScope scope(m, s, "expert_plan");
+    single_expert_plan_kernel<<<1, 256, 0, s>>>(expert, rows, m->cfg.experts_local, m->counts, m->offsets, m->active,
+                                                m->n_active);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+// energy[row] = sum over the expert's intermediate columns n of silu(x[row,:] . gate[n,:])^2
+// (ExpertExec::gate_energy, nn/moe.rs:413-418).  One block per row; the columns are summed in a
+// fixed order (a thread's columns ascending, then a tree over the threads), so the result does not
+// depend on scheduling.
+template <typename TW>
+__global__ void __launch_bounds__(256) gate_energy_kernel(const float* x, const uint8_t* gate, size_t row_bytes, int H,
+                                                          int I, float* energy) {
+    extern __shared__ float s_x[];
+    __shared__ float s_part[256];
+    const int row = blockIdx.x;
+    for (int k = threadIdx.x; k < H; k += blockDim.x) s_x[k] = x[(size_t)row * H + k];
+    __syncthreads();
+    float acc = 0.0f;
+    for (int n = threadIdx.x; n < I; n += blockDim.x) {
+        const uint8_t* wrow = gate + (size_t)n * row_bytes;
+        float d = 0.0f;
+        for (int k = 0; k < H; ++k) d = fmaf(s_x[k], load_w<TW>(wrow, k), d);
+        const float a = silu_f(d);
+        acc += a * a;
+    }
+    s_part[threadIdx.x] = acc;
+    __syncthreads();
+    for (int off = 128; off > 0; off >>= 1) {
+        if ((int)threadIdx.x < off) s_part[threadIdx.x] += s_part[threadIdx.x + off];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) energy[row] = s_part[0];
+}
+
+int launch_gate_energy(MummuMoe* m, int expert, const float* x, int rows, float* energy, cudaStream_t s) {
+    const MummuMoeConfig& c = m->cfg;
+    const size_t row_bytes = bank_row_bytes(c, MUMMU_BANK_GATE);
+    const uint8_t* gate = (const uint8_t*)m->bank[MUMMU_BANK_GATE] + (size_t)expert * row_bytes * c.inter;
+    const size_t smem = (size_t)c.hidden * sizeof(float);
+    if (smem > 200 * 1024) {
+        set_error("gate_energy: hidden %d too wide", c.hidden);
+        return MUMMU_ERR_UNSUPPORTED;
+    }
+    LaunchScope scope(m, s, "gate_energy");
+#define MUMMU_GE(TW)                                                                          \
+    do {                                                                                      \
+        MUMMU_CUDA_TRY(allow_big_smem(gate_energy_kernel<TW>, c.device));                     \
+        gate_energy_kernel<TW><<<rows, 256, smem, s>>>(x, gate, row_bytes, c.hidden, c.inter, energy); \
+    } while (0)
+    switch (c.weight_dtype) {
+        case MUMMU_F32: MUMMU_GE(float); break;
+        case MUMMU_F16: MUMMU_GE(__half); break;
+        case MUMMU_BF16: MUMMU_GE(__nv_bfloat16); break;
+        case MUMMU_Q4_K: MUMMU_GE(q4k_t); break;
+        case MUMMU_Q8_0: MUMMU_GE(q80_t); break;
+        case MUMMU_Q5_K: MUMMU_GE(q5k_t); break;
+        case MUMMU_Q6_K: MUMMU_GE(q6k_t); break;
+        default: set_error("gate_energy: bad weight dtype %d", c.weight_dtype); return MUMMU_ERR_CONTRACT;
+    }
+#undef MUMMU_GE
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Router for callers that must not allocate (mummu_moe_route_noalloc)
 // ---------------------------------------------------------------------------------------------
 // The router kernel needs scratch beyond its inputs and outputs: the [tokens, experts] logits that

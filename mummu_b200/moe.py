@@ -348,12 +348,31 @@ class SparseMoe:
 SparseMoePerExpert = SparseMoe
 
 
+@dataclass
+class Tier:
+    """`tier::Tier` as far as this path uses it (nn/moe.rs:349-350): where an expert is resident and
+    at which stored precision."""
+    device: int
+    precision: int          # a weight dtype code of this library (F32 .. Q6_K)
+
+
 class CudaExpert:
-    """`ExpertExec` (nn/moe.rs:348-419) for one expert of a bank: `run(&[f32], rows, hidden)`."""
+    """`ExpertExec` (nn/moe.rs:348-419) for one expert of a bank on a B200: all ten methods.  The
+    expert is pinned to its device, so `stage`/`evict` are the trait's no-op defaults and
+    `is_staged` is always true; `disable_native` has nothing to switch off (there is no
+    dequantise-first fallback here)."""
 
     def __init__(self, moe: SparseMoe, expert: int):
         self.moe = moe
         self.expert = expert
+
+    def tier(self) -> Tier:
+        c = L.MummuMoeConfig()
+        _check(L.lib.mummu_moe_get_config(self.moe._h, C.byref(c)))
+        return Tier(device=c.device, precision=c.weight_dtype)
+
+    def resident_bytes(self) -> int:
+        return int(L.lib.mummu_expert_resident_bytes(self.moe._h, self.expert))
 
     def run(self, x: np.ndarray, rows: int, hidden: int) -> np.ndarray:
         if hidden != self.moe.cfg.hidden_size:
@@ -365,11 +384,41 @@ class CudaExpert:
         _check(L.lib.mummu_expert_run(self.moe._h, self.expert, x.ctypes.data, rows, y.ctypes.data))
         return y
 
-    def resident_bytes(self) -> int:
-        c = self.moe.cfg
-        per = {L.F32: 4.0, L.F16: 2.0, L.BF16: 2.0, L.Q4_K: 144.0 / 256.0, L.Q8_0: 34.0 / 32.0,
-               L.Q5_K: 176.0 / 256.0, L.Q6_K: 210.0 / 256.0}[self.moe.weight_dtype]
-        return int(3 * c.hidden_size * c.expert_intermediate_size * per)
+    def run_tensor(self, x):
+        """[rows, hidden] torch CUDA tensor of the layer's activation dtype -> the same, no host
+        round trip (nn/moe.rs:399-412)."""
+        import torch
+        assert x.is_cuda and _torch_dtype_code(x) == self.moe.act_dtype and x.shape[1] == self.moe.cfg.hidden_size
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        _check(L.lib.mummu_expert_run_device(self.moe._h, self.expert, xc.data_ptr(), xc.shape[0], y.data_ptr(),
+                                             _torch_stream()))
+        return y
+
+    def run_tensor_resident(self, x):
+        """The result stays on the expert's device and nothing waits (nn/moe.rs:358-367): here the
+        same call, since `run_tensor` already returns without synchronising."""
+        return self.run_tensor(x)
+
+    def gate_energy(self, x: np.ndarray, rows: int, hidden: int) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+        if hidden != self.moe.cfg.hidden_size or x.size != rows * hidden:
+            raise MoeContractError(f"gate_energy input holds {x.size} values, wants {rows} x {self.moe.cfg.hidden_size}")
+        out = np.empty(rows, dtype=np.float32)
+        _check(L.lib.mummu_expert_gate_energy(self.moe._h, self.expert, x.ctypes.data, rows, out.ctypes.data))
+        return out
+
+    def disable_native(self) -> None:
+        pass
+
+    def stage(self, device=None) -> None:
+        pass
+
+    def evict(self) -> None:
+        pass
+
+    def is_staged(self) -> bool:
+        return True
 
 
 def q4k_quantize_device(src):

@@ -556,3 +556,13 @@ int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* The benchmark's reference arm sizes the pool itself: a launcher may have exported
+ * OMP_NUM_THREADS=1 for every rank. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

@@ -69,6 +69,8 @@ def lib() -> C.CDLL:
                                          C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_int, C.c_void_p]
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_num_threads.restype = None
+        L.orc_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -83,6 +85,11 @@ def _p(a: np.ndarray) -> C.c_void_p:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """Size the OpenMP pool (a launcher may have exported OMP_NUM_THREADS=1 for its ranks)."""
+    lib().orc_set_num_threads(int(n))
 
 
 def exp(x) -> np.ndarray:

@@ -43,3 +43,18 @@ def test_null_handle_is_refused_not_crashed(cuda_lib):
     assert rc == cuda_lib.ERR_CONTRACT
     assert "null" in cuda_lib.last_error()
     assert cuda_lib.lib.mummu_moe_destroy(None) == cuda_lib.OK
+
+
+def test_rust_crate_binds_every_declared_symbol_and_builds_every_source():
+    """crates/mummu-cuda is not compiled on this image (no Rust toolchain), so it is kept in step
+    by text: its `extern "C"` block names exactly the header's functions, and its build script
+    compiles exactly the sources the Python build compiles."""
+    from mummu_b200 import build
+    lib_rs = open(os.path.join(ROOT, "crates", "mummu-cuda", "src", "lib.rs")).read()
+    block = lib_rs[lib_rs.index('extern "C" {'):]
+    block = block[:block.index("\n    }\n")]
+    bound = sorted(set(re.findall(r"pub fn (mummu_[a-z0-9_]+)\s*\(", block)))
+    assert bound == header_symbols()
+    build_rs = open(os.path.join(ROOT, "crates", "mummu-cuda", "build.rs")).read()
+    listed = re.findall(r'"([a-z0-9_]+\.cu)"', build_rs[build_rs.index("const SOURCES"):build_rs.index("];")])
+    assert sorted(listed) == sorted(build.SOURCES)

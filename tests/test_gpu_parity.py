@@ -543,3 +543,55 @@ def test_tensor_core_prefill_config_shape(M, cuda_lib):
     err = (y.float() - y_simt.float()).abs().max().item() / y_simt.float().abs().max().item()
     assert err < TOL_16
     m.close()
+
+
+# ---- ExpertExec: one expert on its own -----------------------------------------------------------
+
+@pytest.mark.parametrize("kind", ["f32", "bf16", "q4k"])
+def test_expert_exec_methods(M, cuda_lib, kind):
+    """`ExpertExec` (nn/moe.rs:348-419): run (host f32 rows), run_tensor / run_tensor_resident (device
+    rows), gate_energy, resident_bytes, tier, and the pinned-executor defaults."""
+    import torch
+    L = cuda_lib
+    H, I, E, K, rows = 512, 256, 6, 2, 21
+    router, gate, up, down, x = synth.moe_layer(H, I, E, rows, cfg_seed=33)
+    if kind == "f32":
+        act, wdt, banks, per = L.F32, L.F32, (gate, up, down), 4.0
+        deq = (gate, up, down)
+        tdt = torch.float32
+    elif kind == "bf16":
+        act, wdt = L.BF16, L.BF16
+        banks = tuple(bf16_bits(b) for b in (gate, up, down))
+        deq = tuple(bf16_to_f32(b) for b in banks)
+        per, tdt = 2.0, torch.bfloat16
+    else:
+        act, wdt = L.F16, L.Q4_K
+        banks = tuple(q4k.quantize(b) for b in (gate, up, down))
+        deq = (O.dequant_q4_k(banks[0]).reshape(E, I, H), O.dequant_q4_k(banks[1]).reshape(E, I, H),
+               O.dequant_q4_k(banks[2]).reshape(E, H, I))
+        per, tdt = 144.0 / 256.0, torch.float16
+    m = make_layer(M, L, H, I, E, K, act, wdt, router, *banks)
+    e = 4
+    ex = M.CudaExpert(m, e)
+    xin = x if kind == "f32" else (bf16_to_f32(bf16_bits(x)) if kind == "bf16" else x.astype(np.float16).astype(np.float32))
+    want = O.expert_ffn(deq[0][e], deq[1][e], deq[2][e], xin)
+    tol = TOL_F32 if kind == "f32" else TOL_16
+    got = ex.run(xin.reshape(-1), rows, H).reshape(rows, H)
+    assert rel_err(got, want) < tol
+    assert np.array_equal(got, ex.run(xin.reshape(-1), rows, H).reshape(rows, H))     # staging is reused
+    xd = torch.from_numpy(xin).cuda().to(tdt)
+    yd = ex.run_tensor(xd)
+    yr = ex.run_tensor_resident(xd)
+    torch.cuda.synchronize()
+    assert rel_err(yd.float().cpu().numpy(), want) < tol and torch.equal(yd, yr)
+    energy = ex.gate_energy(xin.reshape(-1), rows, H)
+    g = xin.astype(np.float64) @ deq[0][e].astype(np.float64).T
+    ref_energy = ((g / (1.0 + np.exp(-g))) ** 2).sum(1)
+    assert np.abs(energy - ref_energy).max() / ref_energy.max() < 1e-4
+    assert ex.resident_bytes() == int(3 * H * I * per)
+    t = ex.tier()
+    assert t.device == 0 and t.precision == wdt
+    assert ex.is_staged() and ex.stage() is None and ex.evict() is None and ex.disable_native() is None
+    with pytest.raises(M.MoeContractError):
+        M.CudaExpert(m, E).run(xin.reshape(-1), rows, H)
+    m.close()

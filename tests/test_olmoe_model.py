@@ -28,7 +28,7 @@ def tiny_state(cfg, q4: bool, seed=3):
     return st
 
 
-CFG = OlmoeConfig(vocab_size=97, hidden_size=256, intermediate_size=256, num_hidden_layers=2,
+CFG = OlmoeConfig(vocab_size=128, hidden_size=256, intermediate_size=256, num_hidden_layers=2,
                   num_attention_heads=4, num_key_value_heads=4, num_experts=4, num_experts_per_tok=2)
 
 
@@ -73,23 +73,36 @@ def test_gpu_decoder_matches_restatement(cuda_lib, q4):
         clear = (top2[:, 1] - top2[:, 0]) > 0.05 * np.abs(want).max()
         assert (logits.argmax(-1).cpu().numpy()[clear] == want.argmax(-1)[clear]).all()
         past += 1
-    # the shape-static step (the one a CUDA graph captures) == the growing-cache step
-    ids_buf = torch.tensor(want.argmax(-1), device="cuda")[:, None]
-    pos_buf = torch.tensor([past], device="cuda")
-    static = dec._decode_static(ids_buf, pos_buf)
-    dec.k_cache[:, :, :, past].zero_()
-    dec.v_cache[:, :, :, past].zero_()
-    grown = dec.forward(ids_buf, past)
-    assert (static - grown).abs().max().item() / grown.abs().max().item() < 5e-3
-    g, gi, gp, gl = dec.make_decode_graph(2)
-    gi.copy_(ids_buf)
-    gp.fill_(past)
+    # the static step (hand-written trunk kernels over a preallocated cache, the one a CUDA graph
+    # captures) == the growing-cache step of the torch trunk, and both == the restatement
+    assert dec.static_supported() and dec.static_capturable()
+    assert dec.static_bytes(2, 32) == 2 * CFG.num_hidden_layers * 2 * CFG.num_key_value_heads * 32 * CFG.head_dim * 2
+    ids_next = torch.tensor(want.argmax(-1), device="cuda")[:, None]
+    grown = dec.forward(ids_next, past)
+    state = dec.static_state(2, 32)
+    for b in range(2):
+        dec.seed_static(state, b, past)
+    tokens = ids_next.to(torch.int32)
+    positions = torch.full((2,), past, dtype=torch.int32, device="cuda")
+    from mummu_b200.olmoe import bucket
+    static = dec.forward_static(tokens, positions, state, bucket(past + 1, 32)).clone()
+    want_next = np.stack([r.forward([int(t)], past) for r, t in zip(refs, want.argmax(-1))])
+    assert np.abs(static.cpu().numpy() - want_next).max() / np.abs(want_next).max() < 2e-2
+    assert (static - grown).abs().max().item() / grown.abs().max().item() < 2e-2
+    assert torch.equal(state.argmax[:2].cpu(), static.argmax(-1).to(torch.int32).cpu())
+    state.tokens.copy_(tokens)
+    state.positions.copy_(positions)
+    g = dec.make_decode_graph(state, 2, bucket(past + 1, 32))
     g.replay()
-    assert (gl - grown).abs().max().item() / grown.abs().max().item() < 5e-3
+    torch.cuda.synchronize()
+    assert torch.equal(state.logits[:2], static)          # a replay is the same step, bit for bit
+    state.close()
     # greedy generation runs and is deterministic
     a = dec.greedy_generate(ids, 4)
     b = dec.greedy_generate(ids, 4)
     assert torch.equal(a, b) and a.shape == (2, 4)
+    c = dec.greedy_generate_static(ids, 4)
+    assert c.shape == (2, 4) and torch.equal(c[:, 0], a[:, 0])     # same first pick; later ones may differ on near-ties
     dec.close()
 
 

@@ -135,12 +135,12 @@ pub mod sys {
         pub fn mummu_trunk_destroy(trunk: *mut MummuTrunk) -> i32;
         pub fn mummu_trunk_set_weight(trunk: *mut MummuTrunk, which: i32, layer: i32, data: *const c_void, bytes: usize,
                                       on_device: i32) -> i32;
-        pub fn mummu_trunk_attention_step(trunk: *mut MummuTrunk, layer: i32, x: *mut c_void, positions: *const i32,
-                                          slots: i32, key_len: i32, h2: *mut c_void, stream: *mut c_void) -> i32;
-        pub fn mummu_trunk_add(trunk: *mut MummuTrunk, x: *mut c_void, y: *const c_void, slots: i32, stream: *mut c_void) -> i32;
+        pub fn mummu_trunk_attention_step(trunk: *mut MummuTrunk, layer: i32, x: *mut c_void, y_prev: *const c_void,
+                                          positions: *const i32, slots: i32, key_len: i32, h2: *mut c_void,
+                                          stream: *mut c_void) -> i32;
         pub fn mummu_trunk_embed(trunk: *mut MummuTrunk, tokens: *const i32, slots: i32, x: *mut c_void, stream: *mut c_void) -> i32;
-        pub fn mummu_trunk_head(trunk: *mut MummuTrunk, x: *const c_void, slots: i32, logits: *mut f32, argmax: *mut i32,
-                                stream: *mut c_void) -> i32;
+        pub fn mummu_trunk_head(trunk: *mut MummuTrunk, x: *mut c_void, y_prev: *const c_void, slots: i32, logits: *mut f32,
+                                argmax: *mut i32, stream: *mut c_void) -> i32;
         pub fn mummu_trunk_kv_write(trunk: *mut MummuTrunk, layer: i32, slot: i32, first: i32, count: i32, k: *const c_void,
                                     v: *const c_void, stream: *mut c_void) -> i32;
         pub fn mummu_trunk_static_bytes(cfg: *const MummuTrunkConfig) -> u64;

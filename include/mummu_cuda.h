@@ -368,19 +368,20 @@ int32_t mummu_trunk_set_weight(MummuTrunk* trunk, int32_t which, int32_t layer, 
 /* x[slot] = embedding of tokens[slot] (device int32) - models/olmoe.rs:550. */
 int32_t mummu_trunk_embed(MummuTrunk* trunk, const int32_t* tokens, int32_t slots, void* x,
                           void* stream);
-/* One layer's attention half (models/olmoe.rs:561-566): h = rmsnorm(x); q, k, v; q/k norm; RoPE at
+/* One layer's attention half (models/olmoe.rs:561-566).  First x += y_prev when y_prev is not
+ * NULL: the previous layer's expert-bank output joins the residual stream (models/olmoe.rs:567-571)
+ * in the same launch that normalises it.  Then h = rmsnorm(x); q, k, v; q/k norm; RoPE at
  * positions[slot] (device int32); k, v stored at that position; attention over the keys up to it
  * inside the bucket of `key_len` keys; x += o-projection; h2 = rmsnorm(x) with the
- * post-attention weight - the input of the layer's expert bank.  x: device f16 [slots, hidden],
- * updated in place; h2: device f16 [slots, hidden]. */
-int32_t mummu_trunk_attention_step(MummuTrunk* trunk, int32_t layer, void* x, const int32_t* positions,
-                                   int32_t slots, int32_t key_len, void* h2, void* stream);
-/* x += y (the expert bank's output joins the residual stream, models/olmoe.rs:567-571). */
-int32_t mummu_trunk_add(MummuTrunk* trunk, void* x, const void* y, int32_t slots, void* stream);
-/* Final norm, lm_head and the greedy pick (models/olmoe.rs:573-585; decode.rs:33-48: the largest
- * logit, ties to the lowest id).  logits: device f32 [slots, vocab]; argmax: device int32 [slots]
- * or NULL. */
-int32_t mummu_trunk_head(MummuTrunk* trunk, const void* x, int32_t slots, float* logits,
+ * post-attention weight - the input of this layer's expert bank.  x: device f16 [slots, hidden],
+ * updated in place; y_prev, h2: device f16 [slots, hidden]. */
+int32_t mummu_trunk_attention_step(MummuTrunk* trunk, int32_t layer, void* x, const void* y_prev,
+                                   const int32_t* positions, int32_t slots, int32_t key_len, void* h2,
+                                   void* stream);
+/* x += y_prev (the last layer's expert bank; NULL: nothing to add), final norm, lm_head and the
+ * greedy pick (models/olmoe.rs:573-585; decode.rs:33-48: the largest logit, ties to the lowest
+ * id).  logits: device f32 [slots, vocab]; argmax: device int32 [slots] or NULL. */
+int32_t mummu_trunk_head(MummuTrunk* trunk, void* x, const void* y_prev, int32_t slots, float* logits,
                          int32_t* argmax, void* stream);
 /* `StaticDecode::seed_static` (capture.rs:105-106): copy `count` prefilled positions of one slot,
  * k and v as device f16 [kv_heads, count, head_dim], into the cache from position `first`. */

@@ -97,10 +97,10 @@ SYMBOLS = {
     "mummu_trunk_destroy": (C.c_int32, [C.c_void_p]),
     "mummu_trunk_set_weight": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_int32]),
     "mummu_trunk_embed": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
-    "mummu_trunk_attention_step": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
-                                               C.c_void_p, C.c_void_p]),
-    "mummu_trunk_add": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
-    "mummu_trunk_head": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "mummu_trunk_attention_step": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                               C.c_int32, C.c_void_p, C.c_void_p]),
+    "mummu_trunk_head": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
+                                     C.c_void_p]),
     "mummu_trunk_kv_write": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                          C.c_void_p, C.c_void_p]),
     "mummu_cuda_last_error": (C.c_char_p, []),

@@ -73,9 +73,9 @@ __device__ __forceinline__ float block_sum(float v, float* s_red) {
 }
 
 // x[slot] (+= y[slot]); h[slot] = x / sqrt(mean(x^2) + eps) * gamma        (models/olmoe.rs:561, 566)
-__global__ void __launch_bounds__(256) add_rms_kernel(__half* x, const __half* y, const float* gamma, __half* h, int H,
+__global__ void __launch_bounds__(512) add_rms_kernel(__half* x, const __half* y, const float* gamma, __half* h, int H,
                                                       float eps) {
-    __shared__ float s_red[8];
+    __shared__ float s_red[16];
     extern __shared__ float s_row[];
     const int slot = blockIdx.x;
     float ss = 0.0f;
@@ -151,63 +151,77 @@ __global__ void __launch_bounds__(256) gemv_f16_kernel(const __half* __restrict_
         }
 }
 
-// per slot: q, k, v from the projection partials; RMSNorm of q and k over the whole projection
-// (nn/attention.rs:196-200); rotate-half RoPE (nn/rope.rs:66-105); k, v into the cache at the
-// slot's position (nn/static_kv.rs: index-driven assignment)
-__global__ void __launch_bounds__(256) qk_norm_rope_kernel(const float* part, int ksplit, int B, const float* gq,
+// per (slot, part): part 0 = q, 1 = k, 2 = v.  The projection's output from its partials; RMSNorm of
+// q and of k over the whole projection (nn/attention.rs:196-200); rotate-half RoPE
+// (nn/rope.rs:66-105); k and v stored in the cache at the slot's position (nn/static_kv.rs:
+// index-driven assignment in place)
+__global__ void __launch_bounds__(512) qk_norm_rope_kernel(const float* part, int ksplit, int B, const float* gq,
                                                            const float* gk, const float* cosv, const float* sinv,
                                                            const int32_t* positions, __half* q_out, __half* kc, __half* vc,
                                                            int heads, int kv_heads, int hd, int max_ctx, float eps) {
-    extern __shared__ float s_v[];                  // q | k | v
-    __shared__ float s_red[8];
-    const int slot = blockIdx.x;
+    extern __shared__ float s_v[];
+    __shared__ float s_red[16];
+    const int slot = blockIdx.x, which = blockIdx.y;
     const int nq = heads * hd, nkv = kv_heads * hd, N = nq + 2 * nkv;
-    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    const int n0 = which == 0 ? 0 : (which == 1 ? nq : nq + nkv), nn = which == 0 ? nq : nkv;
+    float ss = 0.0f;
+    for (int n = threadIdx.x; n < nn; n += blockDim.x) {
         float s = 0.0f;
-        for (int ks = 0; ks < ksplit; ++ks) s += part[((size_t)ks * B + slot) * N + n];
-        s_v[n] = __half2float(__float2half_rn(s));  // the projection's output in the trunk's dtype
+        for (int ks = 0; ks < ksplit; ++ks) s += part[((size_t)ks * B + slot) * N + n0 + n];
+        s = __half2float(__float2half_rn(s));       // the projection's output in the trunk's dtype
+        s_v[n] = s;
+        ss += s * s;
     }
-    __syncthreads();
-    float sq = 0.0f, sk = 0.0f;
-    for (int n = threadIdx.x; n < nq; n += blockDim.x) sq += s_v[n] * s_v[n];
-    for (int n = threadIdx.x; n < nkv; n += blockDim.x) sk += s_v[nq + n] * s_v[nq + n];
-    const float rq = rsqrtf(block_sum(sq, s_red) / (float)nq + eps);
-    const float rk = rsqrtf(block_sum(sk, s_red) / (float)nkv + eps);
-    for (int n = threadIdx.x; n < nq; n += blockDim.x) s_v[n] = __half2float(__float2half_rn(s_v[n] * rq * gq[n]));
-    for (int n = threadIdx.x; n < nkv; n += blockDim.x)
-        s_v[nq + n] = __half2float(__float2half_rn(s_v[nq + n] * rk * gk[n]));
-    __syncthreads();
     const int pos = positions[slot];
+    if (which == 2) {
+        __syncthreads();
+        for (int n = threadIdx.x; n < nkv; n += blockDim.x) {
+            const int hh = n / hd, d = n - hh * hd;
+            vc[(((size_t)slot * kv_heads + hh) * max_ctx + pos) * hd + d] = __float2half_rn(s_v[n]);
+        }
+        return;
+    }
+    const float r = rsqrtf(block_sum(ss, s_red) / (float)nn + eps);
+    const float* gamma = which == 0 ? gq : gk;
+    for (int n = threadIdx.x; n < nn; n += blockDim.x) s_v[n] = __half2float(__float2half_rn(s_v[n] * r * gamma[n]));
+    __syncthreads();
     const int half = hd >> 1;
     const float* cr = cosv + (size_t)pos * half;
     const float* sr = sinv + (size_t)pos * half;
-    for (int n = threadIdx.x; n < nq; n += blockDim.x) {
-        const int d = n % hd, i = d < half ? d : d - half;
-        const float other = d < half ? -s_v[n + half] : s_v[n - half];
-        q_out[(size_t)slot * nq + n] = __float2half_rn(s_v[n] * cr[i] + other * sr[i]);
-    }
-    for (int n = threadIdx.x; n < nkv; n += blockDim.x) {
+    for (int n = threadIdx.x; n < nn; n += blockDim.x) {
         const int hh = n / hd, d = n - hh * hd, i = d < half ? d : d - half;
-        const float kvv = s_v[nq + n];
-        const float other = d < half ? -s_v[nq + n + half] : s_v[nq + n - half];
-        const size_t at = (((size_t)slot * kv_heads + hh) * max_ctx + pos) * hd + d;
-        kc[at] = __float2half_rn(kvv * cr[i] + other * sr[i]);
-        vc[at] = __float2half_rn(s_v[nq + nkv + n]);
+        const float other = d < half ? -s_v[n + half] : s_v[n - half];
+        const __half o = __float2half_rn(s_v[n] * cr[i] + other * sr[i]);
+        if (which == 0) q_out[(size_t)slot * nq + n] = o;
+        else kc[(((size_t)slot * kv_heads + hh) * max_ctx + pos) * hd + d] = o;
     }
 }
 
-// grid (heads, slots, splits); 128 threads; one partial (max, sum, value sum) per block
+constexpr int ATT_UN = 8;                           // 16-byte loads in flight per lane
+
+// a 16-byte load that does not displace the weights in L1: each key and value is read once per step
+__device__ __forceinline__ uint4 ld_stream16(const __half* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// grid (heads, slots, splits); 128 threads; one partial (max, sum, value sum) per block.
+// A key or value row of `hd` halves is read by hd/8 lanes with one 16-byte load each, so a warp
+// covers 256 / hd rows... (hd = 128: two rows) per instruction, fully coalesced.
 __global__ void __launch_bounds__(128) decode_attn_kernel(const __half* q, const __half* kc, const __half* vc,
                                                           const int32_t* positions, float* apart, int heads, int kv_heads,
                                                           int hd, int max_ctx, int key_len, int splits, float scale) {
-    extern __shared__ float s_attn[];               // q [hd] | scores [chunk]
+    extern __shared__ float s_attn[];               // scores [chunk] | per-warp value sums [4][hd]
     __shared__ float s_red[4];
     const int head = blockIdx.x, slot = blockIdx.y, sp = blockIdx.z;
     const int pos = min(positions[slot], key_len - 1);
     const int chunk = (key_len + splits - 1) / splits;
     const int lo = sp * chunk, hi = min(pos + 1, lo + chunk);
-    float* s_q = s_attn;
-    float* s_sc = s_attn + hd;
+    float* s_sc = s_attn;
+    float* s_acc = s_attn + chunk;
     float* out = apart + (((size_t)slot * heads + head) * splits + sp) * (hd + 2);
     if (lo >= hi) {                                 // nothing for this split (uniform over the block)
         if (threadIdx.x == 0) {
@@ -216,51 +230,103 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const __half* q, const
         }
         return;
     }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lpr = hd >> 3;                        // lanes per row (16 for head_dim 128)
+    const int rpw = 32 / lpr;                       // rows per warp instruction
+    const int sub = lane / lpr, li = lane - sub * lpr;
     const int hkv = head / (heads / kv_heads);
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) s_q[d] = __half2float(q[((size_t)slot * heads + head) * hd + d]) * scale;
-    __syncthreads();
     const __half* kbase = kc + ((size_t)slot * kv_heads + hkv) * max_ctx * hd;
     const __half* vbase = vc + ((size_t)slot * kv_heads + hkv) * max_ctx * hd;
-    float mx = -FLT_MAX;
-    for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) {
-        const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)j * hd);
-        float s = 0.0f;
-        for (int c = 0; c < hd / 8; ++c) {
-            const uint4 v = kr[c];
-            const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+    // this lane's 8 values of q
+    float qf[8];
+    {
+        const uint4 qv = *reinterpret_cast<const uint4*>(q + ((size_t)slot * heads + head) * hd + li * 8);
+        const __half2* h2 = reinterpret_cast<const __half2*>(&qv);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float2 f = __half22float2(h2[u]);
-                s = fmaf(f.x, s_q[c * 8 + 2 * u], s);
-                s = fmaf(f.y, s_q[c * 8 + 2 * u + 1], s);
+        for (int u = 0; u < 4; ++u) {
+            const float2 f = __half22float2(h2[u]);
+            qf[2 * u] = f.x * scale;
+            qf[2 * u + 1] = f.y * scale;
+        }
+    }
+    // ATT_UN loads per lane are issued before any is used: the kernel is bound by bytes in flight
+    float mx = -FLT_MAX;
+    for (int jb = lo + warp * (rpw * ATT_UN); jb < hi; jb += 4 * rpw * ATT_UN) {
+        uint4 kv[ATT_UN];
+#pragma unroll
+        for (int u = 0; u < ATT_UN; ++u) {
+            const int j = jb + u * rpw + sub;
+            kv[u] = j < hi ? ld_stream16(kbase + (size_t)j * hd + li * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < ATT_UN; ++u) {
+            const int j = jb + u * rpw + sub;
+            const __half2* h2 = reinterpret_cast<const __half2*>(&kv[u]);
+            float s = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h2[e]);
+                s = fmaf(f.x, qf[2 * e], s);
+                s = fmaf(f.y, qf[2 * e + 1], s);
+            }
+            for (int off = lpr >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+            if (j < hi) {
+                if (li == 0) s_sc[j - lo] = s;
+                mx = fmaxf(mx, s);
             }
         }
-        s_sc[j - lo] = s;
-        mx = fmaxf(mx, s);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
-    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mx;
+    if (lane == 0) s_red[warp] = mx;
     __syncthreads();
     mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
-    float sum = 0.0f;
+    float psum = 0.0f;
     for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) {
         const float p = __expf(s_sc[j - lo] - mx);
         s_sc[j - lo] = p;
-        sum += p;
+        psum += p;
     }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) psum += __shfl_xor_sync(0xFFFFFFFFu, psum, off);
+    __syncthreads();                                // everyone has read s_red (the maxima)
+    if (lane == 0) s_red[warp] = psum;
     __syncthreads();
-    float l = 0.0f;
-    for (int j = 0; j < hi - lo; ++j) l += s_sc[j];           // same order in every thread
-    (void)sum;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float acc = 0.0f;
-        for (int j = lo; j < hi; ++j) acc = fmaf(s_sc[j - lo], __half2float(vbase[(size_t)j * hd + d]), acc);
-        out[2 + d] = acc;
+    // values: the lane keeps 8 output dimensions, summed over the rows it reads
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int jb = lo + warp * (rpw * ATT_UN); jb < hi; jb += 4 * rpw * ATT_UN) {
+        uint4 vv[ATT_UN];
+#pragma unroll
+        for (int u = 0; u < ATT_UN; ++u) {
+            const int j = jb + u * rpw + sub;
+            vv[u] = j < hi ? ld_stream16(vbase + (size_t)j * hd + li * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < ATT_UN; ++u) {
+            const int j = jb + u * rpw + sub;
+            const float p = j < hi ? s_sc[j - lo] : 0.0f;
+            const __half2* h2 = reinterpret_cast<const __half2*>(&vv[u]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h2[e]);
+                acc[2 * e] = fmaf(p, f.x, acc[2 * e]);
+                acc[2 * e + 1] = fmaf(p, f.y, acc[2 * e + 1]);
+            }
+        }
     }
+    // fold the row groups of a warp, then the warps (fixed order)
+    for (int off = lpr; off < 32; off <<= 1)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] += __shfl_xor_sync(0xFFFFFFFFu, acc[u], off);
+    if (sub == 0)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) s_acc[warp * hd + li * 8 + u] = acc[u];
+    __syncthreads();
+    for (int d = threadIdx.x; d < hd; d += blockDim.x)
+        out[2 + d] = (s_acc[d] + s_acc[hd + d]) + (s_acc[2 * hd + d] + s_acc[3 * hd + d]);
     if (threadIdx.x == 0) {
         out[0] = mx;
-        out[1] = l;
+        out[1] = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
     }
 }
 
@@ -285,9 +351,9 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* apart, _
 }
 
 // x += sum of the o-projection partials ; h2 = rmsnorm(x) * gamma     (models/olmoe.rs:565-566)
-__global__ void __launch_bounds__(256) residual_rms_kernel(__half* x, const float* part, int ksplit, int B,
+__global__ void __launch_bounds__(512) residual_rms_kernel(__half* x, const float* part, int ksplit, int B,
                                                            const float* gamma, __half* h2, int H, float eps) {
-    __shared__ float s_red[8];
+    __shared__ float s_red[16];
     extern __shared__ float s_row[];
     const int slot = blockIdx.x;
     float ss = 0.0f;
@@ -444,8 +510,10 @@ int32_t mummu_trunk_create(const MummuTrunkConfig* cfg, MummuTrunk** out) {
     *out = nullptr;
     const MummuTrunkConfig& c = *cfg;
     MUMMU_REQUIRE(c.hidden >= 8 && c.hidden % 32 == 0 && c.heads >= 1 && c.kv_heads >= 1 && c.heads % c.kv_heads == 0 &&
-                      c.head_dim >= 8 && c.head_dim % 8 == 0 && c.layers >= 1 && c.vocab >= 1,
-                  "trunk: hidden %d (a multiple of 32), %d heads over %d kv heads of %d, %d layers, vocabulary %d",
+                      c.head_dim >= 8 && c.head_dim <= 256 && (c.head_dim & (c.head_dim - 1)) == 0 && c.layers >= 1 &&
+                      c.vocab >= 1,
+                  "trunk: hidden %d (a multiple of 32), %d heads over %d kv heads of %d (a power of two, 8..256), %d layers, "
+                  "vocabulary %d",
                   c.hidden, c.heads, c.kv_heads, c.head_dim, c.layers, c.vocab);
     MUMMU_REQUIRE((c.heads * c.head_dim) % 32 == 0 && ((c.heads + 2 * c.kv_heads) * c.head_dim) % 128 == 0 &&
                       c.hidden % 128 == 0 && c.vocab % 128 == 0,
@@ -570,23 +638,8 @@ int32_t mummu_trunk_embed(MummuTrunk* t, const int32_t* tokens, int32_t slots, v
     return MUMMU_OK;
 }
 
-int32_t mummu_trunk_add(MummuTrunk* t, void* x, const void* y, int32_t slots, void* stream) {
-    MUMMU_REQUIRE(t && x && y, "mummu_trunk_add: null argument");
-    MUMMU_REQUIRE(slots >= 1 && slots <= t->cfg.slots, "mummu_trunk_add: %d slots of %d", slots, t->cfg.slots);
-    std::lock_guard<std::mutex> lock(t->mu);
-    TrunkDevice guard(t->cfg.device);
-    cudaStream_t s = stream ? (cudaStream_t)stream : t->stream;
-    const MummuTrunkConfig& c = t->cfg;
-    TrunkLaunch l(t);
-    // (the normalised copy it also produces is scratch; the next attention step recomputes its own)
-    MUMMU_CUDA_TRY(allow_big_smem(add_rms_kernel, c.device));
-    add_rms_kernel<<<slots, 256, (size_t)c.hidden * 4, s>>>((__half*)x, (const __half*)y, t->final_norm, t->h, c.hidden, c.rms_eps);
-    MUMMU_CUDA_TRY(cudaGetLastError());
-    return MUMMU_OK;
-}
-
-int32_t mummu_trunk_attention_step(MummuTrunk* t, int32_t layer, void* x, const int32_t* positions, int32_t slots,
-                                   int32_t key_len, void* h2, void* stream) {
+int32_t mummu_trunk_attention_step(MummuTrunk* t, int32_t layer, void* x, const void* y_prev, const int32_t* positions,
+                                   int32_t slots, int32_t key_len, void* h2, void* stream) {
     MUMMU_REQUIRE(t && x && positions && h2, "mummu_trunk_attention_step: null argument");
     const MummuTrunkConfig& c = t->cfg;
     MUMMU_REQUIRE(layer >= 0 && layer < c.layers, "mummu_trunk_attention_step: layer %d of %d", layer, c.layers);
@@ -602,10 +655,10 @@ int32_t mummu_trunk_attention_step(MummuTrunk* t, int32_t layer, void* x, const 
     const float* g_q = t->norms + ((size_t)layer * 4 + 2) * nstride;
     const float* g_k = t->norms + ((size_t)layer * 4 + 3) * nstride;
     int rc;
-    {   // h = rmsnorm(x) * gamma_in
+    {   // x += y_prev (the previous layer's expert bank joins the residual stream); h = rmsnorm(x) * gamma_in
         TrunkLaunch l(t);
         MUMMU_CUDA_TRY(allow_big_smem(add_rms_kernel, c.device));
-        add_rms_kernel<<<slots, 256, (size_t)H * 4, s>>>((__half*)x, nullptr, g_in, t->h, H, c.rms_eps);
+        add_rms_kernel<<<slots, 512, (size_t)H * 4, s>>>((__half*)x, (const __half*)y_prev, g_in, t->h, H, c.rms_eps);
         MUMMU_CUDA_TRY(cudaGetLastError());
     }
     const int ks_qkv = H >= 2048 ? 4 : (H >= 1024 ? 2 : 1);
@@ -616,13 +669,13 @@ int32_t mummu_trunk_attention_step(MummuTrunk* t, int32_t layer, void* x, const 
     {
         TrunkLaunch l(t);
         MUMMU_CUDA_TRY(allow_big_smem(qk_norm_rope_kernel, c.device));
-        qk_norm_rope_kernel<<<slots, 256, (size_t)nqkv * 4, s>>>(t->part, ks_qkv, slots, g_q, g_k, t->rope_cos, t->rope_sin,
+        qk_norm_rope_kernel<<<dim3(slots, 3), 512, (size_t)std::max(nq, nkv) * 4, s>>>(t->part, ks_qkv, slots, g_q, g_k, t->rope_cos, t->rope_sin,
                                                                  positions, t->q, kc, vc, c.heads, c.kv_heads, c.head_dim,
                                                                  c.max_ctx, c.rms_eps);
         MUMMU_CUDA_TRY(cudaGetLastError());
     }
     // key splits: enough blocks to fill the GPU when few sequences decode, chunks of at most 1024 keys
-    int splits = (2 * 148 + slots * c.heads - 1) / (slots * c.heads);
+    int splits = (8 * 148 + slots * c.heads - 1) / (slots * c.heads);
     splits = std::max(splits, (key_len + 1023) / 1024);
     splits = std::min(std::min(splits, TR_MAX_SPLITS), std::max(1, key_len / 32));
     const int chunk = (key_len + splits - 1) / splits;
@@ -630,7 +683,7 @@ int32_t mummu_trunk_attention_step(MummuTrunk* t, int32_t layer, void* x, const 
     {
         TrunkLaunch l(t);
         MUMMU_CUDA_TRY(allow_big_smem(decode_attn_kernel, c.device));
-        decode_attn_kernel<<<dim3(c.heads, slots, splits), 128, (size_t)(c.head_dim + chunk) * 4, s>>>(
+        decode_attn_kernel<<<dim3(c.heads, slots, splits), 128, (size_t)(4 * c.head_dim + chunk) * 4, s>>>(
             t->q, kc, vc, positions, t->apart, c.heads, c.kv_heads, c.head_dim, c.max_ctx, key_len, splits,
             1.0f / sqrtf((float)c.head_dim));
         MUMMU_CUDA_TRY(cudaGetLastError());
@@ -645,13 +698,14 @@ int32_t mummu_trunk_attention_step(MummuTrunk* t, int32_t layer, void* x, const 
     {
         TrunkLaunch l(t);
         MUMMU_CUDA_TRY(allow_big_smem(residual_rms_kernel, c.device));
-        residual_rms_kernel<<<slots, 256, (size_t)H * 4, s>>>((__half*)x, t->part, ks_o, slots, g_post, (__half*)h2, H, c.rms_eps);
+        residual_rms_kernel<<<slots, 512, (size_t)H * 4, s>>>((__half*)x, t->part, ks_o, slots, g_post, (__half*)h2, H, c.rms_eps);
         MUMMU_CUDA_TRY(cudaGetLastError());
     }
     return MUMMU_OK;
 }
 
-int32_t mummu_trunk_head(MummuTrunk* t, const void* x, int32_t slots, float* logits, int32_t* argmax, void* stream) {
+int32_t mummu_trunk_head(MummuTrunk* t, void* x, const void* y_prev, int32_t slots, float* logits, int32_t* argmax,
+                         void* stream) {
     MUMMU_REQUIRE(t && x && logits, "mummu_trunk_head: null argument (logits are always written)");
     const MummuTrunkConfig& c = t->cfg;
     MUMMU_REQUIRE(slots >= 1 && slots <= c.slots, "mummu_trunk_head: %d slots of %d", slots, c.slots);
@@ -662,8 +716,8 @@ int32_t mummu_trunk_head(MummuTrunk* t, const void* x, int32_t slots, float* log
     {
         TrunkLaunch l(t);
         MUMMU_CUDA_TRY(allow_big_smem(add_rms_kernel, c.device));
-        add_rms_kernel<<<slots, 256, (size_t)c.hidden * 4, s>>>((__half*)const_cast<void*>(x), nullptr, t->final_norm, t->h,
-                                                                c.hidden, c.rms_eps);
+        add_rms_kernel<<<slots, 512, (size_t)c.hidden * 4, s>>>((__half*)x, (const __half*)y_prev, t->final_norm, t->h, c.hidden,
+                                                                c.rms_eps);
         MUMMU_CUDA_TRY(cudaGetLastError());
     }
     if ((rc = gemv(t, t->lm_head, t->h, logits, c.vocab, c.hidden, 1, slots, s))) return rc;

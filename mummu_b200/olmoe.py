@@ -285,12 +285,13 @@ class OlmoeDecoder:
         stream = moe_mod._torch_stream()
         x, h2, logits = state.x[:k], state.h2[:k], state.logits[:k]
         moe_mod._check(L.lib.mummu_trunk_embed(h, tokens.data_ptr(), k, x.data_ptr(), stream))
+        y = None
         for l, lay in enumerate(self.layers):
-            moe_mod._check(L.lib.mummu_trunk_attention_step(h, l, x.data_ptr(), positions.data_ptr(), k, length,
-                                                            h2.data_ptr(), stream))
+            moe_mod._check(L.lib.mummu_trunk_attention_step(h, l, x.data_ptr(), None if y is None else y.data_ptr(),
+                                                            positions.data_ptr(), k, length, h2.data_ptr(), stream))
             y = lay["mlp"].forward(h2, c.num_experts_per_tok, c.norm_topk_prob)
-            moe_mod._check(L.lib.mummu_trunk_add(h, x.data_ptr(), y.data_ptr(), k, stream))
-        moe_mod._check(L.lib.mummu_trunk_head(h, x.data_ptr(), k, logits.data_ptr(), state.argmax.data_ptr(), stream))
+        moe_mod._check(L.lib.mummu_trunk_head(h, x.data_ptr(), y.data_ptr(), k, logits.data_ptr(),
+                                              state.argmax.data_ptr(), stream))
         return logits
 
     def seed_static(self, state: "StaticState", slot: int, cache_len: int, src_slot: int = None) -> None:
@@ -383,7 +384,7 @@ class OlmoeDecoder:
         for length in lengths:                   # capture outside the timed region
             graphs[length] = self.make_decode_graph(state, B, length)
         moe_per_step = (sum(l["mlp"].launch_count() for l in self.layers) - moe0) // (3 * len(lengths))
-        launches = moe_per_step + 7 * self.cfg.num_hidden_layers + 16 + 4     # + trunk kernels (7 + add per layer, head)
+        launches = moe_per_step + 7 * self.cfg.num_hidden_layers + 4           # + trunk kernels (7 per layer, head)
         t_.cuda.synchronize()
         a.record()
         for i in range(n_new):

@@ -104,6 +104,8 @@ pub mod sys {
         pub fn mummu_ep_free(ptr: *mut c_void) -> i32;
         pub fn mummu_ep_sync_bytes(world: i32, experts: i32) -> usize;
         pub fn mummu_ep_reset(device: i32, own_sync: *mut c_void, world: i32, experts: i32) -> i32;
+        pub fn mummu_ep_place(moe: *mut MummuMoe, ids: *const i32, table: *const i32, experts_real: i32, n: i64,
+                              ids_out: *mut i32, stream: *mut c_void) -> i32;
         pub fn mummu_ep_post_counts(moe: *mut MummuMoe, counts: *const i32, peer_sync: *const *mut c_void, rank: i32,
                                     world: i32, stream: *mut c_void) -> i32;
         pub fn mummu_ep_dispatch(moe: *mut MummuMoe, x: *const c_void, row_token: *const i32, offsets: *const i32,
@@ -114,7 +116,7 @@ pub mod sys {
                                 recv_own: *const c_void, local_counts: *const i32, rows_cap: i64, ys_own: *mut c_void,
                                 stream: *mut c_void) -> i32;
         pub fn mummu_ep_combine(moe: *mut MummuMoe, peer_sync: *const *mut c_void, peer_ys: *const *mut c_void,
-                                ids: *const i32, w: *const f32, pos: *const i32, offsets: *const i32,
+                                ids: *const i32, order_ids: *const i32, w: *const f32, pos: *const i32, offsets: *const i32,
                                 dst_base: *const i32, rank: i32, world: i32, tokens: i32, top_k: i32, cap_rows: i64,
                                 out: *mut c_void, stream: *mut c_void) -> i32;
         // parity taps, counters, profiling

@@ -225,8 +225,22 @@ int32_t mummu_ep_free(void* ptr);
  *   mummu_ep_experts      stage 3: waits for every rank's rows; runs this rank's experts over its
  *                         receive buffer into its output buffer ys_own ([cap_rows, hidden]).
  *   mummu_ep_combine      stage 4: waits for every rank's outputs; mummu_moe_combine reading each
- *                         expert output row from its owner's buffer peer_ys[owner] with peer loads. */
+ *                         expert output row from its owner's buffer peer_ys[owner] with peer loads.
+ *                         order_ids (NULL: ids) gives the expert id of each pair where `ids` are
+ *                         bank slots (mummu_ep_place): a token's terms are summed in ascending
+ *                         expert id either way. */
 size_t mummu_ep_sync_bytes(int32_t world, int32_t experts);
+/* Hot-expert placement (nn/moe.rs:1527-1535 hands the hit counters to the planner; tier.rs:353-431
+ * plans from them).  A group whose handles are created over `world * slots_per_rank` bank SLOTS
+ * instead of experts can hold an expert in several slots, on different ranks, and any expert on
+ * any rank.  The router (a handle over the real experts) still emits real expert ids; this call
+ * turns them into slot ids for this rank's tokens, ids_out[i] = table[ids[i]] (table: device
+ * int32 [experts_real], every entry a slot of `moe`), and the stages above run on slot ids
+ * unchanged.  The same expert's weights give the same numbers in whichever slot they sit, so the
+ * layer's output does not depend on the placement.  An id or a table entry out of range raises
+ * MUMMU_ERR_CONTRACT at the next mummu_moe_sync. */
+int32_t mummu_ep_place(MummuMoe* moe, const int32_t* ids, const int32_t* table, int32_t experts_real,
+                       int64_t n, int32_t* ids_out, void* stream);
 int32_t mummu_ep_reset(int32_t device, void* own_sync, int32_t world, int32_t experts);
 int32_t mummu_ep_post_counts(MummuMoe* moe, const int32_t* counts, void* const* peer_sync,
                              int32_t rank, int32_t world, void* stream);
@@ -238,7 +252,7 @@ int32_t mummu_ep_experts(MummuMoe* moe, void* const* peer_sync, int32_t rank, in
                          const void* recv_own, const int32_t* local_counts, int64_t rows_cap,
                          void* ys_own, void* stream);
 int32_t mummu_ep_combine(MummuMoe* moe, void* const* peer_sync, void* const* peer_ys,
-                         const int32_t* ids, const float* w, const int32_t* pos,
+                         const int32_t* ids, const int32_t* order_ids, const float* w, const int32_t* pos,
                          const int32_t* offsets, const int32_t* dst_base, int32_t rank,
                          int32_t world, int32_t tokens, int32_t top_k, int64_t cap_rows, void* out,
                          void* stream);

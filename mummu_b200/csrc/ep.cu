@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(32) ep_signal_kernel(PeerTable sync, int rank,
 // ---- combine -----------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) ep_combine_kernel(PeerTable sync, PeerTable ys, const int32_t* ids,
-                                                         const float* w, const int32_t* pos, const int32_t* offsets,
+                                                         const int32_t* order_ids, const float* w, const int32_t* pos, const int32_t* offsets,
                                                          const int32_t* dst_base, int rank, int world, int top_k, int H,
                                                          int EL, int64_t cap_rows, uint32_t wait_polls, int32_t* status,
                                                          T* out) {
@@ -247,11 +247,14 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(PeerTable sync, PeerTab
     if (ok) {
         const int64_t t = blockIdx.x;
         for (int r = threadIdx.x; r < top_k; r += blockDim.x) {
+            // summed in ascending EXPERT id (nn/moe.rs:296-328); with a placement `ids` are bank
+            // slots and the expert ids come separately, so that the order does not follow the slots
             const int id = ids[t * top_k + r];
+            const int key = order_ids[t * top_k + r];
             int rk = 0;
             for (int q = 0; q < top_k; ++q) {
-                const int other = ids[t * top_k + q];
-                rk += (other < id || (other == id && q < r)) ? 1 : 0;
+                const int other = order_ids[t * top_k + q];
+                rk += (other < key || (other == key && q < r)) ? 1 : 0;
             }
             const int64_t drow = (int64_t)dst_base[id] + (pos[t * top_k + r] - offsets[id]);
             const bool inside = drow >= 0 && drow < cap_rows;
@@ -285,6 +288,22 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(PeerTable sync, PeerTab
         }
     }
     if (ep_last_block(own + EP_W_DONE + 1) && threadIdx.x == 0) own[EP_W_WAIT + EP_CH_OUT] += 1;
+}
+
+// Placement: a routed expert id becomes the id of the bank slot that serves it for this rank's
+// tokens.  An id outside the router's experts, or a table entry outside the slots, is reported
+// (STATUS_BOUNDS) and sent to slot 0 so that nothing later indexes past a buffer.
+__global__ void ep_place_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ table, int experts_real,
+                                int slots, int64_t n, int32_t* __restrict__ out, int32_t* status) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int e = ids[i];
+    int v = (e >= 0 && e < experts_real) ? table[e] : -1;
+    if (v < 0 || v >= slots) {
+        atomicOr(status, STATUS_BOUNDS);
+        v = 0;
+    }
+    out[i] = v;
 }
 
 }  // namespace mummu
@@ -376,6 +395,19 @@ static PeerTable peer_table(void* const* ptrs, int world) {
 
 static uint32_t wait_polls_of(const MummuMoe* m) { return m->sw.wait_polls ? m->sw.wait_polls : EP_WAIT_POLLS_DEFAULT; }
 
+int32_t mummu_ep_place(MummuMoe* m, const int32_t* ids, const int32_t* table, int32_t experts_real, int64_t n,
+                       int32_t* ids_out, void* stream) {
+    MUMMU_REQUIRE(m && ids && table && ids_out, "mummu_ep_place: null argument");
+    MUMMU_REQUIRE(experts_real >= 1 && n >= 0, "mummu_ep_place: %d experts, %lld ids", experts_real, (long long)n);
+    if (n == 0) return MUMMU_OK;
+    std::lock_guard<std::mutex> lock(m->mu);
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    LaunchScope scope(m, s, "ep_place");
+    ep_place_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(ids, table, experts_real, m->cfg.experts, n, ids_out, m->status);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
 int32_t mummu_ep_post_counts(MummuMoe* m, const int32_t* counts, void* const* peer_sync, int32_t rank,
                              int32_t world, void* stream) {
     MUMMU_REQUIRE(m && counts && peer_sync, "mummu_ep_post_counts: null argument");
@@ -455,7 +487,7 @@ int32_t mummu_ep_experts(MummuMoe* m, void* const* peer_sync, int32_t rank, int3
 }
 
 int32_t mummu_ep_combine(MummuMoe* m, void* const* peer_sync, void* const* peer_ys, const int32_t* ids,
-                         const float* w, const int32_t* pos, const int32_t* offsets, const int32_t* dst_base,
+                         const int32_t* order_ids, const float* w, const int32_t* pos, const int32_t* offsets, const int32_t* dst_base,
                          int32_t rank, int32_t world, int32_t tokens, int32_t top_k, int64_t cap_rows, void* out,
                          void* stream) {
     MUMMU_REQUIRE(m && peer_sync && peer_ys && ids && w && pos && offsets && dst_base && out,
@@ -475,11 +507,11 @@ int32_t mummu_ep_combine(MummuMoe* m, void* const* peer_sync, void* const* peer_
     const int k_eff = tokens < 1 ? 0 : top_k;
     LaunchScope scope(m, s, "ep_combine");
     if (m->cfg.act_dtype == MUMMU_F16)
-        ep_combine_kernel<__half><<<grid, 256, smem, s>>>(ts, ty, ids, w, pos, offsets, dst_base, rank, world, k_eff, tokens < 1 ? 0 : H,
+        ep_combine_kernel<__half><<<grid, 256, smem, s>>>(ts, ty, ids, order_ids ? order_ids : ids, w, pos, offsets, dst_base, rank, world, k_eff, tokens < 1 ? 0 : H,
                                                          m->cfg.experts_local, cap_rows, wait_polls_of(m), m->status,
                                                          (__half*)out);
     else
-        ep_combine_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(ts, ty, ids, w, pos, offsets, dst_base, rank, world, k_eff,
+        ep_combine_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(ts, ty, ids, order_ids ? order_ids : ids, w, pos, offsets, dst_base, rank, world, k_eff,
                                                                 tokens < 1 ? 0 : H, m->cfg.experts_local, cap_rows,
                                                                 wait_polls_of(m), m->status, (__nv_bfloat16*)out);
     MUMMU_CUDA_TRY(cudaGetLastError());

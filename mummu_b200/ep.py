@@ -177,7 +177,8 @@ class ExpertParallelMoe:
 
     def __init__(self, cfg, group=None, device: Optional[int] = None, act_dtype: int = 2,
                  weight_dtype: Optional[int] = None, max_tokens: int = 0, workspace=None,
-                 scratch_donor=None, rank: Optional[int] = None, world: Optional[int] = None):
+                 scratch_donor=None, rank: Optional[int] = None, world: Optional[int] = None,
+                 placement=None):
         import torch
         from . import moe
         self.group = group
@@ -188,29 +189,52 @@ class ExpertParallelMoe:
             self.world = dist.get_world_size(group)
         else:
             self.dist, self.rank, self.world = None, rank, world
-        assert cfg.num_experts % self.world == 0, "experts must divide evenly over the ranks"
-        self.el = cfg.num_experts // self.world
         self.cfg = cfg
+        self.placement = placement
+        if placement is None:
+            assert cfg.num_experts % self.world == 0, "experts must divide evenly over the ranks"
+            self.el = cfg.num_experts // self.world
+            self.slots_total = cfg.num_experts
+        else:
+            # the bank handles of the group run over SLOTS; a second, bank-less handle routes over
+            # the real experts and its ids are turned into slot ids (mummu_ep_place)
+            assert placement.world == self.world and placement.experts == cfg.num_experts
+            assert workspace is not None, "a placed layer moves rows through a peer workspace"
+            self.el = placement.slots
+            self.slots_total = placement.virtual_experts
         dev = torch.cuda.current_device() if device is None else device
         self.device = torch.device("cuda", dev)
         # scratch for the local experts must hold the rows that can arrive: every rank's tokens * k
         self.workspace = workspace
         if workspace is not None:
-            assert cfg.num_experts <= workspace.experts, "workspace sync block too small for this router"
-        self.moe = moe.SparseMoeConfig(cfg.hidden_size, cfg.expert_intermediate_size, cfg.num_experts,
+            assert self.slots_total <= workspace.experts, "workspace sync block too small for this group"
+        self.moe = moe.SparseMoeConfig(cfg.hidden_size, cfg.expert_intermediate_size, self.slots_total,
                                        cfg.num_experts_per_tok).init(
             device=dev, act_dtype=act_dtype, weight_dtype=weight_dtype,
             max_tokens=0 if scratch_donor is not None else max_tokens * self.world,
             expert_first=self.rank * self.el, experts_local=self.el)
         if scratch_donor is not None:
             self.moe.adopt_scratch(scratch_donor.moe)
+        self.router = self.moe
+        if placement is not None:
+            self.router = moe.SparseMoeConfig(cfg.hidden_size, cfg.expert_intermediate_size, cfg.num_experts,
+                                              cfg.num_experts_per_tok).init(
+                device=dev, act_dtype=act_dtype, weight_dtype=weight_dtype, max_tokens=max_tokens,
+                expert_first=0, experts_local=1)
+            self.table = torch.from_numpy(placement.route_table(self.rank)).to(self.device)
 
     def set_router(self, weight, layout: int = 0, bias=None):
-        self.moe.set_router(weight, layout, bias)
+        self.router.set_router(weight, layout, bias)
 
     def set_local_banks(self, gate, up, down):
-        """Banks of this rank's experts only: [experts / world, out, in]."""
+        """Banks of this rank's experts only: [experts / world, out, in]; with a placement, of its
+        slots: bank[placement.rank_experts(rank)]."""
         self.moe.set_banks(gate, up, down)
+
+    def take_hits(self):
+        """Per (real) expert routing hits of this rank's tokens since the last call
+        (`ExpertPool::take_hits`, nn/moe.rs:1527-1535): the planner's input."""
+        return self.router.take_hits()
 
     # ---- the four stages (see include/mummu_cuda.h); a rank runs them in this order ------------
     def stage_route(self, x, top_k: int, norm_topk_prob: bool):
@@ -219,10 +243,19 @@ class ExpertParallelMoe:
         T = x.shape[0]
         assert T * top_k * self.world <= ws.cap_rows, "workspace too small for the rows that may arrive"
         st = dict(x=x, top_k=top_k)
-        st["ids"], st["w"], st["counts"], st["offsets"], st["row_token"], st["pos"] = m.route_grouped(x, top_k, norm_topk_prob)
-        m.ep_post_counts(st["counts"], ws.sync_table, self.rank, self.world)
         i32 = dict(dtype=torch.int32, device=x.device)
-        st["dst_base"], st["local_counts"] = torch.empty(self.cfg.num_experts, **i32), torch.empty(self.el, **i32)
+        if self.placement is None:
+            st["ids"], st["w"], st["counts"], st["offsets"], st["row_token"], st["pos"] = m.route_grouped(x, top_k, norm_topk_prob)
+        else:
+            st["expert_ids"], st["w"] = self.router.route_flat(x, top_k, norm_topk_prob)
+            st["ids"] = torch.empty_like(st["expert_ids"])
+            m.ep_place(st["expert_ids"], self.table, self.cfg.num_experts, st["ids"])
+            V = self.slots_total
+            st["counts"], st["offsets"] = torch.empty(V, **i32), torch.empty(V + 1, **i32)
+            st["row_token"], st["pos"] = torch.empty(T * top_k, **i32), torch.empty(T * top_k, **i32)
+            m.permute(st["ids"], st["counts"], st["offsets"], st["row_token"], st["pos"])
+        m.ep_post_counts(st["counts"], ws.sync_table, self.rank, self.world)
+        st["dst_base"], st["local_counts"] = torch.empty(self.slots_total, **i32), torch.empty(self.el, **i32)
         return st
 
     def stage_dispatch(self, st):
@@ -240,7 +273,7 @@ class ExpertParallelMoe:
         ws = self.workspace
         y = torch.empty_like(st["x"])
         self.moe.ep_combine(ws.sync_table, ws.ys_table, st["ids"], st["w"], st["pos"], st["offsets"], st["dst_base"],
-                            self.rank, self.world, ws.cap_rows, y)
+                            self.rank, self.world, ws.cap_rows, y, order_ids=st.get("expert_ids"))
         return y
 
     def forward_p2p(self, x, top_k: int, norm_topk_prob: bool):
@@ -282,4 +315,6 @@ class ExpertParallelMoe:
         return y
 
     def close(self):
+        if self.router is not self.moe:
+            self.router.close()
         self.moe.close()

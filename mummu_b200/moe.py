@@ -317,6 +317,10 @@ class SparseMoe:
                                                _torch_stream()))
 
     # stages of the expert-parallel layer (peer memory; see include/mummu_cuda.h)
+    def ep_place(self, ids, table, experts_real: int, ids_out) -> None:
+        _check(L.lib.mummu_ep_place(self._h, ids.data_ptr(), table.data_ptr(), experts_real, ids.numel(),
+                                    ids_out.data_ptr(), _torch_stream()))
+
     def ep_post_counts(self, counts, sync_table, rank: int, world: int) -> None:
         _check(L.lib.mummu_ep_post_counts(self._h, counts.data_ptr(), sync_table, rank, world, _torch_stream()))
 
@@ -332,9 +336,10 @@ class SparseMoe:
                                       rows_cap, ys_ptr, _torch_stream()))
 
     def ep_combine(self, sync_table, ys_table, ids, w, pos, offsets, dst_base, rank: int, world: int,
-                   cap_rows: int, out) -> None:
+                   cap_rows: int, out, order_ids=None) -> None:
         tokens, top_k = ids.shape
-        _check(L.lib.mummu_ep_combine(self._h, sync_table, ys_table, ids.data_ptr(), w.data_ptr(), pos.data_ptr(),
+        _check(L.lib.mummu_ep_combine(self._h, sync_table, ys_table, ids.data_ptr(),
+                                      None if order_ids is None else order_ids.data_ptr(), w.data_ptr(), pos.data_ptr(),
                                       offsets.data_ptr(), dst_base.data_ptr(), rank, world, tokens, top_k,
                                       cap_rows, out.data_ptr(), _torch_stream()))
 

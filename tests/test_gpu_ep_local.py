@@ -199,3 +199,85 @@ def test_ep_wait_runs_out_and_the_group_recovers(cuda_lib):
         ep.close()
     single.close()
     ws.close()
+
+
+@pytest.mark.parametrize("weights", ["bf16", "q4k"])
+def test_ep_hot_expert_placement_changes_loads_not_results(cuda_lib, weights):
+    """A router with a Zipf bias over 64 experts on 8 ranks: hits -> smoothed hotness -> placement
+    with two spare slots per rank.  The placed group (experts moved between ranks, hot ones held
+    several times) must return bit for bit what the plainly sharded group returns - the same
+    weights give the same numbers wherever they sit - while the busiest rank's rows drop."""
+    import torch
+    from mummu_b200 import ep as epmod, moe, placement as P
+    L = cuda_lib
+    H, I, E, K, world, Tr = 1024, 512, 64, 8, 8, 64
+    cfg = moe.SparseMoeConfig(H, I, E, K)
+    g = torch.Generator(device="cuda").manual_seed(91)
+    rnd = lambda *s: (torch.randn(*s, generator=g, device="cuda") * 0.02)
+    router = rnd(H, E).cpu().numpy()
+    bias = synth.zipf_router_bias(E, 1.0, 1.2, seed=5)
+    if weights == "bf16":
+        act, wdt = L.BF16, L.BF16
+        banks = [rnd(E, I, H).to(torch.bfloat16), rnd(E, I, H).to(torch.bfloat16), rnd(E, H, I).to(torch.bfloat16)]
+        xs = [torch.randn(Tr, H, generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    else:
+        act, wdt = L.F16, L.Q4_K
+        banks = [moe.q4k_quantize_device(rnd(E, I, H)).view(E, -1), moe.q4k_quantize_device(rnd(E, I, H)).view(E, -1),
+                 moe.q4k_quantize_device(rnd(E, H, I)).view(E, -1)]
+        xs = [torch.randn(Tr, H, generator=g, device="cuda").to(torch.float16) for _ in range(world)]
+    ws, group = build_group(torch, L, moe, epmod, cfg, world, act, wdt, banks, router, Tr, bias=bias)
+    ys = run_group(torch, group, ws.views, xs, K, True)
+    torch.cuda.synchronize()
+    hits = np.zeros(E, dtype=np.uint64)
+    for ep in group:
+        ep.moe.sync()
+        hits += ep.take_hits()
+    assert int(hits.sum()) == world * Tr * K
+    hot = P.smooth_hotness([], hits.tolist(), 1.0)
+    plan = P.plan_placement(hot, E, world, E // world + 2)
+    assert max(len(h) for h in plan.hosts) >= 2                       # the head of the curve is held more than once
+    S = plan.slots
+    ws2 = epmod.LocalWorkspaces(0, world, world * Tr * K, H, plan.virtual_experts)
+    placed = []
+    for r in range(world):
+        ep = epmod.ExpertParallelMoe(cfg, device=0, act_dtype=act, weight_dtype=wdt, max_tokens=Tr,
+                                     workspace=ws2.views[r], rank=r, world=world, placement=plan)
+        ep.set_router(router, bias=bias)
+        idx = torch.from_numpy(plan.rank_experts(r)).cuda()
+        ep.set_local_banks(*(b.index_select(0, idx).contiguous() for b in banks))
+        placed.append(ep)
+    states = [ep.stage_route(x, K, True) for ep, x in zip(placed, xs)]
+    for ep, st in zip(placed, states):
+        ep.stage_dispatch(st)
+    rows_placed = [int(st["local_counts"].sum().item()) for st in states]
+    for ep, st in zip(placed, states):
+        ep.stage_experts(st)
+    ys2 = [ep.stage_combine(st) for ep, st in zip(placed, states)]
+    torch.cuda.synchronize()
+    for ep in placed:
+        ep.moe.sync()
+    for r in range(world):
+        assert torch.equal(ys[r], ys2[r])
+    el = E // world
+    rows_plain = [int(hits[r * el:(r + 1) * el].sum()) for r in range(world)]
+    assert sum(rows_placed) == sum(rows_plain) == world * Tr * K
+    assert max(rows_placed) < 0.6 * max(rows_plain)
+    # the routing hits of the placed group are still per real expert
+    hits2 = np.zeros(E, dtype=np.uint64)
+    for ep in placed:
+        hits2 += ep.take_hits()
+    assert np.array_equal(hits, hits2)
+    # a table entry outside the slots is reported, not followed
+    bad = placed[0].table.clone()
+    ids_real, _ = placed[0].router.route_flat(xs[0], K, True)
+    bad[int(ids_real[0, 0].item())] = plan.virtual_experts + 3
+    out = torch.empty_like(ids_real)
+    placed[0].moe.ep_place(ids_real, bad, E, out)
+    with pytest.raises(moe.MoeContractError, match="left its buffer"):
+        placed[0].moe.sync()
+    assert int(out.max().item()) < plan.virtual_experts
+    placed[0].moe.sync()                                              # the report does not stick
+    for ep in placed + group:
+        ep.close()
+    ws.close()
+    ws2.close()

@@ -51,7 +51,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="all",
-                    choices=["all", "olmoe_q4k_decode", "olmoe_bf16_prefill", "olmoe_decode", "ep_qwen3"])
+                    choices=["all", "olmoe_q4k_decode", "olmoe_bf16_prefill", "olmoe_decode", "ep_qwen3", "ep_skew"])
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--ep-layers", type=int, default=48, help="layers of the Qwen3-shaped expert-parallel stack")
@@ -546,26 +546,33 @@ def measure_ep(ctx, shape: dict) -> dict:
     el = e // world
     cfg = moe.SparseMoeConfig(h, i, e, k)
     gen = torch.Generator(device=ctx.device)
-    ws = PeerWorkspace(None, ctx.local_rank, world * T * k, h, e) if world > 1 else None
+    plan = shape.get("placement")                                   # None: contiguous shards
+    bias = shape.get("bias")
+    slots_total = plan.virtual_experts if plan is not None else e
+    mine = plan.rank_experts(rank).tolist() if plan is not None else list(range(rank * el, rank * el + el))
+    ws = PeerWorkspace(None, ctx.local_rank, world * T * k, h, slots_total) if world > 1 else None
     layers = []
     for l in range(NL):
         gen.manual_seed(9000 + l)                                   # router: same on every rank
         router = (torch.randn(h, e, generator=gen, device=ctx.device) * 0.02).cpu().numpy()
-        gen.manual_seed(100000 + 1000 * l + rank)                   # this rank's experts
         if world > 1:
             m = ExpertParallelMoe(cfg, device=ctx.local_rank, act_dtype=act, weight_dtype=wdt, max_tokens=T,
-                                  workspace=ws, scratch_donor=layers[0][0] if layers else None)
+                                  workspace=ws, scratch_donor=layers[0][0] if layers else None, placement=plan)
             handle = m.moe
         else:
             m = cfg.init(device=ctx.local_rank, act_dtype=act, weight_dtype=wdt, max_tokens=T if not layers else 0)
             if layers:
                 m.adopt_scratch(layers[0][0])
             handle = m
-        m.set_router(router)
-        for which, shp in ((L.BANK_GATE, (el, i, h)), (L.BANK_UP, (el, i, h)), (L.BANK_DOWN, (el, h, i))):
-            wt = torch.randn(shp, generator=gen, device=ctx.device) * 0.02
+        m.set_router(router, bias=bias)
+        for which, shp in ((L.BANK_GATE, (i, h)), (L.BANK_UP, (i, h)), (L.BANK_DOWN, (h, i))):
+            parts = []
+            for ex in mine:                                         # an expert's weights follow the expert, not the rank
+                gen.manual_seed(100000 + 1000 * l + 8 * ex + which)
+                parts.append(torch.randn(shp, generator=gen, device=ctx.device) * 0.02)
+            wt = torch.stack(parts)
             handle.set_bank(which, moe.q4k_quantize_device(wt) if q4 else wt.to(tdt))
-            del wt
+            del wt, parts
         layers.append((m, handle))
     gen.manual_seed(777 + rank)
     xs = [torch.randn(T, h, generator=gen, device=ctx.device).to(tdt) for _ in range(min(NL, 8))]
@@ -607,6 +614,19 @@ def measure_ep(ctx, shape: dict) -> dict:
     for _, hd in layers:
         hd.sync()                               # raises if a bounded device-side wait ran out or a row was dropped
 
+    hits = None
+    if shape.get("want_hits"):
+        hits = np.zeros(e, dtype=np.uint64)
+        for m, _ in layers:
+            m.take_hits()                                           # drop what warm-up and timing counted
+        step()
+        torch.cuda.synchronize()
+        for m, _ in layers:
+            hits += m.take_hits()
+        if world > 1:
+            t_h = torch.from_numpy(hits.astype(np.int64)).to(ctx.device)
+            ctx.dist.all_reduce(t_h)
+            hits = t_h.cpu().numpy().astype(np.uint64)
     total_tokens = T * world
     flops = total_tokens * k * 6 * h * i * NL
     out = {"workload": shape["name"], "scaling": shape["scaling"], "hidden": h, "intermediate": i, "experts": e,
@@ -634,6 +654,8 @@ def measure_ep(ctx, shape: dict) -> dict:
                 if name in kern:
                     out[name + "_GBps_per_gpu"] = nv / (kern[name]["avg_us"] * 1e-6) / 1e9
             out["nvlink_bytes_per_gpu_per_layer_each_way"] = nv
+    if hits is not None:
+        out["_hits"] = hits
     for m, _ in reversed(layers):
         m.close()
     torch.cuda.synchronize()
@@ -642,6 +664,34 @@ def measure_ep(ctx, shape: dict) -> dict:
         ws.close()
     torch.cuda.empty_cache()
     return out
+
+
+def measure_ep_skew(ctx) -> dict:
+    """The prefill configuration's skewed router (Zipf bias over 64 experts) sharded over the GPUs:
+    once with contiguous shards, once with the placement planned from the first run's hit counters
+    (experts moved between the ranks, the hottest held on several).  Same tokens, same weights per
+    expert; the outputs are bit-equal (tested), the busiest rank's rows and the step time are not."""
+    from mummu_b200 import placement as P, synth
+    args, world = ctx.args, ctx.world
+    total = 4096
+    bias = synth.zipf_router_bias(E, 1.0)
+    base = dict(hidden=H, inter=I, experts=E, top_k=K, tokens_per_rank=total // world, layers=min(args.ep_layers, 16),
+                q4k=False, scaling="strong", bias=bias)
+    plain = measure_ep(ctx, dict(base, name=f"olmoe_bf16_zipf_ep_T{total}", want_hits=True))
+    hits = plain.pop("_hits")
+    hot = P.smooth_hotness([], [int(v) for v in hits], 1.0)
+    slots = E // world + 2
+    plan = P.plan_placement(hot, E, world, slots)
+    placed = measure_ep(ctx, dict(base, name=f"olmoe_bf16_zipf_ep_T{total}_placed", placement=plan))
+    share = lambda p: float(p.rank_loads(hot).max() * world)
+    keep = ("ms_per_step", "us_per_layer", "tokens_per_s", "gpu_launches_per_step", "kernels_rank0", "clocks")
+    return {"workload": f"olmoe_bf16_zipf_ep_T{total}", "n_gpus": world, "layers_per_step": base["layers"],
+            "zipf_alpha": 1.0, "slots_per_gpu": slots, "experts_per_gpu_plain": E // world,
+            "copies_of_hottest": max(len(hs) for hs in plan.hosts),
+            "experts_held_twice_or_more": int(sum(len(hs) > 1 for hs in plan.hosts)),
+            "busiest_gpu_load_over_fair_share": {"contiguous": share(P.contiguous_placement(E, world)), "placed": share(plan)},
+            "contiguous": {k2: plain[k2] for k2 in keep}, "placed": {k2: placed[k2] for k2 in keep},
+            "speedup": plain["ms_per_step"] / placed["ms_per_step"]}
 
 
 def qwen3_shape(args, world: int) -> dict:
@@ -698,6 +748,8 @@ def main() -> int:
                          "kernels_rank0": r["kernels_rank0"], "cpu_baseline": None})
         if args.workload == "all":
             sub("ep_qwen3", lambda: measure_ep(ctx, qwen3_shape(args, world)))
+            if world > 1:
+                sub("ep_skew", lambda: measure_ep_skew(ctx))
     elif args.workload == "olmoe_bf16_prefill":
         r = measure_prefill(ctx)
         line.update({"metric": METRIC, "value": r["tokens_per_s"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
@@ -718,6 +770,14 @@ def main() -> int:
                      "vs_baseline": None, "dtype": "bf16 x bf16, f32 accumulate", "data": "synthetic",
                      "config": {"workload": r["workload"], "tokens": r["tokens"], "layers_per_step": r["layers_per_step"]},
                      "e2e": r["e2e"], "ep_qwen3": r})
+    elif args.workload == "ep_skew":
+        if world < 2:
+            raise SystemExit("the ep_skew workload shards experts over GPUs: run it with --gpus 2, 4 or 8")
+        r = measure_ep_skew(ctx)
+        line.update({"metric": METRIC, "value": r["placed"]["tokens_per_s"], "unit": UNIT, "n_gpus": world,
+                     "steps": args.steps, "warmup": 3, "ms_per_step": r["placed"]["ms_per_step"], "higher_is_better": True,
+                     "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x bf16, f32 accumulate", "data": "synthetic",
+                     "config": {"workload": r["workload"], "layers_per_step": r["layers_per_step"]}, "ep_skew": r})
     if rank == 0:
         print(json.dumps(line), flush=True)
     if ctx.dist is not None:

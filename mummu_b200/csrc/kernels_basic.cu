@@ -582,6 +582,255 @@ __global__ void __launch_bounds__(e_pad * 8 * SPLIT) router_wide_kernel(RouterAr
     }
 }
 
+// Register-tiled large-T router.  The oracle's dot is 8 independent FMA chains per (token, expert),
+// chain j over k = j, 8 + j, 16 + j, ... in ascending order: eight K = H / 8 matrix products whose
+// inner loop may be tiled freely as long as each chain stays in one thread, in order.  Here warp j
+// of a block owns chain j for a tile of TM * 4 tokens x 64 experts; a thread keeps TM x 8
+// accumulators, so a k-step costs (TM + 8) / 4 shared-memory loads of 16 bytes for TM * 8 FMAs, and
+// the router weight is read from L2 once per TM * 4 tokens instead of once per 8.  Chunks of 64 k
+// are staged three deep (weights by cp.async, tokens converted to f32 and laid out per chain on
+// the way in).  Experts beyond the first 64 take further passes over the same tokens; logits,
+// selection and counters are the same code as in the other router kernels.
+constexpr int RT_KC = 64;                  // k per stage: 8 steps of every chain
+constexpr int RT_XROW = 36;                // floats per (chain, step) row of tokens: 32 + 4 against bank conflicts
+constexpr int RT_XSTAGES = 2;
+
+__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gmem), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// Two independent IEEE f32 FMAs in one instruction (sm_100): halves the issue slots of the k loop.
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+// a token's 8 consecutive values as they sit in memory (converted when they are stored)
+template <typename TX> struct OctetRaw { uint4 r; };
+template <> struct OctetRaw<float> { uint4 r, r2; };
+template <typename TX> __device__ __forceinline__ void load_raw(const TX* p, OctetRaw<TX>& o) {
+    o.r = *reinterpret_cast<const uint4*>(p);
+}
+template <> __device__ __forceinline__ void load_raw<float>(const float* p, OctetRaw<float>& o) {
+    o.r = *reinterpret_cast<const uint4*>(p);
+    o.r2 = *reinterpret_cast<const uint4*>(p + 4);
+}
+__device__ __forceinline__ void octet_f32(const OctetRaw<float>& o, float (&v)[8]) {
+    v[0] = __uint_as_float(o.r.x); v[1] = __uint_as_float(o.r.y); v[2] = __uint_as_float(o.r.z); v[3] = __uint_as_float(o.r.w);
+    v[4] = __uint_as_float(o.r2.x); v[5] = __uint_as_float(o.r2.y); v[6] = __uint_as_float(o.r2.z); v[7] = __uint_as_float(o.r2.w);
+}
+__device__ __forceinline__ void octet_f32(const OctetRaw<__half>& o, float (&v)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&o.r);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const float2 f = __half22float2(h[u]);
+        v[2 * u] = f.x;
+        v[2 * u + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void octet_f32(const OctetRaw<__nv_bfloat16>& o, float (&v)[8]) {
+    // bf16 -> f32 is a shift: no conversion instruction
+    const uint32_t w[4] = {o.r.x, o.r.y, o.r.z, o.r.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        v[2 * u] = __uint_as_float(w[u] << 16);
+        v[2 * u + 1] = __uint_as_float(w[u] & 0xFFFF0000u);
+    }
+}
+
+template <typename TX> __device__ __forceinline__ void load_octet(const TX* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load_octet<float>(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load_octet<__half>(const __half* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const float2 f = __half22float2(h[u]);
+        v[2 * u] = f.x;
+        v[2 * u + 1] = f.y;
+    }
+}
+template <> __device__ __forceinline__ void load_octet<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const float2 f = __bfloat1622float2(h[u]);
+        v[2 * u] = f.x;
+        v[2 * u + 1] = f.y;
+    }
+}
+
+// stages of the asynchronous copies: a 16-token tile spends so little time on a chunk that it needs
+// more chunks in flight to cover the latency of L2
+constexpr int rt_stages(int TM) { return TM == 4 ? 5 : 3; }
+
+static size_t router_tile_smem(int E, int k, int TM, size_t x_size) {
+    const size_t S = rt_stages(TM);
+    const size_t stage = S * RT_KC * 64 * 4 + (size_t)RT_XSTAGES * 8 * 8 * RT_XROW * 4 + S * (TM * 4) * RT_KC * x_size;
+    const size_t parts = (size_t)8 * (TM * 4) * 68 * 4;
+    return (stage > parts ? stage : parts) + (size_t)8 * (E + 2 * k) * 4;
+}
+
+template <typename TX, int TM>
+__global__ void __launch_bounds__(256, 2) router_tile_kernel(RouterArgs a) {
+    constexpr int S = rt_stages(TM);                             // copies in flight: S - 1 chunks ahead
+    constexpr int TT = TM * 4;                                   // tokens per block
+    constexpr int NH = TM / 4;                                   // 4-token groups per thread
+    constexpr int OCT = 8 * (int)sizeof(TX);                     // bytes of 8 consecutive values of a token
+    constexpr size_t STAGE_B = (size_t)S * RT_KC * 64 * 4 + (size_t)RT_XSTAGES * 8 * 8 * RT_XROW * 4 +
+                               (size_t)S * TT * RT_KC * sizeof(TX);
+    constexpr size_t PARTS_B = (size_t)8 * TT * 68 * 4;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* ws = reinterpret_cast<float*>(smem_raw);              // [S][8 chains][8 steps][64 experts]
+    float* xs = ws + S * RT_KC * 64;                    // [2][8 chains][8 steps][RT_XROW tokens]
+    unsigned char* raws = reinterpret_cast<unsigned char*>(xs + RT_XSTAGES * 8 * 8 * RT_XROW);   // [S][TT][64 k] as stored
+    float* parts = reinterpret_cast<float*>(smem_raw);           // after the k loop: [8 chains][TT][68]
+    float* tk = reinterpret_cast<float*>(smem_raw + (STAGE_B > PARTS_B ? STAGE_B : PARTS_B));
+    const int tid = threadIdx.x, lane = tid & 31, j = tid >> 5;
+    const int tg = lane >> 3, eg = lane & 7;
+    const int H = a.H, E = a.E, H8 = H & ~7;
+    const int t0 = blockIdx.x * TT;
+    const TX* x = reinterpret_cast<const TX*>(a.x);
+    const int chunks = H8 / RT_KC;
+    // staging roles: thread -> (token, octet of the chunk) for x; four 16-byte pieces of the weights
+    const int x_oc = tid & 7, x_t = tid >> 3;
+    const bool x_role = x_t < TT;
+    const bool x_valid = x_role && t0 + x_t < a.T;
+    const TX* x_src = x + (size_t)(t0 + (x_valid ? x_t : 0)) * H + x_oc * 8;
+    unsigned char* x_raw = raws + ((size_t)x_t * 8 + x_oc) * OCT;
+
+    for (int e0 = 0; e0 < E; e0 += 64) {
+        unsigned long long acc[TM][4];                           // [token][expert pair]
+#pragma unroll
+        for (int m = 0; m < TM; ++m)
+#pragma unroll
+            for (int n = 0; n < 4; ++n) acc[m][n] = 0ull;
+        // group g of the asynchronous copies: weights of chunk g, tokens (as stored) of chunk g + 1
+        auto stage = [&](int g) {
+            if (g < chunks) {
+                float* dst = ws + (size_t)(g % S) * RT_KC * 64;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int idx = tid + 256 * r, kk = idx >> 4, e4 = (idx & 15) * 4;
+                    const bool ok = e0 + e4 < E;                 // E % 4 == 0: a piece is inside or outside
+                    cp_async16_zfill(dst + ((kk & 7) * 8 + (kk >> 3)) * 64 + e4,
+                                     a.w + (size_t)(g * RT_KC + kk) * E + (ok ? e0 + e4 : 0), ok);
+                }
+            }
+            if (g + 1 < chunks && x_role) {
+                unsigned char* dst = x_raw + (size_t)((g + 1) % S) * TT * RT_KC * sizeof(TX);
+                const TX* src = x_src + (size_t)(g + 1) * RT_KC;
+                cp_async16_zfill(dst, src, x_valid);
+                if (sizeof(TX) == 4) cp_async16_zfill(dst + 16, src + 4, x_valid);
+            }
+            cp_async_commit();
+        };
+        auto store_x = [&](int c, const OctetRaw<TX>& raw) {     // chunk c: converted, one row per (chain, step)
+            float v[8];
+            octet_f32(raw, v);
+            float* dst = xs + (size_t)(c % RT_XSTAGES) * 8 * 8 * RT_XROW;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) dst[(u * 8 + x_oc) * RT_XROW + x_t] = v[u];
+        };
+        OctetRaw<TX> xraw;
+        __syncthreads();                                         // the previous pass is done with the buffers
+#pragma unroll
+        for (int g = 0; g < S - 1; ++g) stage(g);
+        if (x_role) {
+            load_raw<TX>(x_src, xraw);
+            if (!x_valid) xraw = OctetRaw<TX>{};
+            store_x(0, xraw);
+        }
+        cp_async_wait<S - 2>();
+        __syncthreads();
+        for (int c = 0; c < chunks; ++c) {
+            stage(c + S - 1);
+            if (c + 1 < chunks && x_role) {                      // landed with group c
+                const unsigned char* src = x_raw + (size_t)((c + 1) % S) * TT * RT_KC * sizeof(TX);
+                xraw.r = *reinterpret_cast<const uint4*>(src);
+                if constexpr (sizeof(TX) == 4) xraw.r2 = *reinterpret_cast<const uint4*>(src + 16);
+                store_x(c + 1, xraw);
+            }
+            const float* wj = ws + (size_t)(c % S) * RT_KC * 64 + (size_t)j * 8 * 64;
+            const float* xj = xs + (size_t)(c % RT_XSTAGES) * 8 * 8 * RT_XROW + (size_t)j * 8 * RT_XROW;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const ulonglong2 w0 = *reinterpret_cast<const ulonglong2*>(wj + i * 64 + eg * 4);
+                const ulonglong2 w1 = *reinterpret_cast<const ulonglong2*>(wj + i * 64 + 32 + eg * 4);
+                const unsigned long long wp[4] = {w0.x, w0.y, w1.x, w1.y};
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    const float4 xq = *reinterpret_cast<const float4*>(xj + i * RT_XROW + h * 16 + tg * 4);
+                    const unsigned long long xp[4] = {pack2(xq.x, xq.x), pack2(xq.y, xq.y), pack2(xq.z, xq.z), pack2(xq.w, xq.w)};
+#pragma unroll
+                    for (int m = 0; m < 4; ++m)
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) acc[h * 4 + m][n] = fma2(xp[m], wp[n], acc[h * 4 + m][n]);
+                }
+            }
+            cp_async_wait<S - 2>();
+            __syncthreads();
+        }
+        cp_async_wait<0>();
+        __syncthreads();
+        // chain partials -> shared memory (over the staging buffers), then the fixed tree
+#pragma unroll
+        for (int h = 0; h < NH; ++h)
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                float* dst = parts + ((size_t)j * TT + h * 16 + tg * 4 + m) * 68;
+                *reinterpret_cast<ulonglong2*>(dst + eg * 4) = make_ulonglong2(acc[h * 4 + m][0], acc[h * 4 + m][1]);
+                *reinterpret_cast<ulonglong2*>(dst + 32 + eg * 4) = make_ulonglong2(acc[h * 4 + m][2], acc[h * 4 + m][3]);
+            }
+        __syncthreads();
+        for (int o = tid; o < TT * 64; o += 256) {
+            const int tt = o >> 6, el = o & 63, e2 = e0 + el, t = t0 + tt;
+            if (t < a.T && e2 < E) {
+                float q[8];
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) q[jj] = parts[((size_t)jj * TT + tt) * 68 + el];
+                float sacc = __fadd_rn(__fadd_rn(__fadd_rn(q[0], q[4]), __fadd_rn(q[1], q[5])),
+                                       __fadd_rn(__fadd_rn(q[2], q[6]), __fadd_rn(q[3], q[7])));
+                for (int i = H8; i < H; ++i)
+                    sacc = __fmaf_rn(to_f32(x[(size_t)t * H + i]), a.w[(size_t)i * E + e2], sacc);
+                if (a.bias) sacc = __fadd_rn(sacc, a.bias[e2]);
+                a.logits[(size_t)t * E + e2] = sacc;             // the selection reads them back (L1 bypass)
+            }
+        }
+    }
+    __threadfence_block();
+    __syncthreads();
+    const int per_warp = E + 2 * a.k;
+    for (int tt = j; tt < TT; tt += 8) {
+        const int t = t0 + tt;
+        float* sm_v = tk + (size_t)j * per_warp;
+        if (t < a.T) {
+            if (E <= 64) warp_softmax_topk<2>(a, t, sm_v, sm_v + E, reinterpret_cast<int32_t*>(sm_v + E + a.k));
+            else if (E <= 128) warp_softmax_topk<4>(a, t, sm_v, sm_v + E, reinterpret_cast<int32_t*>(sm_v + E + a.k));
+            else warp_softmax_topk<R_MAXV>(a, t, sm_v, sm_v + E, reinterpret_cast<int32_t*>(sm_v + E + a.k));
+        }
+    }
+}
+
 static size_t router_wide_smem(int H, int E, int e_pad, int k, int nwarps, int RW_TT) {
     const size_t row = (size_t)((H & ~7) >> 3) + 4;
     return (RW_TT * 8 * row + (size_t)RW_TT * e_pad * 8 + (size_t)RW_TT * E + (size_t)nwarps * (E + 2 * k)) * 4;
@@ -596,6 +845,22 @@ static size_t router_smem(int H, int E, int k, int TT) {
 template <typename TX>
 static int launch_router_t(MummuMoe* m, RouterArgs& a, cudaStream_t s) {
     const int e_pad = (a.E + 31) & ~31;
+    if (a.T >= 256 && a.E > 32 && a.E % 4 == 0 && (a.H & ~7) % RT_KC == 0 && a.H >= RT_KC && !m->sw.router_plain &&
+        (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (a.H * sizeof(TX)) % 16 == 0) {
+        // 32-token tiles while they still give every SM two blocks; 16-token tiles below that
+        const bool big = (a.T + 31) / 32 >= 2 * 148;
+        const size_t smem = router_tile_smem(a.E, a.k, big ? 8 : 4, sizeof(TX));
+        LaunchScope scope(m, s, "router");
+        if (big) {
+            MUMMU_CUDA_TRY(allow_big_smem(router_tile_kernel<TX, 8>, m->cfg.device));
+            router_tile_kernel<TX, 8><<<(a.T + 31) / 32, 256, smem, s>>>(a);
+        } else {
+            MUMMU_CUDA_TRY(allow_big_smem(router_tile_kernel<TX, 4>, m->cfg.device));
+            router_tile_kernel<TX, 4><<<(a.T + 15) / 16, 256, smem, s>>>(a);
+        }
+        MUMMU_CUDA_TRY(cudaGetLastError());
+        return MUMMU_OK;
+    }
     if (a.T >= 256 && e_pad <= 128) {
         // up to 64 experts: 512 threads with 128 registers each take 16 tokens per block; wider
         // routers run 1024 threads (64 registers) and take 8

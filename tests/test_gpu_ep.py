@@ -34,10 +34,21 @@ def _worker(rank, world, port, q, act, wdt_name):
         el = E // world
         cfg = moe.SparseMoeConfig(H, I, E, K)
         from mummu_b200.ep import PeerWorkspace
-        ws = PeerWorkspace(None, rank, world * T * K, H, E) if act == "p2p" else None
-        ep = ExpertParallelMoe(cfg, device=rank, act_dtype=act_code, weight_dtype=wcode, max_tokens=T, workspace=ws)
-        ep.set_router(router)
-        sl = slice(rank * el, (rank + 1) * el)
+        bias, plan = None, None
+        if act == "placed":
+            # a skewed router and a placement with two spare slots per rank: experts move between the
+            # ranks and the hottest are held on both
+            from mummu_b200 import placement as P
+            bias = synth.zipf_router_bias(E, 1.0, 1.5, seed=3)
+            hot = np.exp(bias.astype(np.float64))
+            plan = P.plan_placement(hot / hot.sum(), E, world, el + 2)
+            assert max(len(h) for h in plan.hosts) == 2
+        slots_total = plan.virtual_experts if plan else E
+        ws = PeerWorkspace(None, rank, world * T * K, H, slots_total) if act != "nccl" else None
+        ep = ExpertParallelMoe(cfg, device=rank, act_dtype=act_code, weight_dtype=wcode, max_tokens=T, workspace=ws,
+                               placement=plan)
+        ep.set_router(router, bias=bias)
+        sl = plan.rank_experts(rank) if plan else slice(rank * el, (rank + 1) * el)
         ep.set_local_banks(enc(gate[sl]), enc(up[sl]), enc(down[sl]))
         xd = torch.from_numpy(x).cuda().to(tdt)
         y_ep = ep.forward(xd, K, False)
@@ -45,7 +56,7 @@ def _worker(rank, world, port, q, act, wdt_name):
         ep.moe.sync()                      # raises if a bounded device-side wait ran out
         # the same layer, all experts on this GPU
         single = cfg.init(device=rank, act_dtype=act_code, weight_dtype=wcode, max_tokens=T)
-        single.set_router(router)
+        single.set_router(router, bias=bias)
         single.set_banks(enc(gate), enc(up), enc(down))
         y_one = single.forward(xd, K, False)
         single.sync()
@@ -61,7 +72,7 @@ def _worker(rank, world, port, q, act, wdt_name):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["nccl", "p2p"])
+@pytest.mark.parametrize("mode", ["nccl", "p2p", "placed"])
 @pytest.mark.parametrize("wdt_name", ["bf16", "q4k"])
 def test_expert_parallel_matches_single_gpu(cuda_lib, wdt_name, mode):
     import torch

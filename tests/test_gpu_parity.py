@@ -140,7 +140,11 @@ def test_router_known_answers_on_device(M, cuda_lib):
 
 @pytest.mark.parametrize("T,H,E,K,norm,act", [(16, 2048, 64, 8, False, "f32"), (333, 2048, 64, 8, True, "f32"),
                                               (4096, 2048, 64, 8, False, "bf16"), (64, 2048, 64, 8, False, "f16"),
-                                              (257, 2048, 128, 8, False, "f32"), (7, 100, 20, 5, True, "f32")])
+                                              (257, 2048, 128, 8, False, "f32"), (7, 100, 20, 5, True, "f32"),
+                                              # the register-tiled kernel: 32-token tiles and two expert passes;
+                                              # a partial second pass with a k tail; f16 with a ragged last tile
+                                              (9601, 2048, 128, 8, True, "bf16"), (300, 2116, 72, 6, True, "f32"),
+                                              (1027, 1024, 64, 8, False, "f16")])
 def test_routing_bit_exact(M, cuda_lib, T, H, E, K, norm, act):
     L = cuda_lib
     router = synth.normal(synth.layer_seed(1, 0, 0), (H, E), 0.02)

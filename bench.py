@@ -650,7 +650,7 @@ def measure_ep(ctx, shape: dict) -> dict:
         if world > 1:
             # rows that leave the GPU: (world - 1) / world of T * k rows of hidden 16-bit values, each way
             nv = T * k * h * 2 * (world - 1) / world
-            for name in ("ep_dispatch", "ep_combine"):
+            for name in ("ep_dispatch", "ep_return"):
                 if name in kern:
                     out[name + "_GBps_per_gpu"] = nv / (kern[name]["avg_us"] * 1e-6) / 1e9
             out["nvlink_bytes_per_gpu_per_layer_each_way"] = nv

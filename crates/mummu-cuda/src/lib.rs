@@ -112,13 +112,12 @@ pub mod sys {
                                  peer_sync: *const *mut c_void, peer_recv: *const *mut c_void, rank: i32, world: i32,
                                  rows: i32, cap_rows: i64, dst_base: *mut i32, local_counts: *mut i32,
                                  stream: *mut c_void) -> i32;
-        pub fn mummu_ep_experts(moe: *mut MummuMoe, peer_sync: *const *mut c_void, rank: i32, world: i32,
-                                recv_own: *const c_void, local_counts: *const i32, rows_cap: i64, ys_own: *mut c_void,
-                                stream: *mut c_void) -> i32;
-        pub fn mummu_ep_combine(moe: *mut MummuMoe, peer_sync: *const *mut c_void, peer_ys: *const *mut c_void,
-                                ids: *const i32, order_ids: *const i32, w: *const f32, pos: *const i32, offsets: *const i32,
-                                dst_base: *const i32, rank: i32, world: i32, tokens: i32, top_k: i32, cap_rows: i64,
-                                out: *mut c_void, stream: *mut c_void) -> i32;
+        pub fn mummu_ep_experts(moe: *mut MummuMoe, peer_sync: *const *mut c_void, peer_back: *const *mut c_void,
+                                rank: i32, world: i32, recv_own: *const c_void, local_counts: *const i32, rows_cap: i64,
+                                ys_own: *mut c_void, back_rows: i64, stream: *mut c_void) -> i32;
+        pub fn mummu_ep_combine(moe: *mut MummuMoe, peer_sync: *const *mut c_void, back_own: *const c_void,
+                                ids: *const i32, order_ids: *const i32, w: *const f32, pos: *const i32, rank: i32,
+                                world: i32, tokens: i32, top_k: i32, out: *mut c_void, stream: *mut c_void) -> i32;
         // parity taps, counters, profiling
         pub fn mummu_moe_dequant_bank(moe: *mut MummuMoe, which: i32, expert: i32, out: *mut f32) -> i32;
         pub fn mummu_moe_take_hits(moe: *mut MummuMoe, per_expert: *mut u64) -> i32;

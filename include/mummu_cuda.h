@@ -223,12 +223,15 @@ int32_t mummu_ep_free(void* ptr);
  *                         row that would land at or beyond cap_rows is dropped and reported
  *                         (MUMMU_ERR_CONTRACT from the next mummu_moe_sync).
  *   mummu_ep_experts      stage 3: waits for every rank's rows; runs this rank's experts over its
- *                         receive buffer into its output buffer ys_own ([cap_rows, hidden]).
- *   mummu_ep_combine      stage 4: waits for every rank's outputs; mummu_moe_combine reading each
- *                         expert output row from its owner's buffer peer_ys[owner] with peer loads.
- *                         order_ids (NULL: ids) gives the expert id of each pair where `ids` are
- *                         bank slots (mummu_ep_place): a token's terms are summed in ascending
- *                         expert id either way. */
+ *                         receive buffer into its private output buffer ys_own ([rows_cap, hidden]),
+ *                         then stores every output row into the buffer of the rank the row came
+ *                         from, peer_back[source] ([back_rows, hidden]: that rank's (token, slot)
+ *                         pairs in its own mummu_moe_permute order) with peer stores.  Both
+ *                         directions push: no load crosses NVLink.
+ *   mummu_ep_combine      stage 4: waits for every rank's outputs; mummu_moe_combine over the own
+ *                         buffer back_own.  order_ids (NULL: ids) gives the expert id of each pair
+ *                         where `ids` are bank slots (mummu_ep_place): a token's terms are summed
+ *                         in ascending expert id either way. */
 size_t mummu_ep_sync_bytes(int32_t world, int32_t experts);
 /* Hot-expert placement (nn/moe.rs:1527-1535 hands the hit counters to the planner; tier.rs:353-431
  * plans from them).  A group whose handles are created over `world * slots_per_rank` bank SLOTS
@@ -248,14 +251,13 @@ int32_t mummu_ep_dispatch(MummuMoe* moe, const void* x, const int32_t* row_token
                           const int32_t* offsets, void* const* peer_sync, void* const* peer_recv,
                           int32_t rank, int32_t world, int32_t rows, int64_t cap_rows,
                           int32_t* dst_base, int32_t* local_counts, void* stream);
-int32_t mummu_ep_experts(MummuMoe* moe, void* const* peer_sync, int32_t rank, int32_t world,
-                         const void* recv_own, const int32_t* local_counts, int64_t rows_cap,
-                         void* ys_own, void* stream);
-int32_t mummu_ep_combine(MummuMoe* moe, void* const* peer_sync, void* const* peer_ys,
-                         const int32_t* ids, const int32_t* order_ids, const float* w, const int32_t* pos,
-                         const int32_t* offsets, const int32_t* dst_base, int32_t rank,
-                         int32_t world, int32_t tokens, int32_t top_k, int64_t cap_rows, void* out,
-                         void* stream);
+int32_t mummu_ep_experts(MummuMoe* moe, void* const* peer_sync, void* const* peer_back, int32_t rank,
+                         int32_t world, const void* recv_own, const int32_t* local_counts,
+                         int64_t rows_cap, void* ys_own, int64_t back_rows, void* stream);
+int32_t mummu_ep_combine(MummuMoe* moe, void* const* peer_sync, const void* back_own,
+                         const int32_t* ids, const int32_t* order_ids, const float* w,
+                         const int32_t* pos, int32_t rank, int32_t world, int32_t tokens,
+                         int32_t top_k, void* out, void* stream);
 
 /* -------- parity taps and counters ----------------------------------------------------------- */
 

@@ -317,9 +317,13 @@ int32_t mummu_moe_create(const MummuMoeConfig* cfg, MummuMoe** out) {
         if ((rc = dev_alloc(&m->offsets, (size_t)cfg->experts + 1))) break;
         if ((rc = dev_alloc(&m->active, (size_t)cfg->experts))) break;
         if ((rc = dev_alloc(&m->n_active, 1))) break;
+        if ((rc = dev_alloc(&m->ret_seg, (size_t)cfg->experts_local * 16 + 1))) break;
+        if ((rc = dev_alloc(&m->ret_dst, (size_t)cfg->experts_local * 16))) break;
         if ((rc = dev_alloc(&m->hits, (size_t)cfg->experts))) break;
         if ((rc = dev_alloc(&m->status, 1))) break;
         cudaMemset(m->hits, 0, sizeof(unsigned long long) * cfg->experts);
+        cudaMemset(m->ret_seg, 0, sizeof(int32_t) * ((size_t)cfg->experts_local * 16 + 1));
+        cudaMemset(m->ret_dst, 0, sizeof(int32_t) * (size_t)cfg->experts_local * 16);
         cudaMemset(m->status, 0, sizeof(int32_t));
         if (cudaHostAlloc((void**)&m->status_host, sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess) {
             m->status_host = nullptr;       // pageable reads still work
@@ -346,7 +350,7 @@ int32_t mummu_moe_destroy(MummuMoe* m) {
         for (int b = 0; b < 3; ++b) cudaFree(m->bank[b]);
         cudaFree(m->counts); cudaFree(m->offsets); cudaFree(m->hits); cudaFree(m->status);
         if (m->status_host) cudaFreeHost(m->status_host);
-        cudaFree(m->active); cudaFree(m->n_active);
+        cudaFree(m->active); cudaFree(m->n_active); cudaFree(m->ret_seg); cudaFree(m->ret_dst);
         for (auto& p : m->prof.pending) { cudaEventDestroy(p.a); cudaEventDestroy(p.b); }
         for (auto e : m->prof.pool) cudaEventDestroy(e);
         if (m->stream) cudaStreamDestroy(m->stream);

@@ -210,6 +210,18 @@ struct MummuMoe {
     int32_t* offsets = nullptr;     // [experts + 1]
     int32_t* active = nullptr;      // [experts] ids of experts with rows this call
     int32_t* n_active = nullptr;    // [1]
+    // expert-parallel return path: the local rows as segments (local expert, source rank)
+    int32_t* ret_seg = nullptr;     // [experts_local * 16 + 1] first local row of every segment
+    int32_t* ret_dst = nullptr;     // [experts_local * 16] the segment's first row in its source's buffer
+    // set by the expert-parallel experts stage around its call of the expert kernels: where the
+    // down projection may store its rows directly (peer buffers); `used` tells the stage whether
+    // the kernel that ran took the offer
+    struct {
+        bool offered = false, used = false;
+        int world = 0;
+        int64_t back_rows = 0;
+        void* back[16] = {};
+    } scatter;
     int32_t* row_token = nullptr;   // [tokens * k]
     int32_t* pos = nullptr;         // [tokens * k]
     void* xs = nullptr;             // gathered rows [tokens * k, hidden] act dtype (tensor path)

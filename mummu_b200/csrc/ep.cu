@@ -3,10 +3,13 @@
 // path (its devices exchange through host memory: crates/mummu/src/backend.rs:128-143,
 // nn/moe.rs:1219-1272).
 //
-// Every rank owns a contiguous block of experts and three peer-visible buffers:
+// Every rank owns a contiguous block of experts, three peer-visible buffers and a private one:
 //   recv_x [cap_rows, hidden]  rows routed to its experts, expert-major (sources in rank order)
-//   ys     [cap_rows, hidden]  its experts' outputs for those rows
+//   back   [own_rows, hidden]  the expert outputs of ITS OWN (token, slot) pairs, in its sorted order
 //   sync   flags, epochs and the gathered per-expert row counts (layout below)
+//   ys     [cap_rows, hidden]  its experts' outputs for the received rows (private)
+// Both directions PUSH: remote traffic is stores only (a store needs no round trip; loads over
+// NVLink were three times slower here for the same bytes).
 //
 // One layer on one rank is four stages, each signalling the next ONE WAY: the producer's last
 // block stores its epoch into a flag in every peer's sync block (system-scope release), and the
@@ -19,9 +22,10 @@
 //   dispatch : wait S1; plan from the gathered counts (where each sorted row lives in its owner's
 //              buffers; rows, offsets and work order of the local experts); rows -> owners' recv_x
 //              with 16-byte peer stores; S2
-//   experts  : wait S2; the local experts over recv_x -> ys; S3
+//   experts  : wait S2; the local experts over recv_x -> ys; every output row -> its source rank's
+//              `back` buffer at the row's place in the source's sorted order, 16-byte peer stores; S3
 //   combine  : wait S3; per token, ascending expert id, scaled = w * y; out += scaled, y read from
-//              the owner's ys with peer loads
+//              the own `back` buffer
 // Plain peer loads and stores only.  Every wait is bounded: when it runs out the kernel raises
 // the status word, skips its data movement and returns.
 #include <cstring>
@@ -126,6 +130,19 @@ __global__ void __launch_bounds__(256) ep_post_counts_kernel(const int32_t* coun
     if (threadIdx.x < 32) ep_signal(sync, rank, world, EP_CH_COUNTS);
 }
 
+// One warp copies one row of `vec` 16-byte pieces; up to eight loads are issued before the first store.
+__device__ __forceinline__ void copy_row(const uint4* __restrict__ src, uint4* __restrict__ dst, int vec, int lane) {
+    for (int i0 = lane; i0 < vec; i0 += 256) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (i0 + 32 * u < vec) v[u] = src[i0 + 32 * u];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (i0 + 32 * u < vec) dst[i0 + 32 * u] = v[u];
+    }
+}
+
 // ---- dispatch ----------------------------------------------------------------------------------
 struct DispatchArgs {
     const uint4* x;               // [tokens, hidden] 16-bit
@@ -139,6 +156,8 @@ struct DispatchArgs {
     int32_t* local_offsets;       // out [EL + 1]
     int32_t* active;              // out [EL]: local experts with rows, heaviest first
     int32_t* n_active;            // out [1]
+    int32_t* ret_seg;             // out [EL * world + 1]: first local row of segment (local expert, source)
+    int32_t* ret_dst;             // out [EL * world]: that segment's first row in the source's sorted order
     uint32_t wait_polls;
     int32_t* status;
 };
@@ -191,28 +210,42 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
                 for (int i = 0; i < a.EL; ++i) nz += s_lc[i] > 0;
                 *a.n_active = nz;
             }
-        }
-        __shared__ int s_e;
-        for (int64_t p = blockIdx.x; p < a.rows; p += gridDim.x) {
-            if (threadIdx.x == 0) {
-                int lo = 0, hi = a.E;                          // last e with offsets[e] <= p
-                while (hi - lo > 1) {
-                    const int mid = (lo + hi) >> 1;
-                    if (a.offsets[mid] <= p) lo = mid; else hi = mid;
-                }
-                s_e = lo;
+            // the way back: local rows as segments (local expert, source rank), and where a
+            // segment starts in its source's sorted order (the source's rows of earlier experts)
+            for (int g = threadIdx.x; g < a.EL * a.world; g += blockDim.x) {
+                const int le = g / a.world, s = g - le * a.world, e = a.rank * a.EL + le;
+                int first = 0;
+                for (int i = 0; i < le; ++i) first += s_lc[i];
+                for (int s2 = 0; s2 < s; ++s2) first += all_counts[s2 * a.E + e];
+                int before = 0;
+                for (int e2 = 0; e2 < e; ++e2) before += all_counts[s * a.E + e2];
+                a.ret_seg[g] = first;
+                a.ret_dst[g] = before;
+                if (g == a.EL * a.world - 1) a.ret_seg[g + 1] = first + all_counts[s * a.E + e];
             }
-            __syncthreads();
-            const int e = s_e;
-            const int64_t drow = (int64_t)s_base[e] + (p - a.offsets[e]);
+        }
+        // a warp per row: the row's expert from the offsets (shared memory), then the row in
+        // 16-byte pieces, eight in flight per lane
+        int32_t* s_off = s_lc + a.EL;                            // [E + 1]
+        for (int e = threadIdx.x; e <= a.E; e += blockDim.x) s_off[e] = a.offsets[e];
+        __syncthreads();
+        const int lane = threadIdx.x & 31;
+        const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+        for (int64_t p = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < a.rows; p += warps) {
+            int lo = 0, hi = a.E;                                // last e with offsets[e] <= p
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (s_off[mid] <= p) lo = mid; else hi = mid;
+            }
+            const int e = lo;
+            const int64_t drow = (int64_t)s_base[e] + (p - s_off[e]);
             if (drow >= 0 && drow < a.cap_rows) {
                 const uint4* src = a.x + (size_t)a.row_token[p] * a.vec_per_row;
                 uint4* dst = reinterpret_cast<uint4*>(a.recv.ptr[e / a.EL]) + (size_t)drow * a.vec_per_row;
-                for (int i = threadIdx.x; i < a.vec_per_row; i += blockDim.x) dst[i] = src[i];
-            } else if (threadIdx.x == 0) {
+                copy_row(src, dst, a.vec_per_row, lane);
+            } else if (lane == 0) {
                 atomicOr(a.status, STATUS_BOUNDS);               // the owner's buffer is too small: row dropped
             }
-            __syncthreads();
         }
     }
     if (ep_last_block(own + EP_W_DONE + 0)) {
@@ -232,62 +265,37 @@ __global__ void __launch_bounds__(32) ep_signal_kernel(PeerTable sync, int rank,
     ep_signal(sync, rank, world, ch);
 }
 
-// ---- combine -----------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(256) ep_combine_kernel(PeerTable sync, PeerTable ys, const int32_t* ids,
-                                                         const int32_t* order_ids, const float* w, const int32_t* pos, const int32_t* offsets,
-                                                         const int32_t* dst_base, int rank, int world, int top_k, int H,
-                                                         int EL, int64_t cap_rows, uint32_t wait_polls, int32_t* status,
-                                                         T* out) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const T** s_row = reinterpret_cast<const T**>(smem_raw);
-    float* s_w = reinterpret_cast<float*>(s_row + top_k);
-    int32_t* own = reinterpret_cast<int32_t*>(sync.ptr[rank]);
-    const bool ok = ep_wait(sync, rank, world, EP_CH_OUT, wait_polls, status);
-    if (ok) {
-        const int64_t t = blockIdx.x;
-        for (int r = threadIdx.x; r < top_k; r += blockDim.x) {
-            // summed in ascending EXPERT id (nn/moe.rs:296-328); with a placement `ids` are bank
-            // slots and the expert ids come separately, so that the order does not follow the slots
-            const int id = ids[t * top_k + r];
-            const int key = order_ids[t * top_k + r];
-            int rk = 0;
-            for (int q = 0; q < top_k; ++q) {
-                const int other = order_ids[t * top_k + q];
-                rk += (other < key || (other == key && q < r)) ? 1 : 0;
-            }
-            const int64_t drow = (int64_t)dst_base[id] + (pos[t * top_k + r] - offsets[id]);
-            const bool inside = drow >= 0 && drow < cap_rows;
-            if (!inside) atomicOr(status, STATUS_BOUNDS);
-            s_row[rk] = inside ? reinterpret_cast<const T*>(ys.ptr[id / EL]) + (size_t)drow * H : nullptr;
-            s_w[rk] = w[t * top_k + r];
+// ---- return: expert outputs -> the ranks their tokens live on ----------------------------------
+__global__ void __launch_bounds__(256) ep_return_kernel(const uint4* ys, PeerTable sync, PeerTable back, const int32_t* ret_seg,
+                                                        const int32_t* ret_dst, int rank, int world, int EL,
+                                                        int vec_per_row, int64_t ys_rows, int64_t back_rows, int32_t* status) {
+    extern __shared__ int32_t s_dyn[];
+    const int nseg = EL * world;
+    int32_t* s_seg = s_dyn;                                      // [nseg + 1]
+    int32_t* s_dst = s_seg + nseg + 1;                           // [nseg]
+    for (int g = threadIdx.x; g <= nseg; g += blockDim.x) s_seg[g] = ret_seg[g];
+    for (int g = threadIdx.x; g < nseg; g += blockDim.x) s_dst[g] = ret_dst[g];
+    __syncthreads();
+    const int64_t rows = min((int64_t)s_seg[nseg], ys_rows);
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+        int lo = 0, hi = nseg;                                   // last segment that starts at or before r
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_seg[mid] <= r) lo = mid; else hi = mid;
         }
-        __syncthreads();
-        for (int h = (blockIdx.y * blockDim.x + threadIdx.x) * 8; h < H; h += gridDim.y * blockDim.x * 8) {
-            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int r0 = 0; r0 < top_k; r0 += 4) {
-                uint4 raw[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (r0 + u < top_k)
-                        raw[u] = s_row[r0 + u] ? *reinterpret_cast<const uint4*>(s_row[r0 + u] + h) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (r0 + u < top_k) {
-                        const T* v = reinterpret_cast<const T*>(&raw[u]);
-                        const float wv = s_w[r0 + u];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(wv, to_f32(v[i])));
-                    }
-            }
-            uint4 o;
-            T* ov = reinterpret_cast<T*>(&o);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ov[i] = from_f32<T>(acc[i]);
-            *reinterpret_cast<uint4*>(out + t * H + h) = o;
+        const int s = lo % world;
+        const int64_t drow = (int64_t)s_dst[lo] + (r - s_seg[lo]);
+        if (drow >= 0 && drow < back_rows) {
+            copy_row(ys + (size_t)r * vec_per_row, reinterpret_cast<uint4*>(back.ptr[s]) + (size_t)drow * vec_per_row,
+                     vec_per_row, lane);
+        } else if (lane == 0) {
+            atomicOr(status, STATUS_BOUNDS);
         }
     }
-    if (ep_last_block(own + EP_W_DONE + 1) && threadIdx.x == 0) own[EP_W_WAIT + EP_CH_OUT] += 1;
+    int32_t* own = reinterpret_cast<int32_t*>(sync.ptr[rank]);
+    if (ep_last_block(own + EP_W_DONE + 2) && threadIdx.x < 32) ep_signal(sync, rank, world, EP_CH_OUT);
 }
 
 // Placement: a routed expert id becomes the id of the bank slot that serves it for this rank's
@@ -451,23 +459,29 @@ int32_t mummu_ep_dispatch(MummuMoe* m, const void* x, const int32_t* row_token, 
     a.local_offsets = m->offsets;
     a.active = m->active;
     a.n_active = m->n_active;
+    a.ret_seg = m->ret_seg;
+    a.ret_dst = m->ret_dst;
     a.wait_polls = wait_polls_of(m);
     a.status = m->status;
     // even a rank without rows takes part: its block plans the local experts and signals
-    const int64_t blocks = rows < 1 ? 1 : (rows < 148 * 16 ? rows : 148 * 16);
-    const size_t smem = ((size_t)world * a.E + a.E + a.EL) * sizeof(int32_t);
+    const int64_t blocks = rows < 8 ? 1 : (rows / 8 < 148 * 8 ? rows / 8 : 148 * 8);     // a warp per row
+    const size_t smem = ((size_t)world * a.E + a.E + a.EL + a.E + 1) * sizeof(int32_t);
     LaunchScope scope(m, s, "ep_dispatch");
     ep_dispatch_kernel<<<(unsigned)blocks, 256, smem, s>>>(a);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }
 
-int32_t mummu_ep_experts(MummuMoe* m, void* const* peer_sync, int32_t rank, int32_t world, const void* recv_own,
-                         const int32_t* local_counts, int64_t rows_cap, void* ys_own, void* stream) {
-    MUMMU_REQUIRE(m && peer_sync && recv_own && local_counts && ys_own, "mummu_ep_experts: null argument");
+int32_t mummu_ep_experts(MummuMoe* m, void* const* peer_sync, void* const* peer_back, int32_t rank, int32_t world,
+                         const void* recv_own, const int32_t* local_counts, int64_t rows_cap, void* ys_own,
+                         int64_t back_rows, void* stream) {
+    MUMMU_REQUIRE(m && peer_sync && peer_back && recv_own && local_counts && ys_own, "mummu_ep_experts: null argument");
     int rc = ep_check_ranks(m, rank, world, "mummu_ep_experts");
     if (rc) return rc;
-    MUMMU_REQUIRE(rows_cap >= 0 && rows_cap <= INT32_MAX, "mummu_ep_experts: rows_cap %lld", (long long)rows_cap);
+    MUMMU_REQUIRE(rows_cap >= 0 && rows_cap <= INT32_MAX && back_rows >= 0, "mummu_ep_experts: rows_cap %lld, back_rows %lld",
+                  (long long)rows_cap, (long long)back_rows);
+    MUMMU_REQUIRE(dtype_size(m->cfg.act_dtype) == 2 && m->cfg.hidden % 8 == 0,
+                  "mummu_ep_experts: 16-bit activations with hidden %% 8 == 0 only");
     cudaStream_t s;
     const PeerTable t = peer_table(peer_sync, world);
     {
@@ -477,21 +491,39 @@ int32_t mummu_ep_experts(MummuMoe* m, void* const* peer_sync, int32_t rank, int3
         ep_wait_kernel<<<1, 32, 0, s>>>(t, rank, world, EP_CH_ROWS, wait_polls_of(m), m->status);
         MUMMU_CUDA_TRY(cudaGetLastError());
     }
-    // the dispatch stage left the local experts' offsets and work order in the handle
-    if ((rc = mummu_moe_experts_planned(m, recv_own, local_counts, (int32_t)rows_cap, ys_own, s))) return rc;
+    // the dispatch stage left the local experts' offsets and work order in the handle; the down
+    // projection is offered the peers' buffers and, where the tensor-core kernel runs, stores its
+    // output rows there itself (the transfer then hides under the GEMM)
+    m->scatter.offered = true;
+    m->scatter.used = false;
+    m->scatter.world = world;
+    m->scatter.back_rows = back_rows;
+    for (int r = 0; r < world; ++r) m->scatter.back[r] = peer_back[r];
+    rc = mummu_moe_experts_planned(m, recv_own, local_counts, (int32_t)rows_cap, ys_own, s);
+    m->scatter.offered = false;
+    if (rc) return rc;
     std::lock_guard<std::mutex> lock(m->mu);
-    LaunchScope scope(m, s, "ep_signal_out");
-    ep_signal_kernel<<<1, 32, 0, s>>>(t, rank, world, EP_CH_OUT);
+    if (m->scatter.used) {
+        LaunchScope scope(m, s, "ep_signal_out");
+        ep_signal_kernel<<<1, 32, 0, s>>>(t, rank, world, EP_CH_OUT);
+        MUMMU_CUDA_TRY(cudaGetLastError());
+        return MUMMU_OK;
+    }
+    // even a rank whose experts got no rows takes part: its last block signals
+    const int64_t blocks = rows_cap < 8 ? 1 : (rows_cap / 8 < 148 * 8 ? rows_cap / 8 : 148 * 8);
+    const int nseg = m->cfg.experts_local * world;
+    LaunchScope scope(m, s, "ep_return");
+    ep_return_kernel<<<(unsigned)blocks, 256, (size_t)(2 * nseg + 1) * sizeof(int32_t), s>>>(
+        (const uint4*)ys_own, t, peer_table(peer_back, world), m->ret_seg, m->ret_dst, rank, world, m->cfg.experts_local,
+        m->cfg.hidden * 2 / 16, rows_cap, back_rows, m->status);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }
 
-int32_t mummu_ep_combine(MummuMoe* m, void* const* peer_sync, void* const* peer_ys, const int32_t* ids,
-                         const int32_t* order_ids, const float* w, const int32_t* pos, const int32_t* offsets, const int32_t* dst_base,
-                         int32_t rank, int32_t world, int32_t tokens, int32_t top_k, int64_t cap_rows, void* out,
-                         void* stream) {
-    MUMMU_REQUIRE(m && peer_sync && peer_ys && ids && w && pos && offsets && dst_base && out,
-                  "mummu_ep_combine: null argument");
+int32_t mummu_ep_combine(MummuMoe* m, void* const* peer_sync, const void* back_own, const int32_t* ids,
+                         const int32_t* order_ids, const float* w, const int32_t* pos, int32_t rank, int32_t world,
+                         int32_t tokens, int32_t top_k, void* out, void* stream) {
+    MUMMU_REQUIRE(m && peer_sync && back_own && ids && w && pos && out, "mummu_ep_combine: null argument");
     int rc = ep_check_ranks(m, rank, world, "mummu_ep_combine");
     if (rc) return rc;
     MUMMU_REQUIRE(dtype_size(m->cfg.act_dtype) == 2 && m->cfg.hidden % 8 == 0,
@@ -499,23 +531,15 @@ int32_t mummu_ep_combine(MummuMoe* m, void* const* peer_sync, void* const* peer_
     MUMMU_REQUIRE(tokens >= 0 && top_k >= 1, "mummu_ep_combine: tokens %d, top_k %d", tokens, top_k);
     std::lock_guard<std::mutex> lock(m->mu);
     cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
-    const int H = m->cfg.hidden;
-    // a rank without tokens still consumes the epoch
-    const dim3 grid((unsigned)(tokens < 1 ? 1 : tokens), tokens < 512 ? (unsigned)((H / 8 + 255) / 256) : 1u);
-    const size_t smem = (size_t)top_k * (sizeof(void*) + sizeof(float));
-    const PeerTable ts = peer_table(peer_sync, world), ty = peer_table(peer_ys, world);
-    const int k_eff = tokens < 1 ? 0 : top_k;
-    LaunchScope scope(m, s, "ep_combine");
-    if (m->cfg.act_dtype == MUMMU_F16)
-        ep_combine_kernel<__half><<<grid, 256, smem, s>>>(ts, ty, ids, order_ids ? order_ids : ids, w, pos, offsets, dst_base, rank, world, k_eff, tokens < 1 ? 0 : H,
-                                                         m->cfg.experts_local, cap_rows, wait_polls_of(m), m->status,
-                                                         (__half*)out);
-    else
-        ep_combine_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(ts, ty, ids, order_ids ? order_ids : ids, w, pos, offsets, dst_base, rank, world, k_eff,
-                                                                tokens < 1 ? 0 : H, m->cfg.experts_local, cap_rows,
-                                                                wait_polls_of(m), m->status, (__nv_bfloat16*)out);
-    MUMMU_CUDA_TRY(cudaGetLastError());
-    return MUMMU_OK;
+    {
+        // a rank without tokens still consumes the epoch
+        LaunchScope scope(m, s, "ep_wait_out");
+        ep_wait_kernel<<<1, 32, 0, s>>>(peer_table(peer_sync, world), rank, world, EP_CH_OUT, wait_polls_of(m), m->status);
+        MUMMU_CUDA_TRY(cudaGetLastError());
+    }
+    // a token's terms in ascending EXPERT id (nn/moe.rs:296-328); with a placement `ids` are bank
+    // slots and the expert ids come separately, so that the order does not follow the slots
+    return launch_combine(m, back_own, m->cfg.act_dtype, order_ids ? order_ids : ids, w, pos, tokens, top_k, out, s);
 }
 
 }  // extern "C"

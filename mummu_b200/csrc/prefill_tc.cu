@@ -52,7 +52,16 @@ struct TcArgs {
     void* out;
     int ld_out;
     int32_t* status;
+    // GEMM2 with 16-bit output may send every output row somewhere else (expert parallelism: to
+    // the rank the row came from).  Rows are segments (expert, source rank) in ret_seg order.
+    const int32_t* ret_seg;    // [n_seg + 1] first row of every segment, or null: rows stay in `out`
+    const int32_t* ret_dst;    // [n_seg] the segment's first row in its destination buffer
+    int n_seg, world;
+    int64_t back_rows;         // rows of a destination buffer
+    void* back[16];            // destination buffer per rank (peer memory; plain stores)
 };
+
+constexpr uint32_t TC_EPI_STAGE_BYTES = 32 * 128;            // per epilogue warp: 32 rows x 64 values of 16 bits
 
 // ------------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -110,6 +119,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* tile_start = reinterpret_cast<int*>(tmem_slot + 2);               // [E + 1]
+    // epilogue staging, 4 x 4 KiB, 16-byte aligned behind the tile list
+    unsigned char* epi_stage = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tile_start + a.E + 1) + 15) & ~(uintptr_t)15);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES);
@@ -252,7 +264,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         }
                     }
                 }
-            } else {
+            } else if constexpr (sizeof(TOUT) == 4) {
                 TOUT* orow = reinterpret_cast<TOUT*>(a.out) + (size_t)row * a.ld_out + (size_t)nt * 256;
 #pragma unroll 1
                 for (int c = 0; c < 256; c += 32) {
@@ -260,23 +272,67 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     tmem_ld32(t0 + c, d);
                     tmem_ld_wait();
                     if (valid) {
-                        if constexpr (sizeof(TOUT) == 4) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<uint4*>(reinterpret_cast<float*>(orow) + c + j) =
-                                    make_uint4(d[j], d[j + 1], d[j + 2], d[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 v;
-                                v.x = pack2<TIN>(__uint_as_float(d[j + 0]), __uint_as_float(d[j + 1]));
-                                v.y = pack2<TIN>(__uint_as_float(d[j + 2]), __uint_as_float(d[j + 3]));
-                                v.z = pack2<TIN>(__uint_as_float(d[j + 4]), __uint_as_float(d[j + 5]));
-                                v.w = pack2<TIN>(__uint_as_float(d[j + 6]), __uint_as_float(d[j + 7]));
-                                *reinterpret_cast<uint4*>(reinterpret_cast<TIN*>(orow) + c + j) = v;
-                            }
-                        }
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<float*>(orow) + c + j) =
+                                make_uint4(d[j], d[j + 1], d[j + 2], d[j + 3]);
                     }
+                }
+            } else {
+                // 16-bit output: where this lane's row goes (its own buffer, or the buffer of the
+                // rank the row came from); then 64 columns at a time through shared memory, so that
+                // a store instruction of the warp writes 128 contiguous bytes of each of 4 rows
+                // instead of 16 bytes of each of 32 rows - what a store across NVLink needs
+                unsigned char* dptr = nullptr;
+                if (valid) {
+                    if (a.ret_seg) {
+                        int lo = 0, hi = a.n_seg;                // last segment that starts at or before row
+                        while (hi - lo > 1) {
+                            const int mid = (lo + hi) >> 1;
+                            if (a.ret_seg[mid] <= row) lo = mid; else hi = mid;
+                        }
+                        const int64_t drow = (int64_t)a.ret_dst[lo] + (row - a.ret_seg[lo]);
+                        if (drow >= 0 && drow < a.back_rows)
+                            dptr = reinterpret_cast<unsigned char*>(a.back[lo % a.world]) + (size_t)drow * a.ld_out * 2;
+                        else
+                            atomicOr(a.status, STATUS_BOUNDS);
+                    } else {
+                        dptr = reinterpret_cast<unsigned char*>(a.out) + (size_t)row * a.ld_out * 2;
+                    }
+                    if (dptr) dptr += (size_t)nt * 256 * 2;
+                }
+                uint4* stg = reinterpret_cast<uint4*>(epi_stage + quarter * TC_EPI_STAGE_BYTES);
+#pragma unroll 1
+                for (int c = 0; c < 256; c += 64) {
+                    uint32_t d0[32], d1[32];
+                    tmem_ld32(t0 + c, d0);
+                    tmem_ld32(t0 + c + 32, d1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint4 v, w;
+                        v.x = pack2<TIN>(__uint_as_float(d0[8 * j + 0]), __uint_as_float(d0[8 * j + 1]));
+                        v.y = pack2<TIN>(__uint_as_float(d0[8 * j + 2]), __uint_as_float(d0[8 * j + 3]));
+                        v.z = pack2<TIN>(__uint_as_float(d0[8 * j + 4]), __uint_as_float(d0[8 * j + 5]));
+                        v.w = pack2<TIN>(__uint_as_float(d0[8 * j + 6]), __uint_as_float(d0[8 * j + 7]));
+                        w.x = pack2<TIN>(__uint_as_float(d1[8 * j + 0]), __uint_as_float(d1[8 * j + 1]));
+                        w.y = pack2<TIN>(__uint_as_float(d1[8 * j + 2]), __uint_as_float(d1[8 * j + 3]));
+                        w.z = pack2<TIN>(__uint_as_float(d1[8 * j + 4]), __uint_as_float(d1[8 * j + 5]));
+                        w.w = pack2<TIN>(__uint_as_float(d1[8 * j + 6]), __uint_as_float(d1[8 * j + 7]));
+                        // piece index swizzled by the row: the 32 lanes of a store hit 32 banks x 4
+                        stg[lane * 8 + (j ^ (lane & 7))] = v;
+                        stg[lane * 8 + ((j + 4) ^ (lane & 7))] = w;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int idx = i * 32 + lane, r = idx >> 3, pc = idx & 7;
+                        const uint4 v = stg[r * 8 + (pc ^ (r & 7))];
+                        unsigned char* p = reinterpret_cast<unsigned char*>(
+                            __shfl_sync(0xFFFFFFFFu, reinterpret_cast<unsigned long long>(dptr), r));
+                        if (p) *reinterpret_cast<uint4*>(p + c * 2 + pc * 16) = v;
+                    }
+                    __syncwarp();
                 }
             }
             tc_fence_before();
@@ -360,7 +416,8 @@ bool prefill_tc_supported(const MummuMoeConfig& c, int64_t rows_total) {
 }
 
 static size_t tc_smem_bytes(int E) {
-    return 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (2 * TC_STAGES + 4) * 8 + 16 + (size_t)(E + 1) * 4 + 64;
+    return 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (2 * TC_STAGES + 4) * 8 + 16 + (size_t)(E + 1) * 4 + 64 + 16 +
+           4 * TC_EPI_STAGE_BYTES;
 }
 
 template <typename TIN>
@@ -408,6 +465,15 @@ static int launch_tc_typed(MummuMoe* m, const void* xs, int64_t rows_cap, const 
     d.out = ys;
     d.ld_out = c.hidden;
     d.status = m->status;
+    if (m->scatter.offered && ys_dtype != MUMMU_F32) {
+        d.ret_seg = m->ret_seg;
+        d.ret_dst = m->ret_dst;
+        d.n_seg = c.experts_local * m->scatter.world;
+        d.world = m->scatter.world;
+        d.back_rows = m->scatter.back_rows;
+        for (int r = 0; r < m->scatter.world; ++r) d.back[r] = m->scatter.back[r];
+        m->scatter.used = true;
+    }
     LaunchScope scope(m, s, "tc_down");
     if (ys_dtype == MUMMU_F32) {
         MUMMU_CUDA_TRY(allow_big_smem(grouped_gemm_tc_kernel<TIN, float, false>, c.device));

@@ -57,27 +57,31 @@ def plan_exchange(all_counts: np.ndarray, rank: int, world: int) -> ExchangePlan
 
 
 class PeerWorkspace:
-    """The peer-visible buffers of a rank (rows received for its experts, their outputs, and the
-    block of flags and counts the ranks signal each other through), shared by every layer of a
-    stack: allocated by the CUDA library, exported as IPC handles, exchanged through the process
-    group, mapped by every peer."""
+    """The buffers of a rank, shared by every layer of a stack: rows received for its experts, the
+    expert outputs of its own (token, slot) pairs that come back, and the block of flags and counts
+    the ranks signal each other through - those three allocated by the CUDA library, exported as
+    IPC handles, exchanged through the process group and mapped by every peer - plus the private
+    buffer its experts write into.  cap_rows: rows that may arrive (every rank's tokens * top_k);
+    back_rows: this rank's own tokens * top_k."""
 
-    def __init__(self, group, device: int, cap_rows: int, hidden: int, experts: int = 256):
+    def __init__(self, group, device: int, cap_rows: int, hidden: int, experts: int = 256, back_rows: int = 0):
         import ctypes as C
         import torch.distributed as dist
         from . import _lib as L
         self.L, self.device, self.group = L, device, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.cap_rows, self.bytes = cap_rows, cap_rows * hidden * 2
+        self.back_rows = back_rows or -(-cap_rows // self.world)
         self.own, self.opened, handles = [], [], []
         sync_bytes = int(L.lib.mummu_ep_sync_bytes(self.world, experts))
-        for nbytes in (self.bytes, self.bytes, sync_bytes):
+        for nbytes in (self.bytes, self.back_rows * hidden * 2, sync_bytes, self.bytes):
             ptr, h = C.c_void_p(), C.create_string_buffer(64)
-            rc = L.lib.mummu_ep_alloc(device, nbytes, C.byref(ptr), h)
+            rc = L.lib.mummu_ep_alloc(device, max(nbytes, 16), C.byref(ptr), h)
             if rc:
                 raise RuntimeError(L.last_error())
             self.own.append(ptr.value)
             handles.append(h.raw)
+        handles = handles[:3]                      # the fourth buffer is private
         gathered = [None] * self.world
         dist.all_gather_object(gathered, handles, group=group)
         self.tables = []
@@ -94,8 +98,8 @@ class PeerWorkspace:
                     self.opened.append(ptr.value)
                     table[r] = ptr.value
             self.tables.append(table)
-        self.recv_table, self.ys_table, self.sync_table = self.tables
-        self.recv_ptr, self.ys_ptr, self.sync_ptr = self.own
+        self.recv_table, self.back_table, self.sync_table = self.tables
+        self.recv_ptr, self.back_ptr, self.sync_ptr, self.ys_ptr = self.own
         self.experts = experts
         dist.barrier(group=group)          # every peer has mapped every (zeroed) block
 
@@ -129,17 +133,19 @@ class LocalWorkspaces:
     single stream (tests on one GPU; never several streams or processes: a stage that waits for a
     kernel that has not been scheduled would only run into its bound)."""
 
-    def __init__(self, device: int, world: int, cap_rows: int, hidden: int, experts: int):
+    def __init__(self, device: int, world: int, cap_rows: int, hidden: int, experts: int, back_rows: int = 0):
         import ctypes as C
         from . import _lib as L
         self.L, self.device, self.world, self.experts = L, device, world, experts
         self.cap_rows = cap_rows
+        self.back_rows = back_rows or -(-cap_rows // world)
         sync_bytes = int(L.lib.mummu_ep_sync_bytes(world, experts))
-        self.ptrs = [[], [], []]                       # recv, ys, sync per rank
+        self.ptrs = [[], [], [], []]                   # recv, back, sync, ys per rank
         for _ in range(world):
-            for which, nbytes in enumerate((cap_rows * hidden * 2, cap_rows * hidden * 2, sync_bytes)):
+            sizes = (cap_rows * hidden * 2, self.back_rows * hidden * 2, sync_bytes, cap_rows * hidden * 2)
+            for which, nbytes in enumerate(sizes):
                 ptr, h = C.c_void_p(), C.create_string_buffer(64)
-                rc = L.lib.mummu_ep_alloc(device, nbytes, C.byref(ptr), h)
+                rc = L.lib.mummu_ep_alloc(device, max(nbytes, 16), C.byref(ptr), h)
                 if rc:
                     raise RuntimeError(L.last_error())
                 self.ptrs[which].append(ptr.value)
@@ -155,16 +161,18 @@ class LocalWorkspaces:
         for lst in self.ptrs:
             for p in lst:
                 self.L.lib.mummu_ep_free(p)
-        self.ptrs = [[], [], []]
+        self.ptrs = [[], [], [], []]
 
 
 class _RankView:
     def __init__(self, ws: LocalWorkspaces, rank: int):
         import ctypes as C
         self.world, self.rank, self.cap_rows, self.experts = ws.world, rank, ws.cap_rows, ws.experts
+        self.back_rows = ws.back_rows
         mk = lambda lst: (C.c_void_p * ws.world)(*lst)
-        self.recv_table, self.ys_table, self.sync_table = mk(ws.ptrs[0]), mk(ws.ptrs[1]), mk(ws.ptrs[2])
-        self.recv_ptr, self.ys_ptr, self.sync_ptr = ws.ptrs[0][rank], ws.ptrs[1][rank], ws.ptrs[2][rank]
+        self.recv_table, self.back_table, self.sync_table = mk(ws.ptrs[0]), mk(ws.ptrs[1]), mk(ws.ptrs[2])
+        self.recv_ptr, self.back_ptr, self.sync_ptr = ws.ptrs[0][rank], ws.ptrs[1][rank], ws.ptrs[2][rank]
+        self.ys_ptr = ws.ptrs[3][rank]
 
 
 class ExpertParallelMoe:
@@ -242,6 +250,7 @@ class ExpertParallelMoe:
         m, ws = self.moe, self.workspace
         T = x.shape[0]
         assert T * top_k * self.world <= ws.cap_rows, "workspace too small for the rows that may arrive"
+        assert T * top_k <= ws.back_rows, "workspace too small for the rows that come back"
         st = dict(x=x, top_k=top_k)
         i32 = dict(dtype=torch.int32, device=x.device)
         if self.placement is None:
@@ -265,15 +274,15 @@ class ExpertParallelMoe:
 
     def stage_experts(self, st):
         ws = self.workspace
-        self.moe.ep_experts(ws.sync_table, self.rank, self.world, ws.recv_ptr, st["local_counts"], ws.cap_rows,
-                            ws.ys_ptr)
+        self.moe.ep_experts(ws.sync_table, ws.back_table, self.rank, self.world, ws.recv_ptr, st["local_counts"],
+                            ws.cap_rows, ws.ys_ptr, ws.back_rows)
 
     def stage_combine(self, st):
         import torch
         ws = self.workspace
         y = torch.empty_like(st["x"])
-        self.moe.ep_combine(ws.sync_table, ws.ys_table, st["ids"], st["w"], st["pos"], st["offsets"], st["dst_base"],
-                            self.rank, self.world, ws.cap_rows, y, order_ids=st.get("expert_ids"))
+        self.moe.ep_combine(ws.sync_table, ws.back_ptr, st["ids"], st["w"], st["pos"], self.rank, self.world, y,
+                            order_ids=st.get("expert_ids"))
         return y
 
     def forward_p2p(self, x, top_k: int, norm_topk_prob: bool):

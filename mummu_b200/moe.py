@@ -330,18 +330,16 @@ class SparseMoe:
                                        sync_table, recv_table, rank, world, row_token.numel(), cap_rows,
                                        dst_base.data_ptr(), local_counts.data_ptr(), _torch_stream()))
 
-    def ep_experts(self, sync_table, rank: int, world: int, recv_ptr: int, local_counts, rows_cap: int,
-                   ys_ptr: int) -> None:
-        _check(L.lib.mummu_ep_experts(self._h, sync_table, rank, world, recv_ptr, local_counts.data_ptr(),
-                                      rows_cap, ys_ptr, _torch_stream()))
+    def ep_experts(self, sync_table, back_table, rank: int, world: int, recv_ptr: int, local_counts, rows_cap: int,
+                   ys_ptr: int, back_rows: int) -> None:
+        _check(L.lib.mummu_ep_experts(self._h, sync_table, back_table, rank, world, recv_ptr, local_counts.data_ptr(),
+                                      rows_cap, ys_ptr, back_rows, _torch_stream()))
 
-    def ep_combine(self, sync_table, ys_table, ids, w, pos, offsets, dst_base, rank: int, world: int,
-                   cap_rows: int, out, order_ids=None) -> None:
+    def ep_combine(self, sync_table, back_ptr: int, ids, w, pos, rank: int, world: int, out, order_ids=None) -> None:
         tokens, top_k = ids.shape
-        _check(L.lib.mummu_ep_combine(self._h, sync_table, ys_table, ids.data_ptr(),
+        _check(L.lib.mummu_ep_combine(self._h, sync_table, back_ptr, ids.data_ptr(),
                                       None if order_ids is None else order_ids.data_ptr(), w.data_ptr(), pos.data_ptr(),
-                                      offsets.data_ptr(), dst_base.data_ptr(), rank, world, tokens, top_k,
-                                      cap_rows, out.data_ptr(), _torch_stream()))
+                                      rank, world, tokens, top_k, out.data_ptr(), _torch_stream()))
 
     def combine(self, ys, ids, w, pos, out) -> None:
         tokens, top_k = ids.shape

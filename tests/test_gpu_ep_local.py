@@ -161,6 +161,39 @@ def test_ep_receive_buffer_too_small_is_reported_not_written(cuda_lib):
     ws.close()
 
 
+def test_ep_return_buffer_too_small_is_reported_not_written(cuda_lib):
+    """The way back: a rank whose buffer for returning outputs is smaller than its own rows gets
+    the rows that fit; the rest are dropped by the sender and the sender's next sync reports it."""
+    import torch
+    from mummu_b200 import ep as epmod, moe
+    L = cuda_lib
+    H, I, E, K, Tr, world = 256, 128, 8, 2, 16, 2
+    cfg = moe.SparseMoeConfig(H, I, E, K)
+    router, gate, up, down, _ = synth.moe_layer(H, I, E, 1, cfg_seed=5)
+    banks = [torch.from_numpy(b).cuda().to(torch.bfloat16) for b in (gate, up, down)]
+    ws, group = build_group(torch, L, moe, epmod, cfg, world, L.BF16, L.BF16, banks, router, Tr)
+    xs = [torch.from_numpy(synth.normal(100 + r, (Tr, H), 1.0)).cuda().to(torch.bfloat16) for r in range(world)]
+    states = [ep.stage_route(x, K, False) for ep, x in zip(group, xs)]
+    for ep, st in zip(group, states):
+        ep.stage_dispatch(st)
+    for v in ws.views:
+        v.back_rows = 4                    # the buffers really hold Tr * K = 32 rows
+    for ep, st in zip(group, states):
+        ep.stage_experts(st)
+    torch.cuda.synchronize()
+    reported = 0
+    for ep in group:
+        try:
+            ep.moe.sync()
+        except moe.MoeContractError as exc:
+            assert "left its buffer" in str(exc)
+            reported += 1
+    assert reported >= 1
+    for ep in group:
+        ep.close()
+    ws.close()
+
+
 def test_ep_wait_runs_out_and_the_group_recovers(cuda_lib):
     """Failure detection without a fault: rank 1 never posts its counts, so rank 0's dispatch stage
     runs into the (shortened) bound of its wait.  The kernel returns, moves no row, the next sync

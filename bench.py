@@ -550,7 +550,10 @@ def measure_ep(ctx, shape: dict) -> dict:
     bias = shape.get("bias")
     slots_total = plan.virtual_experts if plan is not None else e
     mine = plan.rank_experts(rank).tolist() if plan is not None else list(range(rank * el, rank * el + el))
-    ws = PeerWorkspace(None, ctx.local_rank, world * T * k, h, slots_total) if world > 1 else None
+    # decode-sized steps take the small-batch form (every token to every rank), whose return buffer
+    # is indexed by the common sorted order: as many rows as all ranks route together
+    ws = (PeerWorkspace(None, ctx.local_rank, world * T * k, h, slots_total, back_rows=world * T * k if q4 else 0)
+          if world > 1 else None)
     layers = []
     for l in range(NL):
         gen.manual_seed(9000 + l)                                   # router: same on every rank

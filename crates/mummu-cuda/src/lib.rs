@@ -104,6 +104,14 @@ pub mod sys {
         pub fn mummu_ep_free(ptr: *mut c_void) -> i32;
         pub fn mummu_ep_sync_bytes(world: i32, experts: i32) -> usize;
         pub fn mummu_ep_reset(device: i32, own_sync: *mut c_void, world: i32, experts: i32) -> i32;
+        pub fn mummu_ep_gather_tokens(moe: *mut MummuMoe, x: *const c_void, tokens: i32, peer_sync: *const *mut c_void,
+                                      peer_gx: *const *mut c_void, rank: i32, world: i32, stream: *mut c_void) -> i32;
+        pub fn mummu_ep_wait(moe: *mut MummuMoe, peer_sync: *const *mut c_void, rank: i32, world: i32, channel: i32,
+                             stream: *mut c_void) -> i32;
+        pub fn mummu_ep_experts_gathered(moe: *mut MummuMoe, peer_sync: *const *mut c_void, peer_back: *const *mut c_void,
+                                         gx_own: *const c_void, row_token: *const i32, counts: *const i32,
+                                         offsets: *const i32, rank: i32, world: i32, tokens_per_rank: i32, top_k: i32,
+                                         back_rows: i64, stream: *mut c_void) -> i32;
         pub fn mummu_ep_place(moe: *mut MummuMoe, ids: *const i32, table: *const i32, experts_real: i32, n: i64,
                               ids_out: *mut i32, stream: *mut c_void) -> i32;
         pub fn mummu_ep_post_counts(moe: *mut MummuMoe, counts: *const i32, peer_sync: *const *mut c_void, rank: i32,

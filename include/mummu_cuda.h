@@ -233,6 +233,29 @@ int32_t mummu_ep_free(void* ptr);
  *                         where `ids` are bank slots (mummu_ep_place): a token's terms are summed
  *                         in ascending expert id either way. */
 size_t mummu_ep_sync_bytes(int32_t world, int32_t experts);
+/* Small-batch form (decode): with few tokens per rank the three hops above cost more than the rows
+ * they move.  Every rank pushes its tokens to every rank (mummu_ep_gather_tokens: x [tokens,
+ * hidden] -> rows [rank * tokens, (rank + 1) * tokens) of every peer_gx[r]; one signal), waits for
+ * everybody's (mummu_ep_wait, channel 0), and routes ALL world * tokens tokens itself with
+ * mummu_moe_route_grouped: the router is replicated and bit-reproducible, so every rank holds the
+ * same plan and no counts are exchanged.  mummu_ep_experts_gathered then runs this rank's experts
+ * on the rows that plan gives them, read in place from the gathered tokens, and stores each output
+ * row into peer_back[rank of the row's token] at the row's position in the common sorted order
+ * ([world * tokens * top_k, hidden] per rank); mummu_ep_combine, given the slice of ids, w and pos
+ * of this rank's own tokens, finishes the layer.  Two hops instead of three and no row copy on
+ * the way out.  f16 activations on Q4_K experts, at most 8192 (token, slot) pairs over all ranks;
+ * otherwise MUMMU_ERR_UNSUPPORTED. */
+int32_t mummu_ep_gather_tokens(MummuMoe* moe, const void* x, int32_t tokens, void* const* peer_sync,
+                               void* const* peer_gx, int32_t rank, int32_t world, void* stream);
+/* Wait (bounded) until every rank has signalled the next epoch of `channel` (0: counts or gathered
+ * tokens, 1: rows, 2: outputs) to this rank. */
+int32_t mummu_ep_wait(MummuMoe* moe, void* const* peer_sync, int32_t rank, int32_t world,
+                      int32_t channel, void* stream);
+int32_t mummu_ep_experts_gathered(MummuMoe* moe, void* const* peer_sync, void* const* peer_back,
+                                  const void* gx_own, const int32_t* row_token, const int32_t* counts,
+                                  const int32_t* offsets, int32_t rank, int32_t world,
+                                  int32_t tokens_per_rank, int32_t top_k, int64_t back_rows,
+                                  void* stream);
 /* Hot-expert placement (nn/moe.rs:1527-1535 hands the hit counters to the planner; tier.rs:353-431
  * plans from them).  A group whose handles are created over `world * slots_per_rank` bank SLOTS
  * instead of experts can hold an expert in several slots, on different ranks, and any expert on

@@ -65,6 +65,12 @@ SYMBOLS = {
     "mummu_ep_free": (C.c_int32, [C.c_void_p]),
     "mummu_ep_sync_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "mummu_ep_reset": (C.c_int32, [C.c_int32, C.c_void_p, C.c_int32, C.c_int32]),
+    "mummu_ep_gather_tokens": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                           C.c_int32, C.c_int32, C.c_void_p]),
+    "mummu_ep_wait": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "mummu_ep_experts_gathered": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p,
+                                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                              C.c_int32, C.c_int64, C.c_void_p]),
     "mummu_ep_place": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p]),
     "mummu_ep_post_counts": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
                                          C.c_void_p]),

@@ -298,6 +298,83 @@ __global__ void __launch_bounds__(256) ep_return_kernel(const uint4* ys, PeerTab
     if (ep_last_block(own + EP_W_DONE + 2) && threadIdx.x < 32) ep_signal(sync, rank, world, EP_CH_OUT);
 }
 
+// ---- small-batch form: every rank gets every token ----------------------------------------------
+// With few tokens per rank the three hops above (counts, rows, outputs) cost more than the rows
+// they move.  Here every rank pushes its tokens to every rank (hop 1), routes ALL tokens itself -
+// the router is replicated and bit-reproducible, so every rank computes the same plan and no
+// counts are exchanged - runs its own experts on the rows the plan gives them, read in place
+// from the gathered tokens, and pushes each output row to the rank its token lives on, at the
+// row's position in the common sorted order (hop 2).
+__global__ void __launch_bounds__(256) ep_gather_tokens_kernel(const uint4* x, PeerTable sync, PeerTable gx, int rank, int world,
+                                                               int tokens, int vec_per_row) {
+    const int lane = threadIdx.x & 31;
+    const int64_t items = (int64_t)world * tokens;               // (destination rank, token)
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t it = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); it < items; it += warps) {
+        const int d = (int)(it / tokens), t = (int)(it - (int64_t)d * tokens);
+        copy_row(x + (size_t)t * vec_per_row,
+                 reinterpret_cast<uint4*>(gx.ptr[d]) + ((size_t)rank * tokens + t) * vec_per_row, vec_per_row, lane);
+    }
+    int32_t* own = reinterpret_cast<int32_t*>(sync.ptr[rank]);
+    if (ep_last_block(own + EP_W_DONE + 0) && threadIdx.x < 32) ep_signal(sync, rank, world, EP_CH_COUNTS);
+}
+
+// local experts' view of the common plan: rows, first sorted row (absolute) and work order
+__global__ void __launch_bounds__(256) ep_local_plan_kernel(const int32_t* counts, const int32_t* offsets, int first, int EL,
+                                                            int32_t* l_counts, int32_t* l_offsets, int32_t* active,
+                                                            int32_t* n_active) {
+    extern __shared__ int32_t s_dyn[];
+    for (int le = threadIdx.x; le < EL; le += blockDim.x) s_dyn[le] = counts[first + le];
+    __syncthreads();
+    for (int le = threadIdx.x; le < EL; le += blockDim.x) {
+        const int c = s_dyn[le];
+        int before = 0;
+        for (int i = 0; i < EL; ++i) before += (s_dyn[i] > c || (s_dyn[i] == c && i < le)) && s_dyn[i] > 0;
+        l_counts[le] = c;
+        l_offsets[le] = offsets[first + le];
+        if (c > 0) active[before] = le;
+        if (le == EL - 1) l_offsets[EL] = offsets[first + le] + c;
+    }
+    if (threadIdx.x == 0) {
+        int nz = 0;
+        for (int i = 0; i < EL; ++i) nz += s_dyn[i] > 0;
+        *n_active = nz;
+    }
+}
+
+// expert outputs (f32, sorted order) of this rank's experts -> f16 rows in the buffer of the rank
+// each row's token lives on, at the same sorted position
+__global__ void __launch_bounds__(256) ep_return_gathered_kernel(const float* ys, const int32_t* row_token, const int32_t* l_offsets,
+                                                                 int EL, PeerTable sync, PeerTable back, int rank, int world,
+                                                                 int tokens_per_rank, int H, int64_t ys_rows, int64_t back_rows,
+                                                                 int32_t* status) {
+    const int lane = threadIdx.x & 31;
+    const int64_t p0 = l_offsets[0], p1 = min((int64_t)l_offsets[EL], ys_rows);
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t p = p0 + (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < p1; p += warps) {
+        const int d = row_token[p] / tokens_per_rank;
+        if (d < 0 || d >= world || p >= back_rows) {
+            if (lane == 0) atomicOr(status, STATUS_BOUNDS);
+            continue;
+        }
+        const float* src = ys + (size_t)p * H;
+        __half* dst = reinterpret_cast<__half*>(back.ptr[d]) + (size_t)p * H;
+        for (int h = lane * 8; h < H; h += 256) {
+            const float4 a = *reinterpret_cast<const float4*>(src + h), b = *reinterpret_cast<const float4*>(src + h + 4);
+            uint4 o;
+            __half2 t0 = __floats2half2_rn(a.x, a.y), t1 = __floats2half2_rn(a.z, a.w);
+            __half2 t2 = __floats2half2_rn(b.x, b.y), t3 = __floats2half2_rn(b.z, b.w);
+            o.x = *reinterpret_cast<uint32_t*>(&t0);
+            o.y = *reinterpret_cast<uint32_t*>(&t1);
+            o.z = *reinterpret_cast<uint32_t*>(&t2);
+            o.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(dst + h) = o;
+        }
+    }
+    int32_t* own = reinterpret_cast<int32_t*>(sync.ptr[rank]);
+    if (ep_last_block(own + EP_W_DONE + 2) && threadIdx.x < 32) ep_signal(sync, rank, world, EP_CH_OUT);
+}
+
 // Placement: a routed expert id becomes the id of the bank slot that serves it for this rank's
 // tokens.  An id outside the router's experts, or a table entry outside the slots, is reported
 // (STATUS_BOUNDS) and sent to slot 0 so that nothing later indexes past a buffer.
@@ -516,6 +593,79 @@ int32_t mummu_ep_experts(MummuMoe* m, void* const* peer_sync, void* const* peer_
     ep_return_kernel<<<(unsigned)blocks, 256, (size_t)(2 * nseg + 1) * sizeof(int32_t), s>>>(
         (const uint4*)ys_own, t, peer_table(peer_back, world), m->ret_seg, m->ret_dst, rank, world, m->cfg.experts_local,
         m->cfg.hidden * 2 / 16, rows_cap, back_rows, m->status);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+int32_t mummu_ep_gather_tokens(MummuMoe* m, const void* x, int32_t tokens, void* const* peer_sync, void* const* peer_gx,
+                               int32_t rank, int32_t world, void* stream) {
+    MUMMU_REQUIRE(m && peer_sync && peer_gx && (x || tokens == 0), "mummu_ep_gather_tokens: null argument");
+    int rc = ep_check_ranks(m, rank, world, "mummu_ep_gather_tokens");
+    if (rc) return rc;
+    MUMMU_REQUIRE(dtype_size(m->cfg.act_dtype) == 2 && m->cfg.hidden % 8 == 0 && tokens >= 0,
+                  "mummu_ep_gather_tokens: 16-bit activations with hidden %% 8 == 0 only");
+    std::lock_guard<std::mutex> lock(m->mu);
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    const int64_t items = (int64_t)world * tokens;
+    const int64_t blocks = items < 8 ? 1 : (items / 8 < 148 * 8 ? (items + 7) / 8 : 148 * 8);
+    LaunchScope scope(m, s, "ep_gather_tokens");
+    ep_gather_tokens_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint4*)x, peer_table(peer_sync, world),
+                                                             peer_table(peer_gx, world), rank, world, tokens,
+                                                             m->cfg.hidden * 2 / 16);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+int32_t mummu_ep_wait(MummuMoe* m, void* const* peer_sync, int32_t rank, int32_t world, int32_t channel, void* stream) {
+    MUMMU_REQUIRE(m && peer_sync && channel >= 0 && channel < 3, "mummu_ep_wait: bad argument");
+    int rc = ep_check_ranks(m, rank, world, "mummu_ep_wait");
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(m->mu);
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    LaunchScope scope(m, s, "ep_wait");
+    ep_wait_kernel<<<1, 32, 0, s>>>(peer_table(peer_sync, world), rank, world, channel, wait_polls_of(m), m->status);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+int32_t mummu_ep_experts_gathered(MummuMoe* m, void* const* peer_sync, void* const* peer_back, const void* gx_own,
+                                  const int32_t* row_token, const int32_t* counts, const int32_t* offsets, int32_t rank,
+                                  int32_t world, int32_t tokens_per_rank, int32_t top_k, int64_t back_rows, void* stream) {
+    MUMMU_REQUIRE(m && peer_sync && peer_back && gx_own && row_token && counts && offsets,
+                  "mummu_ep_experts_gathered: null argument");
+    int rc = ep_check_ranks(m, rank, world, "mummu_ep_experts_gathered");
+    if (rc) return rc;
+    const MummuMoeConfig& c = m->cfg;
+    const int64_t rows_total = (int64_t)world * tokens_per_rank * top_k;
+    MUMMU_REQUIRE(tokens_per_rank >= 1 && top_k >= 1 && top_k <= c.top_k && back_rows >= 0,
+                  "mummu_ep_experts_gathered: %d tokens per rank, top_k %d", tokens_per_rank, top_k);
+    if (!(c.weight_dtype == MUMMU_Q4_K && c.act_dtype == MUMMU_F16 && c.hidden % 256 == 0 && c.inter % 256 == 0 &&
+          c.hidden <= 8192 && c.inter <= 8192 && rows_total <= 8192 && (reinterpret_cast<uintptr_t>(gx_own) & 15) == 0)) {
+        set_error("mummu_ep_experts_gathered: f16 activations on Q4_K experts, at most 8192 (token, slot) pairs over all ranks");
+        return MUMMU_ERR_UNSUPPORTED;
+    }
+    MUMMU_REQUIRE(m->bank_set[0] && m->bank_set[1] && m->bank_set[2],
+                  "MoE: expert banks were never set (mummu_moe_set_bank gate/up/down)");
+    std::lock_guard<std::mutex> lock(m->mu);
+    cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    if ((rc = ensure_scratch(m, (int64_t)world * tokens_per_rank))) return rc;
+    const int EL = c.experts_local;
+    {
+        LaunchScope scope(m, s, "ep_local_plan");
+        ep_local_plan_kernel<<<1, 256, (size_t)EL * sizeof(int32_t), s>>>(counts, offsets, c.expert_first, EL, m->counts,
+                                                                           m->offsets, m->active, m->n_active);
+        MUMMU_CUDA_TRY(cudaGetLastError());
+    }
+    // this rank's experts see about rows_total / world rows; the kernels read them in place
+    if ((rc = launch_decode_q4k_rows(m, gx_own, row_token, m->counts, m->offsets, (rows_total + world - 1) / world, (float*)m->ys, s)))
+        return rc;
+    const int64_t est = (rows_total + world - 1) / world;
+    const int64_t blocks = est < 8 ? 1 : (est / 8 < 148 * 8 ? (est + 7) / 8 : 148 * 8);
+    LaunchScope scope(m, s, "ep_return");
+    ep_return_gathered_kernel<<<(unsigned)blocks, 256, 0, s>>>((const float*)m->ys, row_token, m->offsets, EL,
+                                                               peer_table(peer_sync, world), peer_table(peer_back, world),
+                                                               rank, world, tokens_per_rank, c.hidden, rows_total, back_rows,
+                                                               m->status);
     MUMMU_CUDA_TRY(cudaGetLastError());
     return MUMMU_OK;
 }

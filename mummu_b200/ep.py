@@ -285,6 +285,41 @@ class ExpertParallelMoe:
                             order_ids=st.get("expert_ids"))
         return y
 
+    # ---- small-batch form: every rank gets every token, routes them all, runs its own experts -----
+    def gathered_supported(self, tokens: int, top_k: int) -> bool:
+        from . import _lib as L
+        ws = self.workspace
+        return (ws is not None and self.placement is None and self.moe.weight_dtype == L.Q4_K
+                and self.moe.act_dtype == L.F16 and self.world * tokens * top_k <= min(8192, ws.back_rows)
+                and self.world * tokens <= ws.cap_rows)
+
+    def stage_gather(self, x, top_k: int, norm_topk_prob: bool):
+        ws = self.workspace
+        self.moe.ep_gather_tokens(x, ws.sync_table, ws.recv_table, self.rank, self.world)
+        return dict(x=x, top_k=top_k, norm=norm_topk_prob)
+
+    def stage_route_all(self, st):
+        ws, m, T, k = self.workspace, self.moe, st["x"].shape[0], st["top_k"]
+        m.ep_wait(ws.sync_table, self.rank, self.world, 0)
+        st["ids"], st["w"], st["counts"], st["offsets"], st["row_token"], st["pos"] = m.route_grouped_ptr(
+            ws.recv_ptr, self.world * T, k, st["norm"], st["x"].device)
+        m.ep_experts_gathered(ws.sync_table, ws.back_table, ws.recv_ptr, st["row_token"], st["counts"], st["offsets"],
+                              self.rank, self.world, T, k, ws.back_rows)
+
+    def stage_combine_own(self, st):
+        import torch
+        ws, T = self.workspace, st["x"].shape[0]
+        own = slice(self.rank * T, (self.rank + 1) * T)
+        y = torch.empty_like(st["x"])
+        self.moe.ep_combine(ws.sync_table, ws.back_ptr, st["ids"][own], st["w"][own],
+                            st["pos"].view(-1, st["top_k"])[own], self.rank, self.world, y)
+        return y
+
+    def forward_gathered(self, x, top_k: int, norm_topk_prob: bool):
+        st = self.stage_gather(x, top_k, norm_topk_prob)
+        self.stage_route_all(st)
+        return self.stage_combine_own(st)
+
     def forward_p2p(self, x, top_k: int, norm_topk_prob: bool):
         st = self.stage_route(x, top_k, norm_topk_prob)
         self.stage_dispatch(st)
@@ -293,6 +328,8 @@ class ExpertParallelMoe:
 
     def forward(self, x, top_k: int, norm_topk_prob: bool):
         if self.workspace is not None:
+            if self.gathered_supported(x.shape[0], top_k):
+                return self.forward_gathered(x, top_k, norm_topk_prob)
             return self.forward_p2p(x, top_k, norm_topk_prob)
         import torch
         dist, m = self.dist, self.moe

@@ -317,6 +317,33 @@ class SparseMoe:
                                                _torch_stream()))
 
     # stages of the expert-parallel layer (peer memory; see include/mummu_cuda.h)
+    def ep_gather_tokens(self, x, sync_table, gx_table, rank: int, world: int) -> None:
+        _check(L.lib.mummu_ep_gather_tokens(self._h, x.data_ptr(), x.shape[0], sync_table, gx_table, rank, world,
+                                            _torch_stream()))
+
+    def ep_wait(self, sync_table, rank: int, world: int, channel: int) -> None:
+        _check(L.lib.mummu_ep_wait(self._h, sync_table, rank, world, channel, _torch_stream()))
+
+    def ep_experts_gathered(self, sync_table, back_table, gx_ptr: int, row_token, counts, offsets, rank: int, world: int,
+                            tokens_per_rank: int, top_k: int, back_rows: int) -> None:
+        _check(L.lib.mummu_ep_experts_gathered(self._h, sync_table, back_table, gx_ptr, row_token.data_ptr(),
+                                               counts.data_ptr(), offsets.data_ptr(), rank, world, tokens_per_rank, top_k,
+                                               back_rows, _torch_stream()))
+
+    def route_grouped_ptr(self, x_ptr: int, tokens: int, top_k: int, norm_topk_prob: bool, device):
+        """`route_grouped` over activations given as a device address (a buffer the library allocated)."""
+        import torch
+        E = self.cfg.num_experts
+        i32 = dict(dtype=torch.int32, device=device)
+        ids = torch.empty((tokens, top_k), **i32)
+        w = torch.empty((tokens, top_k), dtype=torch.float32, device=device)
+        counts, offsets = torch.empty(E, **i32), torch.empty(E + 1, **i32)
+        row_token, pos = torch.empty(tokens * top_k, **i32), torch.empty(tokens * top_k, **i32)
+        _check(L.lib.mummu_moe_route_grouped(self._h, x_ptr, tokens, top_k, int(bool(norm_topk_prob)),
+                                             ids.data_ptr(), w.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
+                                             row_token.data_ptr(), pos.data_ptr(), _torch_stream()))
+        return ids, w, counts, offsets, row_token, pos
+
     def ep_place(self, ids, table, experts_real: int, ids_out) -> None:
         _check(L.lib.mummu_ep_place(self._h, ids.data_ptr(), table.data_ptr(), experts_real, ids.numel(),
                                     ids_out.data_ptr(), _torch_stream()))

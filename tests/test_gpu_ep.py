@@ -44,12 +44,14 @@ def _worker(rank, world, port, q, act, wdt_name):
             plan = P.plan_placement(hot / hot.sum(), E, world, el + 2)
             assert max(len(h) for h in plan.hosts) == 2
         slots_total = plan.virtual_experts if plan else E
-        ws = PeerWorkspace(None, rank, world * T * K, H, slots_total) if act != "nccl" else None
+        ws = (PeerWorkspace(None, rank, world * T * K, H, slots_total, back_rows=world * T * K if act == "gathered" else 0)
+              if act != "nccl" else None)
         ep = ExpertParallelMoe(cfg, device=rank, act_dtype=act_code, weight_dtype=wcode, max_tokens=T, workspace=ws,
                                placement=plan)
         ep.set_router(router, bias=bias)
         sl = plan.rank_experts(rank) if plan else slice(rank * el, (rank + 1) * el)
         ep.set_local_banks(enc(gate[sl]), enc(up[sl]), enc(down[sl]))
+        assert ep.gathered_supported(T, K) == (act == "gathered")
         xd = torch.from_numpy(x).cuda().to(tdt)
         y_ep = ep.forward(xd, K, False)
         y_ep2 = ep.forward(xd, K, False)
@@ -72,12 +74,14 @@ def _worker(rank, world, port, q, act, wdt_name):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["nccl", "p2p", "placed"])
+@pytest.mark.parametrize("mode", ["nccl", "p2p", "placed", "gathered"])
 @pytest.mark.parametrize("wdt_name", ["bf16", "q4k"])
 def test_expert_parallel_matches_single_gpu(cuda_lib, wdt_name, mode):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
+    if mode == "gathered" and wdt_name != "q4k":
+        pytest.skip("the small-batch form serves the Q4_K decode layer")
     import torch.multiprocessing as mp
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

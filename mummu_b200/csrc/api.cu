@@ -252,6 +252,14 @@ static int forward_device(MummuMoe* m, const void* x, void* y, int64_t tokens, i
         if ((rc = launch_experts_tc(m, m->xs, m->cap_tokens * c.top_k, m->counts, m->offsets, m->ys, c.act_dtype, s)))
             return rc;
         return launch_combine(m, m->ys, c.act_dtype, m->ids, m->wts, m->pos, tokens, top_k, y, s);
+    } else if (q4k_tc_supported(c, tokens * top_k) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && !m->sw.no_tc) {
+        // Q4_K with more tokens than the packed-weight kernels take: expand the experts that have
+        // rows to f16, then the tensor-core path
+        if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
+        if ((rc = launch_gather_rows(m, x, m->row_token, m->xs, tokens * top_k, s))) return rc;
+        if ((rc = launch_experts_q4k_tc(m, m->xs, m->cap_tokens * c.top_k, m->counts, m->offsets, m->ys, c.act_dtype, s)))
+            return rc;
+        return launch_combine(m, m->ys, c.act_dtype, m->ids, m->wts, m->pos, tokens, top_k, y, s);
     } else {
         if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
         int64_t max_rows = tokens;  // an expert serves a token at most once
@@ -351,6 +359,7 @@ int32_t mummu_moe_destroy(MummuMoe* m) {
         cudaFree(m->counts); cudaFree(m->offsets); cudaFree(m->hits); cudaFree(m->status);
         if (m->status_host) cudaFreeHost(m->status_host);
         cudaFree(m->active); cudaFree(m->n_active); cudaFree(m->ret_seg); cudaFree(m->ret_dst);
+        for (int b = 0; b < 3; ++b) cudaFree(m->wexp[b]);
         for (auto& p : m->prof.pending) { cudaEventDestroy(p.a); cudaEventDestroy(p.b); }
         for (auto e : m->prof.pool) cudaEventDestroy(e);
         if (m->stream) cudaStreamDestroy(m->stream);
@@ -580,6 +589,8 @@ static int32_t experts_rows(MummuMoe* m, const void* xs, const int32_t* counts, 
         if ((rc = launch_decode_q4k_rows(m, xs, nullptr, counts, m->offsets, rows, (float*)m->ys, s))) return rc;
         return launch_narrow((const float*)m->ys, ys, m->cfg.act_dtype, (int64_t)rows * m->cfg.hidden, s);
     }
+    if (q4k_tc_supported(m->cfg, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !m->sw.no_tc)
+        return launch_experts_q4k_tc(m, xs, rows, counts, m->offsets, ys, m->cfg.act_dtype, s);
     return launch_experts_simt(m, xs, m->cfg.act_dtype, nullptr, counts, m->offsets, rows, rows, ys,
                                m->cfg.act_dtype, -1, s);
 }
@@ -776,6 +787,7 @@ int32_t mummu_moe_adopt_scratch(MummuMoe* m, MummuMoe* donor) {
     m->ys = donor->ys; m->io_x = donor->io_x; m->io_y = donor->io_y;
     m->cap_tokens = donor->cap_tokens;
     m->scratch_borrowed = true;
+    m->scratch_donor = donor;
     return MUMMU_OK;
 }
 

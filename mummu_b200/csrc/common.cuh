@@ -216,6 +216,10 @@ struct MummuMoe {
     // set by the expert-parallel experts stage around its call of the expert kernels: where the
     // down projection may store its rows directly (peer buffers); `used` tells the stage whether
     // the kernel that ran took the offer
+    // f16 image of a Q4_K bank for calls with too many rows for the packed-weight kernels: the
+    // experts with rows are expanded per call and fed to the tensor-core GEMMs
+    __half* wexp[3] = {nullptr, nullptr, nullptr};
+    MummuMoe* scratch_donor = nullptr;      // the layer whose scratch (and expanded image) this one uses
     struct {
         bool offered = false, used = false;
         int world = 0;
@@ -304,6 +308,9 @@ int launch_block_dequant(const void* src, int dtype, float* dst, int64_t rows, i
 bool prefill_tc_supported(const MummuMoeConfig& c, int64_t rows_total);
 int launch_gather_rows(MummuMoe* m, const void* x, const int32_t* row_token, void* xs, int64_t rows,
                        cudaStream_t s);
+bool q4k_tc_supported(const MummuMoeConfig& c, int64_t rows_total);
+int launch_experts_q4k_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts, const int32_t* offsets,
+                          void* ys, int ys_dtype, cudaStream_t s);
 int launch_experts_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts,
                       const int32_t* offsets, void* ys, int ys_dtype, cudaStream_t s);
 

@@ -420,17 +420,19 @@ static size_t tc_smem_bytes(int E) {
            4 * TC_EPI_STAGE_BYTES;
 }
 
+// banks: gate, up, down as [experts_local, out, in] in the activation's 16-bit type (the handle's
+// own banks, or the expanded image of its Q4_K banks)
 template <typename TIN>
 static int launch_tc_typed(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts,
-                           const int32_t* offsets, void* ys, int ys_dtype, cudaStream_t s) {
+                           const int32_t* offsets, void* ys, int ys_dtype, const void* const* banks, cudaStream_t s) {
     const MummuMoeConfig& c = m->cfg;
     CUtensorMap map_x, map_h, map_g, map_u, map_d;
     int rc;
     if ((rc = make_map(&map_x, xs, c.act_dtype, (uint64_t)rows_cap, c.hidden))) return rc;
     if ((rc = make_map(&map_h, m->hact, c.act_dtype, (uint64_t)rows_cap, c.inter))) return rc;
-    if ((rc = make_map(&map_g, m->bank[MUMMU_BANK_GATE], c.weight_dtype, (uint64_t)c.experts_local * c.inter, c.hidden))) return rc;
-    if ((rc = make_map(&map_u, m->bank[MUMMU_BANK_UP], c.weight_dtype, (uint64_t)c.experts_local * c.inter, c.hidden))) return rc;
-    if ((rc = make_map(&map_d, m->bank[MUMMU_BANK_DOWN], c.weight_dtype, (uint64_t)c.experts_local * c.hidden, c.inter))) return rc;
+    if ((rc = make_map(&map_g, banks[MUMMU_BANK_GATE], c.act_dtype, (uint64_t)c.experts_local * c.inter, c.hidden))) return rc;
+    if ((rc = make_map(&map_u, banks[MUMMU_BANK_UP], c.act_dtype, (uint64_t)c.experts_local * c.inter, c.hidden))) return rc;
+    if ((rc = make_map(&map_d, banks[MUMMU_BANK_DOWN], c.act_dtype, (uint64_t)c.experts_local * c.hidden, c.inter))) return rc;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c.device);
     const size_t smem = tc_smem_bytes(c.experts_local);
@@ -490,9 +492,72 @@ static int launch_tc_typed(MummuMoe* m, const void* xs, int64_t rows_cap, const 
 // the tensor-map bound); ys: [rows, hidden] in ys_dtype (F32 or the activation dtype)
 int launch_experts_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts,
                       const int32_t* offsets, void* ys, int ys_dtype, cudaStream_t s) {
+    const void* banks[3] = {m->bank[0], m->bank[1], m->bank[2]};
     if (m->cfg.act_dtype == MUMMU_BF16)
-        return launch_tc_typed<__nv_bfloat16>(m, xs, rows_cap, counts, offsets, ys, ys_dtype, s);
-    return launch_tc_typed<__half>(m, xs, rows_cap, counts, offsets, ys, ys_dtype, s);
+        return launch_tc_typed<__nv_bfloat16>(m, xs, rows_cap, counts, offsets, ys, ys_dtype, banks, s);
+    return launch_tc_typed<__half>(m, xs, rows_cap, counts, offsets, ys, ys_dtype, banks, s);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Q4_K banks on the tensor cores: experts with rows are expanded to f16 (one warp per 144-byte
+// super-block: 8 values per lane, the reference's operation order of gguf.rs:1685-1726 in f32, one
+// rounding to f16), then the same two grouped GEMMs.  For calls with more rows than the
+// packed-weight kernels take (a prompt of more than 256 tokens).
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) q4k_expand_f16_kernel(const uint8_t* __restrict__ src, __half* __restrict__ dst,
+                                                             int64_t n_blocks, int64_t blocks_per_expert,
+                                                             const int32_t* __restrict__ counts) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); b < n_blocks; b += warps) {
+        if (counts[b / blocks_per_expert] == 0) continue;        // nobody routed here this call
+        const uint8_t* blk = src + (size_t)b * Q4K_BLOCK_BYTES;
+        const int j = lane >> 2, chunk = j >> 1, b0 = (lane & 3) * 8;
+        const float d = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(blk[2] | (blk[3] << 8))));
+        float sc, mn;
+        q4k_scale_min(blk + 4, j, sc, mn);
+        const float dsc = __fmul_rn(d, sc), off = __fmul_rn(dmin, mn);
+        const uint2 raw = *reinterpret_cast<const uint2*>(blk + 16 + chunk * 32 + b0);
+        const uint32_t w[2] = {raw.x, raw.y};
+        __half out[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+            const float q = (float)((j & 1) ? (byte >> 4) : (byte & 0x0Fu));
+            out[i] = __float2half_rn(__fsub_rn(__fmul_rn(dsc, q), off));
+        }
+        *reinterpret_cast<uint4*>(dst + (size_t)b * 256 + lane * 8) = *reinterpret_cast<const uint4*>(out);
+    }
+}
+
+bool q4k_tc_supported(const MummuMoeConfig& c, int64_t rows_total) {
+    return c.weight_dtype == MUMMU_Q4_K && c.act_dtype == MUMMU_F16 && c.hidden % 256 == 0 && c.inter % 256 == 0 &&
+           rows_total >= 1;
+}
+
+int launch_experts_q4k_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts, const int32_t* offsets,
+                          void* ys, int ys_dtype, cudaStream_t s) {
+    const MummuMoeConfig& c = m->cfg;
+    const int64_t per_bank = (int64_t)c.experts_local * c.inter * c.hidden;
+    // the image is scratch: a stack of layers that shares scratch shares it too (it lives in the
+    // layer the others adopted their scratch from, which must outlive them as for the rest)
+    MummuMoe* owner = m->scratch_donor && m->scratch_donor->cfg.experts_local == c.experts_local ? m->scratch_donor : m;
+    for (int b = 0; b < 3; ++b) {
+        if (owner->wexp[b]) continue;
+        MUMMU_CUDA_TRY(cudaMalloc((void**)&owner->wexp[b], (size_t)per_bank * sizeof(__half)));
+    }
+    const int64_t blocks_per_expert = (int64_t)c.inter * c.hidden / 256, n_blocks = blocks_per_expert * c.experts_local;
+    {
+        LaunchScope scope(m, s, "q4k_expand");
+        for (int b = 0; b < 3; ++b) {
+            q4k_expand_f16_kernel<<<148 * 8, 256, 0, s>>>((const uint8_t*)m->bank[b], owner->wexp[b], n_blocks,
+                                                          blocks_per_expert, counts);
+        }
+        MUMMU_CUDA_TRY(cudaGetLastError());
+    }
+    const void* banks[3] = {owner->wexp[0], owner->wexp[1], owner->wexp[2]};
+    return launch_tc_typed<__half>(m, xs, rows_cap, counts, offsets, ys, ys_dtype, banks, s);
 }
 
 int launch_gather_rows(MummuMoe* m, const void* x, const int32_t* row_token, void* xs, int64_t rows,

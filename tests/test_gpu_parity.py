@@ -356,6 +356,39 @@ def test_host_pointer_calls_replay_a_graph(M, cuda_lib):
     b.close()
 
 
+def test_q4k_prompt_sized_calls_take_the_tensor_cores(M, cuda_lib, olmoe_q4k_layer):
+    """More than 256 tokens on Q4_K experts (a prompt): the experts with rows are expanded to f16
+    and the tcgen05 grouped GEMMs run on them.  Small shape in full against the oracle; the OLMoE
+    shape at 600 tokens on sampled tokens (tokens are independent), and against the generic bank
+    (NO_TC) on every token; the kernel list shows which path ran."""
+    L = cuda_lib
+    H, I, E, K, T = 512, 256, 8, 2, 300
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=23)
+    gq, uq, dq = (q4k.quantize(b) for b in (gate, up, down))
+    xh = x.astype(np.float16)
+    m = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, gq, uq, dq)
+    m.set_profiling(True)
+    y = m.forward(xh, K, True).astype(np.float32)
+    names = set(m.take_profile())
+    assert {"q4k_expand", "tc_gate_up", "tc_down"} <= names, names
+    want, _, _ = O.moe_forward(xh.astype(np.float32), router, gq, uq, dq, K, True, q4k=True)
+    assert rel_err(y, want) < TOL_16
+    m.close()
+    H, I, E, K, router, (gq, uq, dq), xh = olmoe_q4k_layer
+    T = 600
+    rng = np.random.default_rng(4)
+    xl = np.concatenate([xh, (rng.standard_normal((T - xh.shape[0], H))).astype(np.float16)])
+    m = make_layer(M, L, H, I, E, K, L.F16, L.Q4_K, router, gq, uq, dq)
+    y = m.forward(xl, K, False).astype(np.float32)
+    pick = [0, 1, 255, 256, 300, 599]
+    want, _, _ = O.moe_forward(xl[pick].astype(np.float32), router, gq, uq, dq, K, False, q4k=True)
+    assert rel_err(y[pick], want) < TOL_16
+    m.set_switch("NO_TC", 1)
+    y_generic = m.forward(xl, K, False).astype(np.float32)
+    assert rel_err(y, y_generic) < TOL_16
+    m.close()
+
+
 def test_q4k_small_golden(M, cuda_lib):
     L = cuda_lib
     gold = np.load(os.path.join(HERE, "golden", "q4k_small.npz"))

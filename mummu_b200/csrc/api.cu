@@ -241,6 +241,8 @@ static int forward_device(MummuMoe* m, const void* x, void* y, int64_t tokens, i
             rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s);
         }
         if (rc) return rc;
+        if (m->sw.checked && (rc = launch_check_plan(m, m->ids, m->pos, m->row_token, m->counts, m->offsets, tokens, top_k, s)))
+            return rc;
         if ((rc = launch_decode_q4k(m, x, tokens, top_k, s))) return rc;
         return launch_combine(m, m->ys, MUMMU_F32, m->ids, m->wts, m->pos, tokens, top_k, y, s);
     }
@@ -248,6 +250,8 @@ static int forward_device(MummuMoe* m, const void* x, void* y, int64_t tokens, i
     if (prefill_tc_supported(c, tokens * top_k) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && !m->sw.no_tc) {
         // tensor-core path: sorted copy of the routed rows, two grouped GEMMs, 16-bit expert outputs
         if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
+        if (m->sw.checked && (rc = launch_check_plan(m, m->ids, m->pos, m->row_token, m->counts, m->offsets, tokens, top_k, s)))
+            return rc;
         if ((rc = launch_gather_rows(m, x, m->row_token, m->xs, tokens * top_k, s))) return rc;
         if ((rc = launch_experts_tc(m, m->xs, m->cap_tokens * c.top_k, m->counts, m->offsets, m->ys, c.act_dtype, s)))
             return rc;
@@ -256,12 +260,16 @@ static int forward_device(MummuMoe* m, const void* x, void* y, int64_t tokens, i
         // Q4_K with more tokens than the packed-weight kernels take: expand the experts that have
         // rows to f16, then the tensor-core path
         if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
+        if (m->sw.checked && (rc = launch_check_plan(m, m->ids, m->pos, m->row_token, m->counts, m->offsets, tokens, top_k, s)))
+            return rc;
         if ((rc = launch_gather_rows(m, x, m->row_token, m->xs, tokens * top_k, s))) return rc;
         if ((rc = launch_experts_q4k_tc(m, m->xs, m->cap_tokens * c.top_k, m->counts, m->offsets, m->ys, c.act_dtype, s)))
             return rc;
         return launch_combine(m, m->ys, c.act_dtype, m->ids, m->wts, m->pos, tokens, top_k, y, s);
     } else {
         if ((rc = launch_permute(m, m->ids, tokens, top_k, m->counts, m->offsets, m->row_token, m->pos, s))) return rc;
+        if (m->sw.checked && (rc = launch_check_plan(m, m->ids, m->pos, m->row_token, m->counts, m->offsets, tokens, top_k, s)))
+            return rc;
         int64_t max_rows = tokens;  // an expert serves a token at most once
         if ((rc = launch_experts_simt(m, x, c.act_dtype, m->row_token, m->counts, m->offsets, max_rows,
                                       tokens * top_k, m->ys, MUMMU_F32, -1, s)))
@@ -548,9 +556,12 @@ int32_t mummu_moe_route_grouped(MummuMoe* m, const void* x, int32_t tokens, int3
     // decode-sized calls: one launch (the router's last block groups the pairs); else two
     const GroupedOut out{counts, offsets, row_token, pos};
     rc = launch_router(m, x, tokens, top_k, norm, ids, w, counts, s, true, &out);
-    if (rc != MUMMU_ERR_UNSUPPORTED) return rc;
-    if ((rc = launch_router(m, x, tokens, top_k, norm, ids, w, counts, s))) return rc;
-    return launch_permute(m, ids, tokens, top_k, counts, offsets, row_token, pos, s);
+    if (rc == MUMMU_ERR_UNSUPPORTED) {
+        if ((rc = launch_router(m, x, tokens, top_k, norm, ids, w, counts, s))) return rc;
+        rc = launch_permute(m, ids, tokens, top_k, counts, offsets, row_token, pos, s);
+    }
+    if (rc) return rc;
+    return m->sw.checked ? launch_check_plan(m, ids, pos, row_token, counts, offsets, tokens, top_k, s) : MUMMU_OK;
 }
 
 int32_t mummu_moe_permute(MummuMoe* m, const int32_t* ids, int32_t tokens, int32_t top_k,
@@ -580,6 +591,12 @@ static int32_t experts_rows(MummuMoe* m, const void* xs, const int32_t* counts, 
     int64_t tokens_equiv = ((int64_t)rows + m->cfg.top_k - 1) / m->cfg.top_k;
     if ((rc = ensure_scratch(m, tokens_equiv))) return rc;
     cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    if (m->sw.checked && counts != m->counts) {
+        // the caller's counts are copied with the segments clipped to the rows the buffers hold
+        if ((rc = launch_check_counts(m, counts, m->counts, m->cfg.experts_local, rows, s))) return rc;
+        counts = m->counts;
+        planned = false;                     // offsets and work order are rebuilt from the safe copy
+    }
     if (!planned && (rc = launch_offsets_from_counts(m, counts, m->cfg.experts_local, m->offsets, s))) return rc;
     if (prefill_tc_supported(m->cfg, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !m->sw.no_tc)
         return launch_experts_tc(m, xs, rows, counts, m->offsets, ys, m->cfg.act_dtype, s);
@@ -612,6 +629,14 @@ int32_t mummu_moe_combine(MummuMoe* m, const void* ys, const int32_t* ids, const
     std::lock_guard<std::mutex> lock(m->mu);
     DeviceGuard guard(m->cfg.device);
     cudaStream_t s = stream ? (cudaStream_t)stream : m->stream;
+    if (m->sw.checked) {
+        // the caller's indices are copied into the layer's scratch with every one made safe
+        int rc;
+        if ((rc = ensure_scratch(m, tokens))) return rc;
+        if ((rc = launch_check_combine(m, ids, pos, m->ids, m->pos, (int64_t)tokens * top_k, s))) return rc;
+        ids = m->ids;
+        pos = m->pos;
+    }
     return launch_combine(m, ys, m->cfg.act_dtype, ids, w, pos, tokens, top_k, out, s);
 }
 

@@ -286,6 +286,11 @@ int launch_count(MummuMoe* m, const int32_t* ids, int64_t n, int32_t* counts, cu
 int launch_permute(MummuMoe* m, const int32_t* ids, int64_t tokens, int top_k,
                    const int32_t* counts, int32_t* offsets, int32_t* row_token, int32_t* pos,
                    cudaStream_t s);
+int launch_check_plan(MummuMoe* m, int32_t* ids, int32_t* pos, int32_t* row_token, const int32_t* counts,
+                      const int32_t* offsets, int64_t tokens, int top_k, cudaStream_t s);
+int launch_check_combine(MummuMoe* m, const int32_t* ids, const int32_t* pos, int32_t* ids_out, int32_t* pos_out,
+                         int64_t pairs, cudaStream_t s);
+int launch_check_counts(MummuMoe* m, const int32_t* counts, int32_t* counts_out, int n, int64_t rows, cudaStream_t s);
 int launch_combine(MummuMoe* m, const void* ys, int ys_dtype, const int32_t* ids, const float* w,
                    const int32_t* pos, int64_t tokens, int top_k, void* out, cudaStream_t s);
 int launch_offsets_from_counts(MummuMoe* m, const int32_t* counts, int n, int32_t* offsets,

@@ -980,6 +980,106 @@ int launch_router(MummuMoe* m, const void* x, int64_t tokens, int top_k, int nor
 }
 
 // ---------------------------------------------------------------------------------------------
+// checked mode (switch CHECKED): the routing plan drives every hand-computed address of the
+// layer.  These kernels verify it and make it safe in place: a bad index is replaced by one that
+// stays inside its buffer, and the status word is raised (MUMMU_ERR_CONTRACT at the next sync).
+// The reference arms its backend's bounds validation for tests the same way (burn.toml:17).
+// ---------------------------------------------------------------------------------------------
+// whole plan: pair i = (token, slot): ids[i] an expert, pos[i] inside that expert's segment,
+// row_token[pos[i]] the pair's token; per expert: segments tile [0, pairs)
+__global__ void check_plan_kernel(int32_t* ids, int32_t* pos, int32_t* row_token, const int32_t* counts,
+                                  const int32_t* offsets, int64_t pairs, int top_k, int E, int32_t* status) {
+    bool bad = false;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < pairs; i += (int64_t)gridDim.x * blockDim.x) {
+        int e = ids[i];
+        if (e < 0 || e >= E) {
+            bad = true;
+            ids[i] = e = 0;
+        }
+        int p = pos[i];
+        if (p < 0 || p >= pairs) {
+            bad = true;
+            pos[i] = p = 0;
+        }
+        if (p < offsets[e] || p >= offsets[e] + counts[e]) bad = true;
+        const int t = row_token[i];                      // entry i of the sorted order
+        if (t < 0 || (int64_t)t * top_k >= pairs) {
+            bad = true;
+            row_token[i] = 0;
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        int64_t run = 0;
+        for (int e = 0; e < E; ++e) {
+            if (offsets[e] != run || counts[e] < 0) bad = true;
+            run += counts[e];
+        }
+        if (run != pairs) bad = true;
+    }
+    if (bad) atomicOr(status, STATUS_BOUNDS);
+}
+
+// caller-given (ids, pos) of a combine: copied, with every index made safe
+__global__ void check_combine_kernel(const int32_t* ids, const int32_t* pos, int32_t* ids_out, int32_t* pos_out,
+                                     int64_t pairs, int E, int32_t* status) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < pairs; i += (int64_t)gridDim.x * blockDim.x) {
+        int e = ids[i], p = pos[i];
+        if (e < 0 || e >= E || p < 0 || p >= pairs) {
+            atomicOr(status, STATUS_BOUNDS);
+            e = min(max(e, 0), E - 1);
+            p = 0;
+        }
+        ids_out[i] = e;
+        pos_out[i] = p;
+    }
+}
+
+// caller-given per-expert row counts: copied, clipped so that the segments stay inside `rows`
+__global__ void check_counts_kernel(const int32_t* counts, int32_t* counts_out, int n, int64_t rows, int32_t* status) {
+    if (blockIdx.x || threadIdx.x) return;
+    int64_t run = 0;
+    bool bad = false;
+    for (int e = 0; e < n; ++e) {
+        int64_t c = counts[e];
+        if (c < 0 || run + c > rows) {
+            bad = true;
+            c = c < 0 ? 0 : rows - run;
+        }
+        counts_out[e] = (int32_t)c;
+        run += c;
+    }
+    if (bad) atomicOr(status, STATUS_BOUNDS);
+}
+
+int launch_check_plan(MummuMoe* m, int32_t* ids, int32_t* pos, int32_t* row_token, const int32_t* counts,
+                      const int32_t* offsets, int64_t tokens, int top_k, cudaStream_t s) {
+    const int64_t pairs = tokens * top_k;
+    if (pairs == 0) return MUMMU_OK;
+    LaunchScope scope(m, s, "check_plan");
+    check_plan_kernel<<<(unsigned)std::min<int64_t>((pairs + 255) / 256, 1024), 256, 0, s>>>(
+        ids, pos, row_token, counts, offsets, pairs, top_k, m->cfg.experts, m->status);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+int launch_check_combine(MummuMoe* m, const int32_t* ids, const int32_t* pos, int32_t* ids_out, int32_t* pos_out,
+                         int64_t pairs, cudaStream_t s) {
+    if (pairs == 0) return MUMMU_OK;
+    LaunchScope scope(m, s, "check_combine");
+    check_combine_kernel<<<(unsigned)std::min<int64_t>((pairs + 255) / 256, 1024), 256, 0, s>>>(ids, pos, ids_out, pos_out,
+                                                                                             pairs, m->cfg.experts, m->status);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+int launch_check_counts(MummuMoe* m, const int32_t* counts, int32_t* counts_out, int n, int64_t rows, cudaStream_t s) {
+    LaunchScope scope(m, s, "check_counts");
+    check_counts_kernel<<<1, 32, 0, s>>>(counts, counts_out, n, rows, m->status);
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
 // histogram / offsets / permute
 // ---------------------------------------------------------------------------------------------
 __global__ void count_kernel(const int32_t* ids, int64_t n, int E, int32_t* counts, int32_t* status) {

@@ -632,3 +632,61 @@ def test_expert_exec_methods(M, cuda_lib, kind):
     with pytest.raises(M.MoeContractError):
         M.CudaExpert(m, E).run(xin.reshape(-1), rows, H)
     m.close()
+
+
+# ---- checked mode -------------------------------------------------------------------------------
+
+def test_checked_mode_passes_good_plans_and_reports_bad_ones(M, cuda_lib):
+    """Switch CHECKED: the routing plan behind every computed address is verified on the device.
+    Good plans give bit-identical results with no report; a caller-given index outside its buffer
+    is made safe, the call completes, and the next sync reports it.  (The buffers here have slack
+    behind their stated size, so not even an unchecked build would leave allocated memory.)"""
+    import torch
+    L = cuda_lib
+    for act, wdt, T in ((L.F16, L.Q4_K, 40), (L.BF16, L.BF16, 300), (L.F32, L.F32, 33)):
+        H, I, E, K = 512, 256, 8, 2
+        router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=31)
+        if wdt == L.Q4_K:
+            banks = [q4k.quantize(b) for b in (gate, up, down)]
+            xin = x.astype(np.float16)
+        elif wdt == L.BF16:
+            banks = [bf16_bits(b) for b in (gate, up, down)]
+            xin = bf16_bits(x)
+        else:
+            banks, xin = [gate, up, down], x
+        m = make_layer(M, L, H, I, E, K, act, wdt, router, *banks)
+        plain = m.forward(xin, K, True)
+        m.set_switch("CHECKED", 1)
+        checked = m.forward(xin, K, True)
+        m.sync()                                         # nothing to report
+        assert np.array_equal(np.asarray(plain).view(np.uint8), np.asarray(checked).view(np.uint8))
+        m.close()
+    H, I, E, K, T = 256, 128, 8, 2, 37
+    router, gate, up, down, x = synth.moe_layer(H, I, E, T, cfg_seed=12)
+    m = make_layer(M, L, H, I, E, K, L.F32, L.F32, router, gate, up, down)
+    m.set_switch("CHECKED", 1)
+    xd = torch.from_numpy(x).cuda()
+    ids, w, counts, offsets, row_token, pos = m.route_grouped(xd, K, False)
+    m.sync()
+    slack = 8
+    xs = torch.zeros(T * K + slack, H, device="cuda")
+    xs[:T * K] = xd[row_token.long()]
+    ys = torch.zeros_like(xs)
+    m.experts_grouped(xs[:T * K], counts, ys[:T * K])
+    out = torch.empty_like(xd)
+    m.combine(ys[:T * K], ids, w, pos, out)
+    m.sync()
+    assert torch.equal(out, m.forward(xd, K, False))
+    bad_pos = pos.clone()
+    bad_pos[5] = T * K + 1                               # behind the rows the call states
+    m.combine(ys[:T * K], ids, w, bad_pos, out)
+    with pytest.raises(M.MoeContractError, match="left its buffer"):
+        m.sync()
+    assert torch.isfinite(out).all()
+    bad_counts = counts.clone()
+    bad_counts[E - 1] += 3                               # segments run past the rows the call states
+    m.experts_grouped(xs[:T * K], bad_counts, ys[:T * K])
+    with pytest.raises(M.MoeContractError, match="left its buffer"):
+        m.sync()
+    m.sync()
+    m.close()

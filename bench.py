@@ -41,7 +41,7 @@ METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the gate/up kernel, from ncu captures
 # (summaries under profiles/), keyed by (tokens, experts hit); other shapes report null
-GATE_UP_TRAFFIC = {}
+GATE_UP_TRAFFIC = {(64, 64): 156.35e6}
 
 
 def parse():
@@ -55,6 +55,8 @@ def parse():
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--ep-layers", type=int, default=48, help="layers of the Qwen3-shaped expert-parallel stack")
+    ap.add_argument("--new-tokens", type=int, default=128, help="decode steps of the olmoe_decode workload")
+    ap.add_argument("--batches", default="1,32", help="batch sizes of the olmoe_decode workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sub", action="store_true", help="headline only (profiling runs)")
     return ap.parse_args()
@@ -496,10 +498,10 @@ def measure_model(ctx) -> dict:
     from mummu_b200 import _lib as L
     from mummu_b200.olmoe import OlmoeConfig, OlmoeDecoder
     cfg = OlmoeConfig()
-    prompt, n_new = 512, 128
+    prompt, n_new = 512, ctx.args.new_tokens
     peaks = ctx.peaks
     results = {}
-    for B in (1, 32):
+    for B in [int(b) for b in ctx.args.batches.split(",")]:
         chunk = max(1, 2048 // B)                       # prompt fed in chunks of <= 2048 tokens over the batch
         dec = OlmoeDecoder(cfg, device=ctx.local_rank, expert_dtype=L.Q4_K, max_batch=B, max_ctx=prompt + n_new,
                            max_tokens=B * chunk)
@@ -762,8 +764,9 @@ def main() -> int:
                      "roofline": r.get("roofline"), "prefill": r})
     elif args.workload == "olmoe_decode":
         r = measure_model(ctx)
-        line.update({"metric": "olmoe_decode_tokens_per_s", "value": r["batch_32"]["decode_tok_per_s"], "unit": UNIT,
-                     "n_gpus": 1, "steps": r["new_tokens"], "warmup": 0, "ms_per_step": r["batch_32"]["ms_per_token_step"],
+        big = r["batch_" + str(max(int(b) for b in args.batches.split(",")))]
+        line.update({"metric": "olmoe_decode_tokens_per_s", "value": big["decode_tok_per_s"], "unit": UNIT,
+                     "n_gpus": 1, "steps": r["new_tokens"], "warmup": 0, "ms_per_step": big["ms_per_token_step"],
                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": r["dtype"],
                      "data": "synthetic", "config": {"workload": r["workload"]}, "olmoe_decode": r})
     elif args.workload == "ep_qwen3":

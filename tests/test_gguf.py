@@ -181,3 +181,76 @@ def test_loader_refuses_what_the_bank_cannot_take(tmp_path):
     gguf.write_gguf(p, META, base[:3])
     with pytest.raises(KeyError, match="ffn_down_exps"):
         gguf.load_moe_layer(gguf.GgufFile.open(p), 0)
+
+
+# ---- cross-check with the independent `gguf` package (llama.cpp's gguf-py) ------------------------
+
+def _gguf_py():
+    return pytest.importorskip("gguf", reason="the gguf package is not installed")
+
+
+def test_reads_a_file_written_by_the_gguf_package(tmp_path):
+    """The reader against a writer it shares no code with: metadata of several types, an array, and
+    F32 / F16 / Q4_K tensors placed by gguf-py's own alignment logic.  Q4_K bytes must come back
+    verbatim and decode (oracle) to what gguf-py's own dequantizer gives."""
+    g = _gguf_py()
+    from oracle import oracle as O
+    H, I, E = 256, 256, 4
+    router, gate, up, down, _ = synth.moe_layer(H, I, E, 1, cfg_seed=77)
+    gq = q4k.quantize(gate)                                   # uint8 [E, I, H/256*144]
+    p = str(tmp_path / "pkg.gguf")
+    w = g.GGUFWriter(p, "olmoe")
+    w.add_uint32("olmoe.embedding_length", H)
+    w.add_uint32("olmoe.expert_feed_forward_length", I)
+    w.add_uint32("olmoe.expert_count", E)
+    w.add_uint32("olmoe.expert_used_count", 2)
+    w.add_uint32("olmoe.block_count", 1)
+    w.add_bool("olmoe.expert_weights_norm", True)
+    w.add_float32("olmoe.rope.freq_base", 10000.0)
+    w.add_array("tokenizer.ggml.tokens", ["a", "bc", "def"])
+    w.add_tensor("blk.0.ffn_gate_inp.weight", np.ascontiguousarray(router.T))
+    w.add_tensor("blk.0.attn_norm.weight", np.linspace(0, 1, H, dtype=np.float16))
+    w.add_tensor("blk.0.ffn_gate_exps.weight", gq.reshape(E, I, -1), raw_dtype=g.GGMLQuantizationType.Q4_K)
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+    f = gguf.GgufFile.open(p)
+    assert f.architecture() == "olmoe" and f.version == 3
+    assert f.get("olmoe.expert_count") == E and f.get("olmoe.expert_weights_norm") is True
+    assert abs(f.get("olmoe.rope.freq_base") - 10000.0) < 1e-3
+    assert f.get("tokenizer.ggml.tokens") == ["a", "bc", "def"]
+    shape = gguf.olmoe_moe_shape(f)
+    assert (shape.hidden_size, shape.expert_intermediate_size, shape.num_experts, shape.num_experts_per_tok,
+            shape.norm_topk_prob, shape.num_hidden_layers) == (H, I, E, 2, True, 1)
+    t = f.tensor("blk.0.ffn_gate_exps.weight")
+    assert t.dtype == "Q4_K" and t.shape == (E, I, H) and t.offset % f.alignment == 0
+    raw = f.tensor_bytes("blk.0.ffn_gate_exps.weight")
+    assert np.array_equal(raw.reshape(-1), gq.reshape(-1))
+    want = g.quants.dequantize(gq.reshape(E * I, -1), g.GGMLQuantizationType.Q4_K).reshape(E, I, H)
+    got = O.dequant_q4_k(raw).reshape(E, I, H)
+    assert np.array_equal(got.view(np.uint32), np.asarray(want, np.float32).view(np.uint32))
+    assert np.array_equal(f.tensor_array("blk.0.ffn_gate_inp.weight"), np.ascontiguousarray(router.T))
+    assert f.tensor("blk.0.attn_norm.weight").dtype == "F16"
+    f.close()
+
+
+def test_the_gguf_package_reads_a_file_written_here(tmp_path):
+    """The other direction: the writer used by the other tests produces files gguf-py's reader
+    accepts, with the same keys, tensor types, shapes and bytes."""
+    g = _gguf_py()
+    p = str(tmp_path / "ours.gguf")
+    truth = synthetic_file(p, alignment=64, layers=1)
+    r = g.GGUFReader(p)
+    assert r.alignment == 64
+    arch = r.fields["general.architecture"]
+    assert bytes(arch.parts[arch.data[0]]).decode() == "olmoe"
+    assert int(r.fields["olmoe.expert_count"].parts[-1][0]) == 4
+    by_name = {t.name: t for t in r.tensors}
+    gate = by_name["blk.0.ffn_gate_exps.weight"]
+    assert gate.tensor_type == g.GGMLQuantizationType.Q4_K
+    assert list(gate.shape) == [256, 256, 4]                      # ggml order, innermost first
+    assert np.array_equal(np.asarray(gate.data).reshape(-1), truth[0][1]["gate"].reshape(-1))
+    inp = by_name["blk.0.ffn_gate_inp.weight"]
+    assert inp.tensor_type == g.GGMLQuantizationType.F32
+    assert np.array_equal(np.asarray(inp.data).reshape(4, 256), np.ascontiguousarray(truth[0][0].T))

@@ -198,7 +198,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t fmt = sizeof(TIN) == 2 && std::is_same<TIN, __nv_bfloat16>::value ? 1u : 0u;
-            const uint32_t idesc = make_idesc(fmt, 128, 128);
+            // one M=128, N=256, K=16 MMA per K step: the two 128-row weight tiles of a stage lie back
+            // to back in shared memory (8-row groups 1024 bytes apart throughout), so one descriptor
+            // covers both and the accumulator's two halves are columns 0..127 and 128..255
+            const uint32_t idesc = make_idesc(fmt, 128, 256);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tcount) {
@@ -212,14 +215,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     tc_fence_after();
                     const uint32_t sa = smem_u32(tiles + s * TC_STAGE_BYTES);
                     const uint64_t da = smem_desc_sw128(sa);
-                    const uint64_t db0 = smem_desc_sw128(sa + TC_BM * TC_BK * 2);
-                    const uint64_t db1 = smem_desc_sw128(sa + 2 * TC_BM * TC_BK * 2);
+                    const uint64_t db = smem_desc_sw128(sa + TC_BM * TC_BK * 2);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k) {
-                        const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
-                        umma_f16(d0, da + 2 * k, db0 + 2 * k, idesc, acc);
-                        umma_f16(d0 + 128u, da + 2 * k, db1 + 2 * k, idesc, acc);
-                    }
+                    for (int k = 0; k < TC_BK / 16; ++k) umma_f16(d0, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     umma_commit(empty0 + 8 * s);          // stage reusable once these MMAs have read it
                 }
                 if (ok) umma_commit(tfull0 + 8 * as);      // accumulator complete

@@ -231,7 +231,12 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
         __syncthreads();
         const int lane = threadIdx.x & 31;
         const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-        for (int64_t p = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < a.rows; p += warps) {
+        // Every rank walks its sorted rows starting at the rows of the NEXT rank's experts: at any
+        // moment the ranks then write to different destinations instead of all to the same one
+        // (whose ingress would carry the whole group's traffic while the other links idle).
+        const int64_t rot = s_off[((a.rank + 1) % a.world) * a.EL];
+        for (int64_t q = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); q < a.rows; q += warps) {
+            const int64_t p = q + rot < a.rows ? q + rot : q + rot - a.rows;
             int lo = 0, hi = a.E;                                // last e with offsets[e] <= p
             while (hi - lo > 1) {
                 const int mid = (lo + hi) >> 1;

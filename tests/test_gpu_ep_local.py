@@ -43,14 +43,15 @@ def build_group(torch, L, moe, epmod, cfg, world, act, wdt, banks_dev, router, T
     return ws, group
 
 
-@pytest.mark.parametrize("world", [2, 8])
-def test_ep_stages_bf16_qwen3_layer_shape(cuda_lib, world):
+@pytest.mark.parametrize("world,Tr", [(2, 48), (8, 48), (2, 160)])
+def test_ep_stages_bf16_qwen3_layer_shape(cuda_lib, world, Tr):
     """The expert-parallel configuration's layer: hidden 2048, 128 experts, top-8, intermediate 768,
-    bf16; 48 tokens per rank (ragged segments, some experts without rows)."""
+    bf16; 48 tokens per rank (ragged segments, some experts without rows), and 160 per rank (1280
+    rows: enough for the dispatch to move its rows through the copy engine)."""
     import torch
     from mummu_b200 import ep as epmod, moe
     L = cuda_lib
-    H, I, E, K, Tr = 2048, 768, 128, 8, 48
+    H, I, E, K = 2048, 768, 128, 8
     cfg = moe.SparseMoeConfig(H, I, E, K)
     g = torch.Generator(device="cuda").manual_seed(50 + world)
     rnd = lambda *s: (torch.randn(*s, generator=g, device="cuda") * 0.02)

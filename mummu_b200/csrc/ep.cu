@@ -316,7 +316,10 @@ __global__ void __launch_bounds__(256) ep_gather_tokens_kernel(const uint4* x, P
     const int64_t items = (int64_t)world * tokens;               // (destination rank, token)
     const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
     for (int64_t it = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); it < items; it += warps) {
-        const int d = (int)(it / tokens), t = (int)(it - (int64_t)d * tokens);
+        // destinations in a different order on every rank, starting with the next one (no rank is
+        // everybody's first target)
+        const int dq = (int)(it / tokens), t = (int)(it - (int64_t)dq * tokens);
+        const int d = (dq + rank + 1) % world;
         copy_row(x + (size_t)t * vec_per_row,
                  reinterpret_cast<uint4*>(gx.ptr[d]) + ((size_t)rank * tokens + t) * vec_per_row, vec_per_row, lane);
     }

@@ -639,8 +639,12 @@ def measure_ep(ctx, shape: dict) -> dict:
            "n_gpus": world, "steps": steps, "ms_per_step": ms, "ms_per_step_min": min(win), "timed_windows": len(win),
            "tokens_per_s": total_tokens * NL / (ms * 1e-3), "us_per_layer": 1e3 * ms / NL,
            "launch": "one CUDA graph per step" if is_graph else "eager",
-           "parallelism": (f"ep{world}: {el} experts per GPU, dispatch by peer stores and combine by peer loads over "
-                           "NVLink, one-way device-side signals, no host sync") if world > 1 else "single GPU",
+           "parallelism": ((f"ep{world}: {el} experts per GPU, " +
+                            ("tokens pushed to every GPU, replicated bit-reproducible routing, expert outputs pushed back"
+                             if q4 and plan is None else
+                             "rows pushed to the experts' GPUs, expert outputs pushed back from the down GEMM's epilogue") +
+                            ": peer stores over NVLink, one-way device-side signals, no host sync, no collective")
+                           if world > 1 else "single GPU"),
            "l2": "inputs larger than L2: %.2f GB of expert weights per GPU rotate every step"
                  % (NL * el * 3 * h * i * (144 / 256 if q4 else 2) / 1e9),
            "e2e": {"value": total_tokens * NL / (e2e_ms * 1e-3), "unit": UNIT,

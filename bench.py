@@ -57,6 +57,8 @@ def parse():
     ap.add_argument("--ep-layers", type=int, default=48, help="layers of the Qwen3-shaped expert-parallel stack")
     ap.add_argument("--new-tokens", type=int, default=128, help="decode steps of the olmoe_decode workload")
     ap.add_argument("--batches", default="1,32", help="batch sizes of the olmoe_decode workload")
+    ap.add_argument("--ep-form", default="auto", choices=["auto", "gathered", "hops"],
+                    help="decode-sized expert-parallel steps: tokens to every GPU (gathered) or the three-hop exchange")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sub", action="store_true", help="headline only (profiling runs)")
     return ap.parse_args()
@@ -554,7 +556,8 @@ def measure_ep(ctx, shape: dict) -> dict:
     mine = plan.rank_experts(rank).tolist() if plan is not None else list(range(rank * el, rank * el + el))
     # decode-sized steps take the small-batch form (every token to every rank), whose return buffer
     # is indexed by the common sorted order: as many rows as all ranks route together
-    ws = (PeerWorkspace(None, ctx.local_rank, world * T * k, h, slots_total, back_rows=world * T * k if q4 else 0)
+    gathered = q4 and (args.ep_form == "gathered" or (args.ep_form == "auto" and world * T * k <= 1024))
+    ws = (PeerWorkspace(None, ctx.local_rank, world * T * k, h, slots_total, back_rows=world * T * k if gathered else 0)
           if world > 1 else None)
     layers = []
     for l in range(NL):
@@ -641,7 +644,7 @@ def measure_ep(ctx, shape: dict) -> dict:
            "launch": "one CUDA graph per step" if is_graph else "eager",
            "parallelism": ((f"ep{world}: {el} experts per GPU, " +
                             ("tokens pushed to every GPU, replicated bit-reproducible routing, expert outputs pushed back"
-                             if q4 and plan is None else
+                             if gathered and plan is None else
                              "rows pushed to the experts' GPUs, expert outputs pushed back from the down GEMM's epilogue") +
                             ": peer stores over NVLink, one-way device-side signals, no host sync, no collective")
                            if world > 1 else "single GPU"),

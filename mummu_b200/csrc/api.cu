@@ -600,6 +600,15 @@ static int32_t experts_rows(MummuMoe* m, const void* xs, const int32_t* counts, 
     if (!planned && (rc = launch_offsets_from_counts(m, counts, m->cfg.experts_local, m->offsets, s))) return rc;
     if (prefill_tc_supported(m->cfg, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !m->sw.no_tc)
         return launch_experts_tc(m, xs, rows, counts, m->offsets, ys, m->cfg.act_dtype, s);
+    // A shard with few experts and many rows each (expert parallelism over many ranks at decode
+    // sizes: 8 experts x 64 rows): the packed-weight kernels would expand every expert's weights once
+    // per 16-row pass; expanding them once to f16 and running the tensor-core GEMMs is cheaper.
+    // `rows` bounds all ranks' rows; this shard expects its share.
+    const int shards = m->cfg.experts / m->cfg.experts_local;
+    const int64_t rows_per_expert = (int64_t)rows / shards / m->cfg.experts_local;
+    const bool few_fat_experts = m->cfg.experts_local <= 8 && rows_per_expert >= 32;
+    if (few_fat_experts && q4k_tc_supported(m->cfg, rows) && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && !m->sw.no_tc)
+        return launch_experts_q4k_tc(m, xs, rows, counts, m->offsets, ys, m->cfg.act_dtype, s);
     if (m->cfg.weight_dtype == MUMMU_Q4_K && m->cfg.act_dtype == MUMMU_F16 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 &&
         rows <= 8192 && m->cfg.hidden <= 8192 && m->cfg.inter <= 8192) {
         // decode regime: packed-weight kernels (f32 out), then narrowed to the activation dtype

@@ -260,6 +260,11 @@ def test_ep_hot_expert_placement_changes_loads_not_results(cuda_lib, weights):
                  moe.q4k_quantize_device(rnd(E, H, I)).view(E, -1)]
         xs = [torch.randn(Tr, H, generator=g, device="cuda").to(torch.float16) for _ in range(world)]
     ws, group = build_group(torch, L, moe, epmod, cfg, world, act, wdt, banks, router, Tr, bias=bias)
+    if weights == "q4k":
+        # 8 experts per rank would take the expand-to-f16 path, 10 slots per rank the packed-weight
+        # kernels: pin both groups to the same kernels, the comparison below is bit for bit
+        for ep in group:
+            ep.moe.set_switch("NO_TC", 1)
     ys = run_group(torch, group, ws.views, xs, K, True)
     torch.cuda.synchronize()
     hits = np.zeros(E, dtype=np.uint64)
@@ -277,6 +282,8 @@ def test_ep_hot_expert_placement_changes_loads_not_results(cuda_lib, weights):
         ep = epmod.ExpertParallelMoe(cfg, device=0, act_dtype=act, weight_dtype=wdt, max_tokens=Tr,
                                      workspace=ws2.views[r], rank=r, world=world, placement=plan)
         ep.set_router(router, bias=bias)
+        if weights == "q4k":
+            ep.moe.set_switch("NO_TC", 1)
         idx = torch.from_numpy(plan.rank_experts(r)).cuda()
         ep.set_local_banks(*(b.index_select(0, idx).contiguous() for b in banks))
         placed.append(ep)
@@ -320,8 +327,9 @@ def test_ep_hot_expert_placement_changes_loads_not_results(cuda_lib, weights):
 @pytest.mark.parametrize("world,Tr", [(2, 24), (8, 64)])
 def test_ep_gathered_decode_form(cuda_lib, world, Tr):
     """The small-batch form: tokens to every rank, every rank routes them all and runs its own
-    experts, outputs back.  Stage by stage on one stream; bit-equal to the three-hop form (same
-    kernels on the same rows of an expert in the same order) and checked against the oracle."""
+    experts, outputs back.  Stage by stage on one stream; bit-equal to the three-hop form where
+    both run the packed-weight kernels (same rows of an expert in the same order), and checked
+    against the oracle."""
     import torch
     from mummu_b200 import ep as epmod, moe
     L = cuda_lib
@@ -359,7 +367,13 @@ def test_ep_gathered_decode_form(cuda_lib, world, Tr):
         ep.moe.sync()
     for r in range(world):
         assert torch.equal(ys[r], ys_again[r])
-        assert torch.equal(ys[r], ys_hops[r])
+        if world == 2:
+            assert torch.equal(ys[r], ys_hops[r])
+        else:
+            # 8 experts with about 64 rows each per rank: the three-hop form expands them to f16 for
+            # the tensor cores, this form keeps the packed-weight kernels - same layer, other roundings
+            a, b = ys[r].float(), ys_hops[r].float()
+            assert (a - b).abs().max().item() / b.abs().max().item() < 2e-2
     gq, uq, dq = (b.cpu().numpy() for b in banks)
     for r in (0, world - 1):
         pick = [0, Tr // 2, Tr - 1]

@@ -313,6 +313,7 @@ int launch_block_dequant(const void* src, int dtype, float* dst, int64_t rows, i
 bool prefill_tc_supported(const MummuMoeConfig& c, int64_t rows_total);
 int launch_gather_rows(MummuMoe* m, const void* x, const int32_t* row_token, void* xs, int64_t rows,
                        cudaStream_t s);
+int launch_block_expand_f16(MummuMoe* m, int which, __half* dst, const int32_t* counts, cudaStream_t s);
 bool q4k_tc_supported(const MummuMoeConfig& c, int64_t rows_total);
 int launch_experts_q4k_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts, const int32_t* offsets,
                           void* ys, int ys_dtype, cudaStream_t s);

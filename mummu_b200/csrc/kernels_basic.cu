@@ -1412,6 +1412,44 @@ __global__ void block_dequant_kernel(const uint8_t* src, float* dst, int64_t row
     }
 }
 
+// rows of a block-quantised bank -> f16 [rows, cols], eight values per thread, only for experts
+// that have rows this call (the image feeds the tensor-core GEMMs; the element decoders keep the
+// reference's operation order in f32, the f16 rounding comes last)
+template <typename TW>
+__global__ void block_expand_f16_kernel(const uint8_t* src, __half* dst, int64_t rows, int64_t cols, size_t row_bytes,
+                                        int64_t rows_per_expert, const int32_t* counts) {
+    const int64_t n8 = rows * cols / 8;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = (i * 8) / cols;
+        if (counts[r / rows_per_expert] == 0) continue;
+        const int k0 = (int)(i * 8 - r * cols);
+        const uint8_t* row = src + (size_t)r * row_bytes;
+        __half out[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) out[u] = __float2half_rn(load_w<TW>(row, k0 + u));
+        *reinterpret_cast<uint4*>(dst + i * 8) = *reinterpret_cast<const uint4*>(out);
+    }
+}
+
+int launch_block_expand_f16(MummuMoe* m, int which, __half* dst, const int32_t* counts, cudaStream_t s) {
+    const MummuMoeConfig& c = m->cfg;
+    const int64_t out_dim = which == MUMMU_BANK_DOWN ? c.hidden : c.inter, cols = which == MUMMU_BANK_DOWN ? c.inter : c.hidden;
+    const int64_t rows = out_dim * c.experts_local;
+    const size_t row_bytes = bank_row_bytes(c, which);
+    const unsigned blocks = (unsigned)std::min<int64_t>((rows * cols / 8 + 255) / 256, 148 * 16);
+    const uint8_t* p = (const uint8_t*)m->bank[which];
+    switch (c.weight_dtype) {
+        case MUMMU_Q8_0: block_expand_f16_kernel<q80_t><<<blocks, 256, 0, s>>>(p, dst, rows, cols, row_bytes, out_dim, counts); break;
+        case MUMMU_Q5_K: block_expand_f16_kernel<q5k_t><<<blocks, 256, 0, s>>>(p, dst, rows, cols, row_bytes, out_dim, counts); break;
+        case MUMMU_Q6_K: block_expand_f16_kernel<q6k_t><<<blocks, 256, 0, s>>>(p, dst, rows, cols, row_bytes, out_dim, counts); break;
+        default:
+            set_error("block expand: dtype %d has no generic expander", c.weight_dtype);
+            return MUMMU_ERR_CONTRACT;
+    }
+    MUMMU_CUDA_TRY(cudaGetLastError());
+    return MUMMU_OK;
+}
+
 int launch_block_dequant(const void* src, int dtype, float* dst, int64_t rows, int64_t cols, size_t row_bytes,
                          cudaStream_t s) {
     const int64_t n = rows * cols;

@@ -529,9 +529,11 @@ __global__ void __launch_bounds__(256) q4k_expand_f16_kernel(const uint8_t* __re
     }
 }
 
+// Q4_K and, through the generic element decoders, its sibling block formats
 bool q4k_tc_supported(const MummuMoeConfig& c, int64_t rows_total) {
-    return c.weight_dtype == MUMMU_Q4_K && c.act_dtype == MUMMU_F16 && c.hidden % 256 == 0 && c.inter % 256 == 0 &&
-           rows_total >= 1;
+    const bool packed = c.weight_dtype == MUMMU_Q4_K || c.weight_dtype == MUMMU_Q8_0 || c.weight_dtype == MUMMU_Q5_K ||
+                        c.weight_dtype == MUMMU_Q6_K;
+    return packed && c.act_dtype == MUMMU_F16 && c.hidden % 256 == 0 && c.inter % 256 == 0 && rows_total >= 1;
 }
 
 int launch_experts_q4k_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const int32_t* counts, const int32_t* offsets,
@@ -546,7 +548,13 @@ int launch_experts_q4k_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const i
         MUMMU_CUDA_TRY(cudaMalloc((void**)&owner->wexp[b], (size_t)per_bank * sizeof(__half)));
     }
     const int64_t blocks_per_expert = (int64_t)c.inter * c.hidden / 256, n_blocks = blocks_per_expert * c.experts_local;
-    {
+    if (c.weight_dtype != MUMMU_Q4_K) {
+        LaunchScope scope(m, s, "block_expand");
+        for (int b = 0; b < 3; ++b) {
+            int rc = launch_block_expand_f16(m, b, owner->wexp[b], counts, s);
+            if (rc) return rc;
+        }
+    } else {
         LaunchScope scope(m, s, "q4k_expand");
         for (int b = 0; b < 3; ++b) {
             q4k_expand_f16_kernel<<<148 * 8, 256, 0, s>>>((const uint8_t*)m->bank[b], owner->wexp[b], n_blocks,

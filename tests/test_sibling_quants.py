@@ -44,18 +44,18 @@ def test_q8_0_block():
     assert out[0] == 2.0 and out[1] == -0.5 and out[31] == -64.0 and out[2] == 0.0
 
 
-def random_blocks(kind, n_blocks, seed):
+def random_blocks(kind, n_blocks, seed, d_scale=1.0):
     """Every byte pattern is a valid block; f16 scales kept small and finite."""
     elems, nbytes = FORMATS[kind]
     rng = np.random.default_rng(seed)
     raw = rng.integers(0, 256, size=(n_blocks, nbytes), dtype=np.uint8)
-    d = np.frombuffer(rng.uniform(0.0005, 0.003, n_blocks).astype(np.float16).tobytes(), np.uint8).reshape(n_blocks, 2)
+    d = np.frombuffer(rng.uniform(0.0005 * d_scale, 0.003 * d_scale, n_blocks).astype(np.float16).tobytes(), np.uint8).reshape(n_blocks, 2)
     if kind == "Q6_K":
         raw[:, 208:210] = d
     else:
         raw[:, 0:2] = d
     if kind == "Q5_K":
-        raw[:, 2:4] = np.frombuffer(rng.uniform(0.0005, 0.003, n_blocks).astype(np.float16).tobytes(), np.uint8).reshape(n_blocks, 2)
+        raw[:, 2:4] = np.frombuffer(rng.uniform(0.0005 * d_scale, 0.003 * d_scale, n_blocks).astype(np.float16).tobytes(), np.uint8).reshape(n_blocks, 2)
     return raw
 
 
@@ -86,4 +86,40 @@ def test_sibling_format_layer(kind):
     assert np.array_equal(ids, oid) and np.array_equal(w.view(np.uint32), ow.view(np.uint32))
     err = np.linalg.norm(y - want) / np.linalg.norm(want)
     assert err < 1e-4
+    m.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["Q8_0", "Q5_K", "Q6_K"])
+@pytest.mark.parametrize("T", [13, 300])
+def test_sibling_format_layer_f16_takes_the_tensor_cores(kind, T):
+    """With f16 activations a bank in a sibling format is expanded to f16 (experts with rows only;
+    the same element decoders, one more rounding) and runs the tcgen05 grouped GEMMs instead of
+    the generic bank.  Against the oracle's f32 layer over the exactly dequantised weights."""
+    from mummu_b200 import _lib as L, moe as M
+    H, I, E, K = 512, 256, 4, 2
+    elems, nbytes = FORMATS[kind]
+    code = {"Q8_0": L.Q8_0, "Q5_K": L.Q5_K, "Q6_K": L.Q6_K}[kind]
+    router, _, _, _, x = synth.moe_layer(H, 16, E, T, cfg_seed=29)
+    # random scale bytes make weights of magnitude d * 63 * 31: scales small enough that the 16-bit
+    # intermediate stays far from its range
+    gate = random_blocks(kind, E * I * H // elems, 4, d_scale=0.05)
+    up = random_blocks(kind, E * I * H // elems, 5, d_scale=0.05)
+    down = random_blocks(kind, E * H * I // elems, 6, d_scale=0.05)
+    xh = x.astype(np.float16)
+    m = M.SparseMoeConfig(H, I, E, K).init(act_dtype=L.F16, weight_dtype=code)
+    m.set_router(router)
+    m.set_banks(gate, up, down)
+    m.set_profiling(True)
+    y = m.forward(xh, K, True).astype(np.float32)
+    names = set(m.take_profile())
+    assert {"block_expand", "tc_gate_up", "tc_down"} <= names, names
+    gf = O.dequant_blocks(gate, kind).reshape(E, I, H)
+    uf = O.dequant_blocks(up, kind).reshape(E, I, H)
+    df = O.dequant_blocks(down, kind).reshape(E, H, I)
+    want, _, _ = O.moe_forward(xh.astype(np.float32), router, gf, uf, df, K, True)
+    assert np.abs(y - want).max() / np.abs(want).max() < 2e-2
+    m.set_switch("NO_TC", 1)                                   # the generic bank on the same call
+    y2 = m.forward(xh, K, True).astype(np.float32)
+    assert np.abs(y2 - want).max() / np.abs(want).max() < 2e-2
     m.close()

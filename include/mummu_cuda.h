@@ -19,6 +19,12 @@
  *    (order them with events, or give each stream its own handle; handles can share weights'
  *    source buffers but not scratch).  mummu_moe_set_router / mummu_moe_set_bank wait for the
  *    handle's own stream; work the caller queued on its own streams must have finished first.
+ *  - Device memory is allocated when a handle is created (banks, router, scratch for max_tokens)
+ *    and, once, when a call first needs more: a larger token count than max_tokens, and the f16
+ *    image of a block-quantised bank (first call of more than 256 tokens on Q4_K, first call on a
+ *    Q8_0 / Q5_K / Q6_K bank with f16 activations, first call of a shard of at most 8 experts with
+ *    32 or more rows each).  A call that allocates cannot be inside a stream capture: make the
+ *    first call of each kind before capturing.
  *  - Matrices are row-major.  Router weight: [hidden, experts] (burn `Linear` stores [in, out],
  *    nn/moe.rs:1642) or [experts, hidden] (GGUF `ffn_gate_inp`, models/olmoe.rs:338-339), chosen by
  *    a flag.  Banks: [experts, out, in], byte-identical to GGUF `ffn_{gate,up,down}_exps`
@@ -47,8 +53,9 @@ typedef enum {
     MUMMU_F16  = 1,
     MUMMU_BF16 = 2,
     MUMMU_Q4_K = 3,     /* GGUF Q4_K super-blocks; weights only */
-    /* sibling GGUF formats (gguf.rs:1535-1543, 1731-1797), weights only, computed by the generic
-     * bank (every weight decoded element by element; no fast decode kernel) */
+    /* sibling GGUF formats (gguf.rs:1535-1543, 1731-1797), weights only: with f16 activations the
+     * experts that have rows are expanded to f16 and run the tensor-core GEMMs, otherwise the
+     * generic bank decodes every weight element by element (no packed-weight decode kernel) */
     MUMMU_Q8_0 = 4,     /* 34-byte blocks of 32 */
     MUMMU_Q5_K = 5,     /* 176-byte super-blocks of 256 */
     MUMMU_Q6_K = 6      /* 210-byte super-blocks of 256 */

@@ -506,26 +506,35 @@ __global__ void __launch_bounds__(256) q4k_expand_f16_kernel(const uint8_t* __re
                                                              int64_t n_blocks, int64_t blocks_per_expert,
                                                              const int32_t* __restrict__ counts) {
     const int lane = threadIdx.x & 31;
+    const int j = lane >> 2, chunk = j >> 1, b0 = (lane & 3) * 8;
+    const int jm = j & 3;                                       // position inside the packed scale words
     const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
     for (int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); b < n_blocks; b += warps) {
         if (counts[b / blocks_per_expert] == 0) continue;        // nobody routed here this call
         const uint8_t* blk = src + (size_t)b * Q4K_BLOCK_BYTES;
-        const int j = lane >> 2, chunk = j >> 1, b0 = (lane & 3) * 8;
-        const float d = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
-        const float dmin = __half2float(__ushort_as_half((unsigned short)(blk[2] | (blk[3] << 8))));
-        float sc, mn;
-        q4k_scale_min(blk + 4, j, sc, mn);
-        const float dsc = __fmul_rn(d, sc), off = __fmul_rn(dmin, mn);
+        // the 16-byte head (d, dmin, 12 packed scale bytes) in one load - the same address for the
+        // whole warp - and this lane's 8 quant bytes
+        const uint4 head = *reinterpret_cast<const uint4*>(blk);
         const uint2 raw = *reinterpret_cast<const uint2*>(blk + 16 + chunk * 32 + b0);
-        const uint32_t w[2] = {raw.x, raw.y};
-        __half out[8];
+        const float d = __half2float(__ushort_as_half((unsigned short)(head.x & 0xFFFFu)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(head.x >> 16)));
+        // 6-bit unpack (gguf.rs:1688-1695) on the words: scales[0..3] = head.y, [4..7] = head.z, [8..11] = head.w
+        const uint32_t s0 = (head.y >> (8 * jm)) & 0xFFu, s1 = (head.z >> (8 * jm)) & 0xFFu, s2 = (head.w >> (8 * jm)) & 0xFFu;
+        const uint32_t sc_i = j < 4 ? (s0 & 63u) : ((s2 & 0x0Fu) | ((s0 >> 6) << 4));
+        const uint32_t mn_i = j < 4 ? (s1 & 63u) : ((s2 >> 4) | ((s1 >> 6) << 4));
+        const float dsc = __fmul_rn(d, (float)sc_i), off = __fmul_rn(dmin, (float)mn_i);
+        // the lane's 8 values are all low or all high nibbles of its 8 bytes
+        const uint32_t w0 = (j & 1) ? (raw.x >> 4) & 0x0F0F0F0Fu : raw.x & 0x0F0F0F0Fu;
+        const uint32_t w1 = (j & 1) ? (raw.y >> 4) & 0x0F0F0F0Fu : raw.y & 0x0F0F0F0Fu;
+        uint32_t o[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
-            const float q = (float)((j & 1) ? (byte >> 4) : (byte & 0x0Fu));
-            out[i] = __float2half_rn(__fsub_rn(__fmul_rn(dsc, q), off));
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w = i < 2 ? w0 : w1;
+            const float qa = (float)((w >> (16 * (i & 1))) & 0xFFu), qb = (float)((w >> (16 * (i & 1) + 8)) & 0xFFu);
+            const __half2 h = __floats2half2_rn(__fsub_rn(__fmul_rn(dsc, qa), off), __fsub_rn(__fmul_rn(dsc, qb), off));
+            o[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
-        *reinterpret_cast<uint4*>(dst + (size_t)b * 256 + lane * 8) = *reinterpret_cast<const uint4*>(out);
+        *reinterpret_cast<uint4*>(dst + (size_t)b * 256 + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -557,7 +566,7 @@ int launch_experts_q4k_tc(MummuMoe* m, const void* xs, int64_t rows_cap, const i
     } else {
         LaunchScope scope(m, s, "q4k_expand");
         for (int b = 0; b < 3; ++b) {
-            q4k_expand_f16_kernel<<<148 * 8, 256, 0, s>>>((const uint8_t*)m->bank[b], owner->wexp[b], n_blocks,
+            q4k_expand_f16_kernel<<<148 * 16, 256, 0, s>>>((const uint8_t*)m->bank[b], owner->wexp[b], n_blocks,
                                                           blocks_per_expert, counts);
         }
         MUMMU_CUDA_TRY(cudaGetLastError());

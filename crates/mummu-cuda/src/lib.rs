@@ -9,6 +9,8 @@
 //!  * `CudaBank`   — one MoE layer on one GPU: what `SparseMoe` / `SparseMoePerExpert`
 //!                   (crates/mummu/src/nn/moe.rs:34-39, 201-329) hold when the `cuda-b200` feature is
 //!                   on, with `forward`, `route`, `take_hits` under the reference's names;
+//!  * `CudaTrunk`  — the decode trunk (attention half of every layer, embedding, head) that
+//!                   `impl StaticDecode for Olmoe` (capture.rs:48-107) drives between the banks;
 //!  * `CudaExpert` — one expert of a bank with the method set of `ExpertExec`
 //!                   (nn/moe.rs:348-419).  The trait itself lives in crates/mummu (which depends on
 //!                   this crate, not the other way round); the five-line `impl ExpertExec for
@@ -446,6 +448,89 @@ impl CudaExpert<'_> {
     pub fn evict(&self) {}
     pub fn is_staged(&self) -> bool {
         true
+    }
+}
+
+
+/// The decode trunk of an OLMoE-shaped model on one B200 (`mummu_cuda.h`, section "decode trunk"):
+/// what `impl StaticDecode for Olmoe` (capture.rs:48-107) holds as its `State`.  Every call takes
+/// device pointers and one stream, allocates nothing and reads nothing back, so a step can be
+/// captured once per bucket of keys.
+pub struct CudaTrunk {
+    h: *mut sys::MummuTrunk,
+    cfg: sys::MummuTrunkConfig,
+}
+
+unsafe impl Send for CudaTrunk {}
+
+impl CudaTrunk {
+    /// `StaticDecode::static_bytes` (capture.rs:63-66): device bytes of the weights, the KV cache
+    /// for `slots` sequences of `max_ctx` positions and the scratch.
+    pub fn static_bytes(cfg: &sys::MummuTrunkConfig) -> u64 {
+        unsafe { sys::mummu_trunk_static_bytes(cfg) }
+    }
+
+    /// `StaticDecode::static_state` (capture.rs:68-75).  A shape the kernels do not take is the
+    /// reference's `static_supported() == false`: it comes back as `Unsupported`.
+    pub fn new(cfg: sys::MummuTrunkConfig) -> Result<Self, CudaMoeError> {
+        let mut h = ptr::null_mut();
+        check(unsafe { sys::mummu_trunk_create(&cfg, &mut h) })?;
+        Ok(Self { h, cfg })
+    }
+
+    pub fn config(&self) -> &sys::MummuTrunkConfig {
+        &self.cfg
+    }
+
+    /// One weight tensor (`which` = MUMMU_TRUNK_EMBED .. K_NORM; `layer` ignored for the embedding,
+    /// the final norm and lm_head) as host bytes: f16 matrices `[out, in]`, f32 norm weights.
+    pub fn set_weight(&self, which: i32, layer: usize, bytes: &[u8]) -> Result<(), CudaMoeError> {
+        check(unsafe { sys::mummu_trunk_set_weight(self.h, which, layer as i32, bytes.as_ptr().cast(), bytes.len()) })
+    }
+
+    /// `StaticDecode::seed_static` (capture.rs:105-106) for one layer: `count` positions of keys
+    /// and values from `first` on, device f16 `[kv_heads, count, head_dim]` each.
+    ///
+    /// # Safety
+    /// `k` and `v` are device pointers of that size, valid until `stream` has passed the call.
+    pub unsafe fn kv_write(&self, layer: usize, slot: usize, first: usize, count: usize, k: *const c_void,
+                           v: *const c_void, stream: *mut c_void) -> Result<(), CudaMoeError> {
+        check(sys::mummu_trunk_kv_write(self.h, layer as i32, slot as i32, first as i32, count as i32, k, v, stream))
+    }
+
+    /// One `forward_static` step (capture.rs:77-103; models/olmoe.rs:553-587) over `banks`, one
+    /// `CudaBank` per layer with f16 activations: embedding, then per layer the attention half
+    /// (which first joins the previous layer's expert output to the residual stream) and the
+    /// layer's expert bank, then the head.  `tokens`, `positions`: device int32 `[slots]`;
+    /// `x`, `h2`, `y`: device f16 `[slots, hidden]` scratch; `logits`: device f32 `[slots, vocab]`;
+    /// `argmax`: device int32 `[slots]` or null.  `length`: the bucket of keys attended to.
+    ///
+    /// # Safety
+    /// All pointers are device pointers of the stated sizes, valid until `stream` has passed the
+    /// calls; nothing else uses the banks or this trunk on another stream meanwhile.
+    #[allow(clippy::too_many_arguments)]
+    pub unsafe fn forward_static(&self, banks: &[CudaBank], top_k: usize, norm_topk_prob: bool, tokens: *const i32,
+                                 positions: *const i32, slots: usize, length: usize, x: *mut c_void, h2: *mut c_void,
+                                 y: *mut c_void, logits: *mut f32, argmax: *mut i32, stream: *mut c_void)
+                                 -> Result<(), CudaMoeError> {
+        assert_eq!(banks.len(), self.cfg.layers as usize, "one expert bank per layer");
+        check(sys::mummu_trunk_embed(self.h, tokens, slots as i32, x, stream))?;
+        let mut y_prev: *const c_void = ptr::null();
+        for (layer, bank) in banks.iter().enumerate() {
+            check(sys::mummu_trunk_attention_step(self.h, layer as i32, x, y_prev, positions, slots as i32, length as i32,
+                                                  h2, stream))?;
+            check(sys::mummu_moe_forward(bank.raw(), h2, y, slots as i32, top_k as i32, norm_topk_prob as i32, 1, stream))?;
+            y_prev = y;
+        }
+        check(sys::mummu_trunk_head(self.h, x, y_prev, slots as i32, logits, argmax, stream))
+    }
+}
+
+impl Drop for CudaTrunk {
+    fn drop(&mut self) {
+        unsafe {
+            sys::mummu_trunk_destroy(self.h);
+        }
     }
 }
 

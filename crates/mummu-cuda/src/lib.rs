@@ -485,7 +485,7 @@ impl CudaTrunk {
     /// One weight tensor (`which` = MUMMU_TRUNK_EMBED .. K_NORM; `layer` ignored for the embedding,
     /// the final norm and lm_head) as host bytes: f16 matrices `[out, in]`, f32 norm weights.
     pub fn set_weight(&self, which: i32, layer: usize, bytes: &[u8]) -> Result<(), CudaMoeError> {
-        check(unsafe { sys::mummu_trunk_set_weight(self.h, which, layer as i32, bytes.as_ptr().cast(), bytes.len()) })
+        check(unsafe { sys::mummu_trunk_set_weight(self.h, which, layer as i32, bytes.as_ptr().cast(), bytes.len(), 0) })
     }
 
     /// `StaticDecode::seed_static` (capture.rs:105-106) for one layer: `count` positions of keys

@@ -58,3 +58,47 @@ def test_rust_crate_binds_every_declared_symbol_and_builds_every_source():
     build_rs = open(os.path.join(ROOT, "crates", "mummu-cuda", "build.rs")).read()
     listed = re.findall(r'"([a-z0-9_]+\.cu)"', build_rs[build_rs.index("const SOURCES"):build_rs.index("];")])
     assert sorted(listed) == sorted(build.SOURCES)
+
+
+def _top_level_args(arglist: str) -> int:
+    arglist = arglist.strip()
+    if arglist in ("", "void"):
+        return 0
+    depth, n = 0, 1
+    for ch in arglist:
+        depth += ch in "([<"
+        depth -= ch in ")]>"
+        n += ch == "," and depth == 0
+    return n
+
+
+def test_argument_counts_agree_between_header_ctypes_and_rust(cuda_lib):
+    """Names alone do not catch a parameter added on one side only: the number of parameters of
+    every export must be the same in the header, in the ctypes table and in the Rust `extern "C"`
+    block, and every call of a `sys::` function in the crate must pass that many arguments."""
+    header = open(os.path.join(ROOT, "include", "mummu_cuda.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    h_counts = {m.group(1): _top_level_args(m.group(2))
+                for m in re.finditer(r"\b(mummu_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", header, flags=re.S)}
+    assert set(h_counts) == set(cuda_lib.SYMBOLS)
+    for name, (_, argtypes) in cuda_lib.SYMBOLS.items():
+        assert len(argtypes) == h_counts[name], f"{name}: ctypes has {len(argtypes)} parameters, the header {h_counts[name]}"
+    lib_rs = open(os.path.join(ROOT, "crates", "mummu-cuda", "src", "lib.rs")).read()
+    block = lib_rs[lib_rs.index('extern "C" {'):]
+    block = block[:block.index("\n    }\n")]
+    r_counts = {m.group(1): _top_level_args(m.group(2))
+                for m in re.finditer(r"pub fn (mummu_[a-z0-9_]+)\s*\((.*?)\)\s*(?:->[^;]*)?;", block, flags=re.S)}
+    assert r_counts == h_counts
+    rest = lib_rs[lib_rs.index('extern "C" {') + len(block):]
+    rest = "\n".join(line for line in rest.splitlines() if not line.lstrip().startswith("//"))
+    calls = 0
+    for m in re.finditer(r"sys::(mummu_[a-z0-9_]+)\s*\(", rest):
+        depth, i = 1, m.end()
+        while depth:
+            depth += rest[i] in "([{"
+            depth -= rest[i] in ")]}"
+            i += 1
+        got = _top_level_args(rest[m.end():i - 1])
+        assert got == h_counts[m.group(1)], f"a call of {m.group(1)} in lib.rs passes {got} arguments, it takes {h_counts[m.group(1)]}"
+        calls += 1
+    assert calls >= 20

@@ -91,14 +91,17 @@ static void free_scratch(MummuMoe* m) {
         m->logits = nullptr; m->tile_done = nullptr; m->ids = nullptr; m->wts = nullptr;
         m->row_token = nullptr; m->pos = nullptr; m->xs = nullptr; m->hact = nullptr; m->ys = nullptr;
         m->io_x = nullptr; m->io_y = nullptr;
+        m->whist = nullptr;
+        m->whist_elems = 0;
         m->cap_tokens = 0;
         m->scratch_borrowed = false;
         return;
     }
-    cudaFree(m->logits); cudaFree(m->tile_done); cudaFree(m->ids); cudaFree(m->wts);
+    cudaFree(m->logits); cudaFree(m->tile_done); cudaFree(m->ids); cudaFree(m->wts); cudaFree(m->whist);
     cudaFree(m->row_token); cudaFree(m->pos); cudaFree(m->xs); cudaFree(m->hact); cudaFree(m->ys);
     cudaFree(m->io_x); cudaFree(m->io_y);
-    m->logits = nullptr; m->tile_done = nullptr; m->ids = nullptr; m->wts = nullptr;
+    m->logits = nullptr; m->tile_done = nullptr; m->ids = nullptr; m->wts = nullptr; m->whist = nullptr;
+    m->whist_elems = 0;
     m->row_token = nullptr; m->pos = nullptr; m->xs = nullptr; m->hact = nullptr; m->ys = nullptr;
     m->io_x = nullptr; m->io_y = nullptr;
     m->cap_tokens = 0;
@@ -133,6 +136,8 @@ int ensure_scratch(MummuMoe* m, int64_t tokens) {
     if ((rc = dev_alloc(&m->ids, (size_t)rows))) return rc;
     if ((rc = dev_alloc(&m->wts, (size_t)rows))) return rc;
     if ((rc = dev_alloc(&m->row_token, (size_t)rows))) return rc;
+    m->whist_elems = ((rows + 2047) / 2048) * 8 * (int64_t)c.experts;
+    if ((rc = dev_alloc(&m->whist, (size_t)m->whist_elems))) return rc;
     if ((rc = dev_alloc(&m->pos, (size_t)rows))) return rc;
     if ((rc = dev_alloc((uint8_t**)&m->xs, (size_t)rows * c.hidden * act))) return rc;
     if ((rc = dev_alloc((float**)&m->hact, (size_t)rows * c.inter))) return rc;
@@ -819,6 +824,7 @@ int32_t mummu_moe_adopt_scratch(MummuMoe* m, MummuMoe* donor) {
     m->logits = donor->logits; m->tile_done = donor->tile_done; m->ids = donor->ids; m->wts = donor->wts;
     m->row_token = donor->row_token; m->pos = donor->pos; m->xs = donor->xs; m->hact = donor->hact;
     m->ys = donor->ys; m->io_x = donor->io_x; m->io_y = donor->io_y;
+    m->whist = donor->whist; m->whist_elems = donor->whist_elems;
     m->cap_tokens = donor->cap_tokens;
     m->scratch_borrowed = true;
     m->scratch_donor = donor;

@@ -210,6 +210,8 @@ struct MummuMoe {
     int32_t* offsets = nullptr;     // [experts + 1]
     int32_t* active = nullptr;      // [experts] ids of experts with rows this call
     int32_t* n_active = nullptr;    // [1]
+    int32_t* whist = nullptr;       // large-call grouping: per (warp of 256 pairs, expert) counts, then first rows
+    int64_t whist_elems = 0;
     // expert-parallel return path: the local rows as segments (local expert, source rank)
     int32_t* ret_seg = nullptr;     // [experts_local * 16 + 1] first local row of every segment
     int32_t* ret_dst = nullptr;     // [experts_local * 16] the segment's first row in its source's buffer

@@ -1229,10 +1229,119 @@ __global__ void __launch_bounds__(P_THREADS) permute_kernel(const int32_t* ids, 
     }
 }
 
+// Large calls: a counting sort in three launches instead of one block per expert scanning every
+// pair.  A warp owns 256 consecutive pairs (8 steps of 32, in index order, so the order inside an
+// expert stays ascending by token):
+//   count   : per-warp histogram by expert (warp match)            -> whist[warp][expert]
+//   scan    : per expert, exclusive prefix over the warps + the expert's first row
+//             (also offsets and the heaviest-first list of active experts) -> whist in place
+//   scatter : the same walk again; pos = whist[warp][expert] + earlier pairs of the expert in the warp
+constexpr int PS_PAIRS_PER_WARP = 256, PS_WARPS = 8, PS_PAIRS_PER_BLOCK = PS_PAIRS_PER_WARP * PS_WARPS;
+
+__global__ void __launch_bounds__(PS_WARPS * 32) permute_count_kernel(const int32_t* __restrict__ ids, int64_t n, int E,
+                                                                      int32_t* __restrict__ whist) {
+    extern __shared__ int32_t s_tbl[];                           // [PS_WARPS][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int32_t* tbl = s_tbl + warp * E;
+    for (int e = lane; e < E; e += 32) tbl[e] = 0;
+    __syncwarp();
+    const int64_t first = ((int64_t)blockIdx.x * PS_WARPS + warp) * PS_PAIRS_PER_WARP;
+    for (int st = 0; st < PS_PAIRS_PER_WARP / 32; ++st) {
+        const int64_t i = first + st * 32 + lane;
+        const int e = i < n ? ids[i] : -1;
+        const int key = (e >= 0 && e < E) ? e : -1 - lane;       // pairs without a valid expert match nobody
+        const unsigned mask = __match_any_sync(0xFFFFFFFFu, key);
+        if (key >= 0 && lane == __ffs(mask) - 1) tbl[key] += __popc(mask);
+        __syncwarp();
+    }
+    int32_t* out = whist + ((int64_t)blockIdx.x * PS_WARPS + warp) * E;
+    for (int e = lane; e < E; e += 32) out[e] = tbl[e];
+}
+
+// one warp per expert
+__global__ void __launch_bounds__(32) permute_scan_kernel(const int32_t* __restrict__ counts, int E, int64_t n_warps,
+                                                          int32_t* __restrict__ whist, int32_t* offsets, int32_t* active,
+                                                          int32_t* n_active) {
+    const int e = blockIdx.x, lane = threadIdx.x;
+    const int mine = counts[e];
+    int before = 0, nz = 0;
+    for (int i = lane; i < E; i += 32) {
+        const int c = counts[i];
+        if (i < e) before += c;
+        nz += (c > mine || (c == mine && i < e)) && c > 0;       // work order: most rows first, then lower id
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        before += __shfl_xor_sync(0xFFFFFFFFu, before, off);
+        nz += __shfl_xor_sync(0xFFFFFFFFu, nz, off);
+    }
+    if (lane == 0) {
+        if (offsets) {
+            offsets[e] = before;
+            if (e == E - 1) offsets[E] = before + mine;
+        }
+        if (active && mine > 0) active[nz] = e;
+        if (n_active && mine > 0) atomicMax(n_active, nz + 1);
+    }
+    int run = before;
+    for (int64_t k0 = 0; k0 < n_warps; k0 += 32) {
+        const int64_t k = k0 + lane;
+        const int c = k < n_warps ? whist[k * E + e] : 0;
+        int incl = c;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int up = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+            if (lane >= off) incl += up;
+        }
+        if (k < n_warps) whist[k * E + e] = run + incl - c;
+        run += __shfl_sync(0xFFFFFFFFu, incl, 31);
+    }
+}
+
+__global__ void __launch_bounds__(PS_WARPS * 32) permute_scatter_kernel(const int32_t* __restrict__ ids, int64_t n, int top_k,
+                                                                        int E, const int32_t* __restrict__ whist,
+                                                                        int32_t* __restrict__ row_token,
+                                                                        int32_t* __restrict__ pos) {
+    extern __shared__ int32_t s_tbl[];                           // [PS_WARPS][E]: next row of the expert for this warp
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int32_t* nxt = s_tbl + warp * E;
+    const int32_t* base = whist + ((int64_t)blockIdx.x * PS_WARPS + warp) * E;
+    for (int e = lane; e < E; e += 32) nxt[e] = base[e];
+    __syncwarp();
+    const int64_t first = ((int64_t)blockIdx.x * PS_WARPS + warp) * PS_PAIRS_PER_WARP;
+    for (int st = 0; st < PS_PAIRS_PER_WARP / 32; ++st) {
+        const int64_t i = first + st * 32 + lane;
+        const int e = i < n ? ids[i] : -1;
+        const int key = (e >= 0 && e < E) ? e : -1 - lane;
+        const unsigned mask = __match_any_sync(0xFFFFFFFFu, key);
+        if (key >= 0) {
+            const int p = nxt[key] + __popc(mask & ((1u << lane) - 1u));
+            if (pos) pos[i] = p;
+            if (row_token) row_token[p] = (int32_t)(i / top_k);
+        }
+        __syncwarp();
+        if (key >= 0 && lane == __ffs(mask) - 1) nxt[key] += __popc(mask);
+        __syncwarp();
+    }
+}
+
 int launch_permute(MummuMoe* m, const int32_t* ids, int64_t tokens, int top_k,
                    const int32_t* counts, int32_t* offsets, int32_t* row_token, int32_t* pos,
                    cudaStream_t s) {
     MUMMU_CUDA_TRY(cudaMemsetAsync(m->n_active, 0, sizeof(int32_t), s));
+    const int64_t n = tokens * top_k;
+    const int E = m->cfg.experts;
+    const int64_t blocks = (n + PS_PAIRS_PER_BLOCK - 1) / PS_PAIRS_PER_BLOCK;
+    const size_t tbl_bytes = (size_t)PS_WARPS * E * sizeof(int32_t);
+    // three launches cost about 15 us of launch latency: they pay from about 64 K pairs on
+    if (n >= 65536 && m->whist && blocks * PS_WARPS * E <= m->whist_elems && tbl_bytes <= 48 * 1024) {
+        LaunchScope scope(m, s, "permute");
+        permute_count_kernel<<<(unsigned)blocks, PS_WARPS * 32, tbl_bytes, s>>>(ids, n, E, m->whist);
+        permute_scan_kernel<<<E, 32, 0, s>>>(counts, E, blocks * PS_WARPS, m->whist, offsets, m->active, m->n_active);
+        permute_scatter_kernel<<<(unsigned)blocks, PS_WARPS * 32, tbl_bytes, s>>>(ids, n, top_k, E, m->whist, row_token, pos);
+        MUMMU_CUDA_TRY(cudaGetLastError());
+        return MUMMU_OK;
+    }
     LaunchScope scope(m, s, "permute");
     permute_kernel<<<m->cfg.experts, P_THREADS, 0, s>>>(ids, tokens * top_k, top_k, m->cfg.experts,
                                                         counts, offsets, row_token, pos, m->active,

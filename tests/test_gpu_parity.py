@@ -470,6 +470,32 @@ def test_route_grouped_equals_route_then_permute(M, cuda_lib, T):
     m.close()
 
 
+@pytest.mark.parametrize("T,E,K", [(1100, 64, 8), (9001, 128, 8), (22000, 20, 3)])
+def test_permute_of_a_large_call_is_the_stable_sort_by_expert(M, cuda_lib, T, E, K):
+    """From 65536 (token, slot) pairs on, grouping is a three-launch counting sort (the last two
+    shapes); it must give what the one-launch kernel gives: rows ordered by expert, ascending token
+    inside an expert (`Routing.per_expert` of nn/moe.rs:275-289), counts and offsets."""
+    import torch
+    L = cuda_lib
+    H = 256
+    router, gate, up, down, x = synth.moe_layer(H, 16, E, T, cfg_seed=19)
+    m = make_layer(M, L, H, 16, E, K, L.F32, L.F32, router, gate, up, down)
+    xd = torch.from_numpy(x).cuda()
+    ids, w, counts, offsets, row_token, pos = m.route_grouped(xd, K, False)
+    m.sync()
+    idn = ids.cpu().numpy().reshape(-1)
+    want_counts = np.bincount(idn, minlength=E)
+    assert np.array_equal(counts.cpu().numpy(), want_counts)
+    assert np.array_equal(offsets.cpu().numpy(), np.concatenate([[0], np.cumsum(want_counts)]))
+    order = np.argsort(idn, kind="stable")
+    assert np.array_equal(row_token.cpu().numpy(), order // K)
+    assert np.array_equal(pos.cpu().numpy()[order], np.arange(T * K))
+    y = m.forward(xd, K, False)                      # and the layer that runs on this plan
+    want, _, _ = O.moe_forward(x[:64], router, gate, up, down, K, False)
+    assert rel_err(y[:64].cpu().numpy(), want) < TOL_F32
+    m.close()
+
+
 def test_staged_calls_match_whole_layer(M, cuda_lib):
     """permute -> experts_grouped -> combine on device tensors == forward."""
     import torch

@@ -1424,16 +1424,19 @@ __global__ void __launch_bounds__(256) combine_vec8_kernel(const TY* ys, const i
     for (int h = (blockIdx.y * blockDim.x + threadIdx.x) * 8; h < H; h += gridDim.y * blockDim.x * 8) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int r0 = 0; r0 < top_k; r0 += BATCH) {
-            float v[BATCH][8];
+            // the rows stay as loaded (16-bit rows: 4 registers each) until they are summed: the
+            // kernel lives on loads in flight, and registers decide how many blocks an SM holds
+            Vec8<TY> raw[BATCH];
 #pragma unroll
             for (int u = 0; u < BATCH; ++u)
-                if (r0 + u < top_k) load8(ys + (size_t)s_pos[r0 + u] * H + h, v[u]);
+                if (r0 + u < top_k) raw[u] = *reinterpret_cast<const Vec8<TY>*>(ys + (size_t)s_pos[r0 + u] * H + h);
 #pragma unroll
             for (int u = 0; u < BATCH; ++u)
                 if (r0 + u < top_k) {
                     const float wv = s_w[r0 + u];
+                    const TY* e = reinterpret_cast<const TY*>(&raw[u]);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(wv, v[u][i]));
+                    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(wv, to_f32(e[i])));
                 }
         }
         store8(out + t * H + h, acc);

@@ -348,13 +348,24 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
 }
 
-// gather the routed rows in sorted order: xs[p, :] = x[row_token[p], :]   (16-bit rows)
-__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* x, const int32_t* row_token, uint4* xs,
-                                                          int64_t rows, int vec_per_row) {
-    for (int64_t p = blockIdx.x; p < rows; p += gridDim.x) {
+// gather the routed rows in sorted order: xs[p, :] = x[row_token[p], :]   (16-bit rows).  A warp per
+// row, up to eight 16-byte loads per lane issued before the first store.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ row_token,
+                                                          uint4* __restrict__ xs, int64_t rows, int vec_per_row) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t p = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < rows; p += warps) {
         const uint4* src = x + (size_t)row_token[p] * vec_per_row;
         uint4* dst = xs + (size_t)p * vec_per_row;
-        for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = src[i];
+        for (int i0 = lane; i0 < vec_per_row; i0 += 256) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (i0 + 32 * u < vec_per_row) v[u] = src[i0 + 32 * u];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (i0 + 32 * u < vec_per_row) dst[i0 + 32 * u] = v[u];
+        }
     }
 }
 
@@ -579,7 +590,7 @@ int launch_gather_rows(MummuMoe* m, const void* x, const int32_t* row_token, voi
                        cudaStream_t s) {
     if (rows == 0) return MUMMU_OK;
     const int vec = m->cfg.hidden * 2 / 16;
-    int64_t blocks = rows < 148 * 16 ? rows : 148 * 16;
+    int64_t blocks = rows < 8 ? 1 : (rows / 8 < 148 * 8 ? (rows + 7) / 8 : 148 * 8);     // a warp per row
     LaunchScope scope(m, s, "gather_rows");
     gather_rows_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint4*)x, row_token, (uint4*)xs, rows, vec);
     MUMMU_CUDA_TRY(cudaGetLastError());

@@ -91,3 +91,57 @@ def test_fold_hits_sums_the_copies():
     for r in plan.hosts[0]:
         slot_hits[r * 3 + plan.slot_of(0, r)] = 5
     assert plan.fold_hits(slot_hits).tolist() == [10, 0, 0, 0]
+
+
+def test_random_plans_are_valid_and_conserve_load():
+    """Random shapes and hotness (zeros, spikes, ties included): every plan is a valid placement,
+    the loads it predicts add up to the total, and the folded slot hits of a simulated routing
+    give the experts' own counts back."""
+    hyp = pytest.importorskip("hypothesis")
+    st = hyp.strategies
+
+    @hyp.settings(max_examples=120, deadline=None, derandomize=True)
+    @hyp.given(st.data())
+    def run(data):
+        world = data.draw(st.integers(1, 8))
+        E = data.draw(st.integers(1, 40))
+        need = -(-E // world)
+        slots = data.draw(st.integers(need, need + 4))
+        kind = data.draw(st.sampled_from(["floats", "spike", "ties", "zeros", "empty"]))
+        if kind == "floats":
+            h = data.draw(st.lists(st.floats(0.0, 1e6, allow_nan=False), min_size=E, max_size=E))
+        elif kind == "spike":
+            h = [1.0] * E
+            h[data.draw(st.integers(0, E - 1))] = 1e4
+        elif kind == "ties":
+            h = [float(data.draw(st.integers(0, 2))) for _ in range(E)]
+        elif kind == "zeros":
+            h = [0.0] * E
+        else:
+            h = []
+        plan = P.plan_placement(h, E, world, slots)
+        assert plan.slot_expert.shape == (world, slots)
+        for r in range(world):
+            row = plan.slot_expert[r][plan.slot_expert[r] >= 0]
+            assert len(set(row.tolist())) == len(row)
+        for e in range(E):
+            assert plan.hosts[e] and plan.hosts[e] == sorted(r for r in range(world) if e in plan.slot_expert[r])
+        tables = [plan.route_table(s) for s in range(world)]
+        for s in range(world):
+            for e in range(E):
+                r, slot = divmod(int(tables[s][e]), slots)
+                assert plan.slot_expert[r, slot] == e
+        hh = np.asarray(h if len(h) else [1.0] * E, dtype=np.float64)
+        assert np.isclose(plan.rank_loads(hh).sum(), hh.sum(), rtol=1e-9, atol=1e-12)
+        # a routing drawn per source rank, counted per slot, folds back to the experts' counts
+        seed = data.draw(st.integers(0, 2**31 - 1))
+        rng = np.random.default_rng(seed)
+        slot_hits = np.zeros(plan.virtual_experts, dtype=np.int64)
+        per_expert = np.zeros(E, dtype=np.int64)
+        for s in range(world):
+            ids = rng.integers(0, E, size=50)
+            np.add.at(per_expert, ids, 1)
+            np.add.at(slot_hits, tables[s][ids], 1)
+        assert np.array_equal(plan.fold_hits(slot_hits).astype(np.int64), per_expert)
+
+    run()
